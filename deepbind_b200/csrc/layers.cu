@@ -1,0 +1,162 @@
+// Layer arithmetic that the reference evaluates through generic smat array
+// expressions, one launch and one HBM round trip per operator
+// (code/libs/deepity/deepity/std/elemwise.py:71-82,162-180, softmax.py:50-77,
+// loss.py:52-155).  Plain-pointer f32 entry points; reductions use a fixed
+// order so that repeated runs agree bit for bit (the reference's reduce_y is
+// also free of atomics, smat_cuda/reduce_y.cuh:52-126).
+#include "db_common.cuh"
+
+namespace db {
+
+#define GRID_STRIDE(i, n) for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (n); i += (size_t)gridDim.x * blockDim.x)
+
+__global__ void bias_add_kernel(float* Z, const float* X, const float* b, size_t n, unsigned ncol)
+{
+	GRID_STRIDE(i, n) Z[i] = X[i] + b[i % ncol];
+}
+
+__global__ void relu_kernel(float* Z, const float* X, size_t n)
+{
+	GRID_STRIDE(i, n) Z[i] = fmaxf(0.0f, X[i]);
+}
+
+// dZ * sign(Z) with Z the rectified output, so the factor is 0 or 1 (elemwise.py:78).
+__global__ void relu_bprop_kernel(float* dX, const float* dZ, const float* Z, size_t n)
+{
+	GRID_STRIDE(i, n) { float z = Z[i]; dX[i] = dZ[i] * (z > 0.0f ? 1.0f : (z < 0.0f ? -1.0f : 0.0f)); }
+}
+
+__global__ void logistic_kernel(float* Z, const float* X, size_t n)
+{
+	GRID_STRIDE(i, n) Z[i] = 1.0f / (1.0f + expf(-X[i]));
+}
+
+// Column sums, stage 1: a CTA owns 256 rows x 32 columns; 8 row slices are
+// summed by 8 thread groups and combined in slice order.
+__global__ void __launch_bounds__(256)
+colsum_stage1(const float* __restrict__ A, unsigned nrow, unsigned ncol, float* __restrict__ partial)
+{
+	__shared__ float part[8][32];
+	const unsigned c = blockIdx.y * 32 + threadIdx.x % 32, slice = threadIdx.x / 32;
+	const unsigned r0 = blockIdx.x * 256, r1 = min(nrow, r0 + 256);
+	float s = 0.0f;
+	if (c < ncol)
+		for (unsigned r = r0 + slice; r < r1; r += 8) s += A[(size_t)r * ncol + c];
+	part[slice][threadIdx.x % 32] = s;
+	__syncthreads();
+	if (slice == 0 && c < ncol) {
+		float t = part[0][threadIdx.x];
+		for (int k = 1; k < 8; ++k) t += part[k][threadIdx.x];
+		partial[(size_t)blockIdx.x * ncol + c] = t;
+	}
+}
+
+__global__ void colsum_stage2(float* __restrict__ out, const float* __restrict__ partial, unsigned ncol, unsigned nparts)
+{
+	unsigned c = blockIdx.x * blockDim.x + threadIdx.x;
+	if (c >= ncol) return;
+	float s = 0.0f;
+	for (unsigned p = 0; p < nparts; ++p) s += partial[(size_t)p * ncol + c];
+	out[c] = s;
+}
+
+// One CTA per output column: masked loss mean and dZ = maskout(Z-Y)/nrow.
+__global__ void __launch_bounds__(256)
+loss_kernel(int kind, const float* __restrict__ Z, const float* __restrict__ Y, const uint8_t* __restrict__ Ymask,
+            const uint8_t* __restrict__ Zmask, unsigned nrow, unsigned ncol, float* __restrict__ loss_out, float* __restrict__ dZ)
+{
+	__shared__ float red[256];
+	const unsigned c = blockIdx.x;
+	const float inv = 1.0f / (float)nrow;
+	float s = 0.0f;
+	for (unsigned r = threadIdx.x; r < nrow; r += blockDim.x) {
+		size_t i = (size_t)r * ncol + c;
+		float z = Z[i], y = Y[i];
+		bool keep = (!Ymask || Ymask[i]) && (!Zmask || Zmask[i]);
+		float l;
+		if (kind == 0) { float d = z - y; l = d * d; }
+		else l = logf(fmaxf(1e-15f, z)) * y + logf(fmaxf(1e-15f, 1.0f - z)) * (1.0f - y);
+		if (keep) s += l;
+		if (dZ) dZ[i] = keep ? (z - y) * inv : 0.0f;
+	}
+	red[threadIdx.x] = s;
+	__syncthreads();
+	for (unsigned w = 128; w > 0; w >>= 1) {
+		if (threadIdx.x < w) red[threadIdx.x] += red[threadIdx.x + w];
+		__syncthreads();
+	}
+	if (threadIdx.x == 0 && loss_out)
+		loss_out[c] = (kind == 0 ? 0.5f : -1.0f) * (red[0] * inv);
+}
+
+}  // namespace db
+
+using namespace db;
+
+DB_EXPORT void db_bias_add(float* Z, const float* X, const float* b, uint32_t nrow, uint32_t ncol)
+{
+	DB_API_TRY
+	size_t n = (size_t)nrow * ncol;
+	if (!n) return;
+	DB_REQUIRE(Z && X && b, "ValueError: db_bias_add got a NULL pointer");
+	bias_add_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(Z, X, b, n, ncol);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+DB_EXPORT void db_relu(float* Z, const float* X, size_t n)
+{
+	DB_API_TRY
+	if (!n) return;
+	DB_REQUIRE(Z && X, "ValueError: db_relu got a NULL pointer");
+	relu_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(Z, X, n);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+DB_EXPORT void db_relu_bprop(float* dX, const float* dZ, const float* Z, size_t n)
+{
+	DB_API_TRY
+	if (!n) return;
+	DB_REQUIRE(dX && dZ && Z, "ValueError: db_relu_bprop got a NULL pointer");
+	relu_bprop_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(dX, dZ, Z, n);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+DB_EXPORT void db_logistic(float* Z, const float* X, size_t n)
+{
+	DB_API_TRY
+	if (!n) return;
+	DB_REQUIRE(Z && X, "ValueError: db_logistic got a NULL pointer");
+	logistic_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(Z, X, n);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+DB_EXPORT void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t ncol)
+{
+	DB_API_TRY
+	if (!ncol) return;
+	DB_REQUIRE(out && (A || !nrow), "ValueError: db_colsum got a NULL pointer");
+	if (!nrow) { DB_CUDA(cudaMemsetAsync(out, 0, (size_t)ncol * 4, state().stream)); return; }
+	unsigned parts = divup(nrow, 256u);
+	float* partial = (float*)scratch((size_t)parts * ncol * sizeof(float));
+	colsum_stage1<<<dim3(parts, divup(ncol, 32u)), 256, 0, state().stream>>>(A, nrow, ncol, partial);
+	DB_LAUNCH_CHECK();
+	colsum_stage2<<<divup(ncol, 128u), 128, 0, state().stream>>>(out, partial, ncol, parts);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+DB_EXPORT void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, const uint8_t* Zmask,
+                       uint32_t nrow, uint32_t ncol, float* loss_out, float* dZ)
+{
+	DB_API_TRY
+	DB_REQUIRE(kind == 0 || kind == 1, "ValueError: loss kind must be 0 (mse) or 1 (nll)");
+	if (!nrow || !ncol) return;
+	DB_REQUIRE(Z && Y, "ValueError: db_loss got a NULL pointer");
+	loss_kernel<<<ncol, 256, 0, state().stream>>>(kind, Z, Y, Ymask, Zmask, nrow, ncol, loss_out, dZ);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}

@@ -1,0 +1,425 @@
+// Fused motif scan + bias + rectify + region pooling, forward and backward, in
+// FP32 lookup-add form.  The per-position activation [npos, nf] that the
+// reference writes and re-reads eight times per training step never leaves the
+// SM: a CTA scans a tile of rows into shared memory and pools it there.
+//
+// Arithmetic is that of the reference chain, operator by operator:
+//   scan      corr1ord.cuh:108-164   taps ascending from +0; N = ((W0+W1)+W2+W3)/4; 254 adds 0
+//   bias      elemwise.py:171        Z + b
+//   rectify   elemwise.py:74-78      max(0, .)
+//   pooling   poolrgn.cuh:44-160     rows ascending; strict '>' (first maximum wins); running
+//                                    sum in row order; mean = sum / integer row count
+// so max, argmax, sum and mean agree with the unfused path bit for bit.
+//
+// Work split.  A CTA owns up to 8 regions (sequences) x FB filters.  In the scan
+// phase a thread owns one row x 16 filters: a warp is 32 consecutive rows of the
+// same 16 filters, so the 32 lanes read at most six distinct 16-byte entries of
+// one 128-byte line of the lookup table (conflict-free, broadcast).  The table
+// lut[tap][filter quad][code 0..7][4] holds W, the N mean and a zero row.  The
+// scan is bound by the shared-memory return path (one 4-byte operand per add),
+// not by FP32 issue; the ALU work around it is free.  In the pool phase a thread
+// owns one (region, filter) column and walks the tile's rows in order.
+#include "db_common.cuh"
+
+namespace db {
+
+static constexpr int TR = 128;           // rows per tile
+static constexpr int GMAX = TR / 16;     // regions per CTA (one pool thread per (region, filter))
+
+__device__ __forceinline__ unsigned code16_of(unsigned x)
+{
+	return x < 4u ? x * 16u : (x == 254u ? 80u : 64u);
+}
+
+struct fwd_args {
+	const float* W; const float* bias; const uint8_t* X; const uint32_t* R;
+	float* pooled; uint32_t* argmax; uint16_t* actmask;
+	unsigned m, nf, npos, n, nregion, G, FB;
+	int relu, ptype;
+};
+
+// Builds lut[j][q][c][4] for the CTA's filter block.
+__device__ __forceinline__ void build_lut(float* lut, const float* __restrict__ W, unsigned m, unsigned nf,
+                                           unsigned f0, unsigned FB)
+{
+	const unsigned NQ = FB / 4;
+	for (unsigned t = threadIdx.x; t < m * FB; t += blockDim.x) {
+		unsigned j = t / FB, f = t % FB;
+		float w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
+		if (f0 + f < nf) {
+			w0 = W[(size_t)(4*j+0)*nf + f0 + f]; w1 = W[(size_t)(4*j+1)*nf + f0 + f];
+			w2 = W[(size_t)(4*j+2)*nf + f0 + f]; w3 = W[(size_t)(4*j+3)*nf + f0 + f];
+		}
+		float z = w0; z += w1; z += w2; z += w3;
+		float* e = lut + ((size_t)(j * NQ + f / 4) * 8) * 4 + (f & 3);
+		e[0] = w0; e[4] = w1; e[8] = w2; e[12] = w3; e[16] = z * 0.25f; e[20] = 0.f; e[24] = 0.f; e[28] = 0.f;
+	}
+}
+
+// z[16] for the row whose window starts at byte `rl` of the staged codes.
+template <int M>
+__device__ __forceinline__ void scan_row(const unsigned char* lutp, unsigned stride, const uint8_t* xs,
+                                         unsigned rl, unsigned m, float (&z)[16])
+{
+	#pragma unroll
+	for (int v = 0; v < 16; ++v) z[v] = 0.f;
+	if constexpr (M > 0) {
+		constexpr int NW = (M + 3) / 4;
+		const uint32_t* xw = reinterpret_cast<const uint32_t*>(xs) + (rl >> 2);
+		const unsigned sh = (rl & 3u) * 8u;
+		uint32_t win[NW];
+		#pragma unroll
+		for (int i = 0; i < NW; ++i) win[i] = __funnelshift_r(xw[i], xw[i + 1], sh);
+		#pragma unroll
+		for (int j = 0; j < M; ++j) {
+			unsigned c16 = (win[j >> 2] >> (8 * (j & 3))) & 0xffu;
+			const float4* e = reinterpret_cast<const float4*>(lutp + (size_t)j * stride + c16);
+			float4 a = e[0], b = e[8], c = e[16], d = e[24];
+			z[0] += a.x; z[1] += a.y; z[2]  += a.z; z[3]  += a.w;
+			z[4] += b.x; z[5] += b.y; z[6]  += b.z; z[7]  += b.w;
+			z[8] += c.x; z[9] += c.y; z[10] += c.z; z[11] += c.w;
+			z[12] += d.x; z[13] += d.y; z[14] += d.z; z[15] += d.w;
+		}
+	} else {
+		for (unsigned j = 0; j < m; ++j) {
+			unsigned c16 = xs[rl + j];
+			const float4* e = reinterpret_cast<const float4*>(lutp + (size_t)j * stride + c16);
+			float4 a = e[0], b = e[8], c = e[16], d = e[24];
+			z[0] += a.x; z[1] += a.y; z[2]  += a.z; z[3]  += a.w;
+			z[4] += b.x; z[5] += b.y; z[6]  += b.z; z[7]  += b.w;
+			z[8] += c.x; z[9] += c.y; z[10] += c.z; z[11] += c.w;
+			z[12] += d.x; z[13] += d.y; z[14] += d.z; z[15] += d.w;
+		}
+	}
+}
+
+template <int M>
+__global__ void __launch_bounds__(512)
+scanpool_fwd_kernel(const fwd_args a)
+{
+	extern __shared__ __align__(16) unsigned char smem[];
+	const unsigned m = M > 0 ? (unsigned)M : a.m;
+	const unsigned FB = a.FB, NQ = FB / 4;
+	float* lut = reinterpret_cast<float*>(smem);                       // m*NQ*32 floats
+	float* act = lut + (size_t)m * NQ * 32;                            // FB*(TR+1) floats
+	uint8_t* xs = reinterpret_cast<uint8_t*>(act + (size_t)FB * (TR + 1));   // TR + m + 8 bytes (4-aligned)
+	__shared__ unsigned rg0[GMAX], rg1[GMAX];
+	__shared__ unsigned s_lo, s_hi, s_sum;
+
+	const unsigned f0 = blockIdx.y * FB;
+	const unsigned g0 = blockIdx.x * a.G;
+	const unsigned ng = min(a.G, a.nregion - g0);
+	build_lut(lut, a.W, m, a.nf, f0, FB);
+	if (threadIdx.x == 0) {
+		unsigned lo = 0xffffffffu, hi = 0, sum = 0;
+		for (unsigned g = 0; g < ng; ++g) {
+			unsigned r0 = a.R[2 * (g0 + g)], r1 = a.R[2 * (g0 + g) + 1];
+			if (r1 <= r0) r1 = r0 + 1;          // an empty region still reads its first row (poolrgn.cuh:60)
+			rg0[g] = r0; rg1[g] = r1;
+			lo = min(lo, r0); hi = max(hi, r1); sum += r1 - r0;
+		}
+		s_lo = lo; s_hi = hi; s_sum = sum;
+	}
+	__syncthreads();
+	// One span over all regions when they sit close together (the batch layout),
+	// else one span per region.
+	const bool one_span = (s_hi - s_lo) <= 2 * s_sum;
+	const unsigned nspan = one_span ? 1 : ng;
+
+	// scan-phase identity
+	const unsigned rl = threadIdx.x % TR, fg = threadIdx.x / TR;
+	const unsigned char* lutp = reinterpret_cast<const unsigned char*>(lut) + fg * 512;
+	const unsigned stride = NQ * 128;
+	float bv[16];
+	#pragma unroll
+	for (int v = 0; v < 16; ++v) {
+		unsigned f = f0 + fg * 16 + v;
+		bv[v] = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
+	}
+	// pool-phase identity and state
+	const unsigned pg = threadIdx.x / FB, pf = threadIdx.x % FB;
+	const bool pool_thread = pg < ng && f0 + pf < a.nf;
+	float xmax = 0.f, xsum = 0.f; unsigned xidx = 0; bool started = false;
+
+	for (unsigned s = 0; s < nspan; ++s) {
+		const unsigned lo = one_span ? s_lo : rg0[s], hi = one_span ? s_hi : rg1[s];
+		for (unsigned t0 = lo; t0 < hi; t0 += TR) {
+			__syncthreads();
+			for (unsigned t = threadIdx.x; t < TR + m + 3; t += blockDim.x) {
+				unsigned i = t0 + t;
+				xs[t] = (uint8_t)(i < a.npos ? code16_of(a.X[i]) : 80u);
+			}
+			__syncthreads();
+			const unsigned row = t0 + rl;
+			if (row < hi) {
+				float z[16];
+				if (row < a.n) scan_row<M>(lutp, stride, xs, rl, m, z);
+				else {
+					#pragma unroll
+					for (int v = 0; v < 16; ++v) z[v] = 0.f;
+				}
+				unsigned bits = 0;
+				#pragma unroll
+				for (int v = 0; v < 16; ++v) {
+					float x = z[v];
+					if (a.bias) x = x + bv[v];
+					if (a.relu) x = x > 0.f ? x : 0.f;
+					if (x > 0.f) bits |= 1u << v;
+					act[(fg * 16 + v) * (TR + 1) + rl] = x;
+				}
+				if (a.actmask && f0 + fg * 16 < a.nf)
+					a.actmask[(size_t)row * ((a.nf + 15) / 16) + (f0 / 16 + fg)] = (uint16_t)bits;
+			}
+			__syncthreads();
+			if (pool_thread && (one_span || pg == s)) {
+				unsigned r0 = max(rg0[pg], t0), r1 = min(rg1[pg], min(hi, t0 + TR));
+				const float* col = act + pf * (TR + 1);
+				for (unsigned r = r0; r < r1; ++r) {
+					float v = col[r - t0];
+					if (!started) { xmax = v; xidx = r; xsum = v; started = true; }
+					else { if (v > xmax) { xmax = v; xidx = r; } xsum += v; }
+				}
+			}
+		}
+	}
+	if (pool_thread) {
+		const unsigned g = g0 + pg, f = f0 + pf;
+		const unsigned cnt = a.R[2 * g + 1] - a.R[2 * g];     // integer row count (poolrgn.cuh:112,152)
+		const size_t o = (size_t)g * a.nf + f;
+		switch (a.ptype) {
+		case DB_PT_MAX: a.pooled[o] = xmax; if (a.argmax) a.argmax[o] = xidx * a.nf + f; break;
+		case DB_PT_AVG: a.pooled[o] = xsum / (float)cnt; break;
+		case DB_PT_SUM: a.pooled[o] = xsum; break;
+		default:
+			reinterpret_cast<float2*>(a.pooled)[o] = make_float2(xmax, xsum / (float)cnt);
+			if (a.argmax) a.argmax[o] = xidx * a.nf + f;
+			break;
+		}
+	}
+}
+
+// --------------------------------------------------------------- backward
+// dZ[i,f] = active(i,f) ? (mean share of region(i) + (i is argmax ? max delta : 0)) : 0
+// (poolrgn_bprop.cuh:45-127 then elemwise.py:78), dbias = column sums of dZ
+// (elemwise.py:176), dW[(4j+k),f] = sum_i dZ[i,f] * [X[i+j]==k]  (+1/4 to all four
+// channels for N; corr1ord_bprop.cuh:121-132).  Regions must be disjoint.
+// A CTA owns up to 8 regions x FB filters: per tile it rebuilds dZ in shared
+// memory, then a thread per (tap, filter) adds the tile's rows in order.
+// Per-CTA partials go to scratch and are added, CTA ascending, by a second
+// kernel: fixed order, no float atomics.
+struct bwd_args {
+	const uint8_t* X; const uint32_t* R; const float* dpooled; const uint32_t* argmax; const uint16_t* actmask;
+	float* partial;
+	unsigned m, nf, npos, n, nregion, G, FB;
+	int ptype;
+};
+
+__global__ void __launch_bounds__(512)
+scanpool_bwd_kernel(const bwd_args a)
+{
+	extern __shared__ __align__(16) unsigned char smem[];
+	const unsigned m = a.m, FB = a.FB;
+	float* dz = reinterpret_cast<float*>(smem);                         // [TR][FB]
+	float* davg = dz + (size_t)TR * FB;                                 // [GMAX][FB] mean share per row
+	float* dmax = davg + GMAX * FB;                                     // [GMAX][FB]
+	unsigned* amax = reinterpret_cast<unsigned*>(dmax + GMAX * FB);     // [GMAX][FB] argmax row
+	uint8_t* xs = reinterpret_cast<uint8_t*>(amax + GMAX * FB);         // TR + m codes (0..5)
+	__shared__ unsigned rg0[GMAX], rg1[GMAX];
+	__shared__ unsigned s_lo, s_hi;
+
+	const unsigned f0 = blockIdx.y * FB;
+	const unsigned g0 = blockIdx.x * a.G;
+	const unsigned ng = min(a.G, a.nregion - g0);
+	if (threadIdx.x == 0) {
+		unsigned lo = 0xffffffffu, hi = 0;
+		for (unsigned g = 0; g < ng; ++g) {
+			unsigned r0 = a.R[2 * (g0 + g)], r1 = a.R[2 * (g0 + g) + 1];
+			rg0[g] = r0; rg1[g] = r1;
+			if (r1 > r0) { lo = min(lo, r0); hi = max(hi, r1); }
+		}
+		s_lo = lo; s_hi = hi;
+	}
+	for (unsigned t = threadIdx.x; t < ng * FB; t += blockDim.x) {
+		unsigned g = t / FB, f = f0 + t % FB;
+		float va = 0.f, vm = 0.f; unsigned am = 0xffffffffu;
+		if (f < a.nf) {
+			size_t o = (size_t)(g0 + g) * a.nf + f;
+			unsigned cnt = a.R[2 * (g0 + g) + 1] - a.R[2 * (g0 + g)];
+			switch (a.ptype) {
+			case DB_PT_MAX: vm = a.dpooled[o]; am = a.argmax[o] / a.nf; break;
+			case DB_PT_AVG: va = a.dpooled[o] / (float)cnt; break;
+			case DB_PT_SUM: va = a.dpooled[o]; break;
+			default:        vm = a.dpooled[2*o]; va = a.dpooled[2*o+1] / (float)cnt; am = a.argmax[o] / a.nf; break;
+			}
+		}
+		davg[t] = va; dmax[t] = vm; amax[t] = am;
+	}
+	__syncthreads();
+
+	// accumulator identity: pair p = (tap j, filter f); pairs beyond m*FB idle.
+	// The extra FB threads after the pairs sum dbias.
+	const unsigned npair = m * FB;
+	float a0[2] = {0.f, 0.f}, a1[2] = {0.f, 0.f}, a2[2] = {0.f, 0.f}, a3[2] = {0.f, 0.f};
+	float bsum = 0.f;
+	const unsigned nwords = (a.nf + 15) / 16;
+
+	if (s_hi > s_lo)
+	for (unsigned t0 = s_lo; t0 < s_hi; t0 += TR) {
+		__syncthreads();
+		for (unsigned t = threadIdx.x; t < TR + m; t += blockDim.x) {
+			unsigned i = t0 + t, x = i < a.npos ? a.X[i] : 254u;
+			xs[t] = (uint8_t)(x < 4u ? x : (x == 254u ? 5u : 4u));
+		}
+		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
+			unsigned r = t / FB, fl = t % FB, row = t0 + r;
+			float v = 0.f;
+			if (row < s_hi && f0 + fl < a.nf) {
+				int g = -1;
+				for (unsigned k = 0; k < ng; ++k) if (row >= rg0[k] && row < rg1[k]) g = (int)k;
+				if (g >= 0) {
+					unsigned bits = a.actmask[(size_t)row * nwords + (f0 + fl) / 16];
+					if ((bits >> ((f0 + fl) & 15)) & 1u) {
+						v = davg[g * FB + fl];
+						if (amax[g * FB + fl] == row) v = v + dmax[g * FB + fl];
+					}
+				}
+			}
+			dz[t] = v;
+		}
+		__syncthreads();
+		#pragma unroll
+		for (int k = 0; k < 2; ++k) {
+			unsigned p = threadIdx.x + k * blockDim.x;
+			if (p < npair) {
+				unsigned j = p / FB, fl = p % FB;
+				float c0 = a0[k], c1 = a1[k], c2 = a2[k], c3 = a3[k];
+				// Rows at or past n have no scan output, hence no filter gradient.
+				unsigned rows = min((unsigned)TR, a.n > t0 ? a.n - t0 : 0u);
+				for (unsigned r = 0; r < rows; ++r) {
+					float v = dz[r * FB + fl];
+					unsigned c = xs[r + j];
+					if (c == 0) c0 += v; else if (c == 1) c1 += v; else if (c == 2) c2 += v; else if (c == 3) c3 += v;
+					else if (c == 4) { float q = v * 0.25f; c0 += q; c1 += q; c2 += q; c3 += q; }
+				}
+				a0[k] = c0; a1[k] = c1; a2[k] = c2; a3[k] = c3;
+			}
+		}
+		if (threadIdx.x < FB) {
+			float s = bsum;
+			for (unsigned r = 0; r < TR; ++r) s += dz[r * FB + threadIdx.x];
+			bsum = s;
+		}
+	}
+	// partial[cta][(4m+1)][nf]; row 4m is dbias
+	float* out = a.partial + (size_t)blockIdx.x * (4 * m + 1) * a.nf;
+	#pragma unroll
+	for (int k = 0; k < 2; ++k) {
+		unsigned p = threadIdx.x + k * blockDim.x;
+		if (p < npair) {
+			unsigned j = p / FB, f = f0 + p % FB;
+			if (f < a.nf) {
+				out[(size_t)(4*j+0)*a.nf + f] = a0[k]; out[(size_t)(4*j+1)*a.nf + f] = a1[k];
+				out[(size_t)(4*j+2)*a.nf + f] = a2[k]; out[(size_t)(4*j+3)*a.nf + f] = a3[k];
+			}
+		}
+	}
+	if (threadIdx.x < FB && f0 + threadIdx.x < a.nf)
+		out[(size_t)4 * m * a.nf + f0 + threadIdx.x] = bsum;
+}
+
+__global__ void scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const float* __restrict__ partial,
+                                    size_t wcount, unsigned nf, unsigned nparts)
+{
+	const size_t total = wcount + nf;
+	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+		float s = 0.f;
+		for (unsigned p = 0; p < nparts; ++p) s += partial[(size_t)p * total + i];
+		if (i < wcount) dW[i] = s; else if (dbias) dbias[i - wcount] = s;
+	}
+}
+
+static unsigned pick_fb(unsigned nf, unsigned m, size_t per_filter_bytes, size_t budget)
+{
+	unsigned FB = nf <= 16 ? 16 : (nf <= 32 ? 32 : 64);
+	while (FB > 16 && (size_t)m * FB * per_filter_bytes > budget) FB /= 2;
+	return FB;
+}
+
+static unsigned pick_group(unsigned nregion, unsigned nfb)
+{
+	unsigned G = GMAX;
+	while (G > 1 && (size_t)divup(nregion, G) * nfb < (size_t)2 * state().sm_count) G /= 2;
+	return G;
+}
+
+}  // namespace db
+
+using namespace db;
+
+DB_EXPORT void db_scanpool_fwd(const float* W, uint32_t m, uint32_t nf, const float* bias, int relu,
+                               const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion,
+                               int ptype, float* pooled, uint32_t* argmax, uint16_t* actmask)
+{
+	DB_API_TRY
+	DB_REQUIRE(ptype >= DB_PT_MAX && ptype <= DB_PT_ALL, "ValueError: unknown pooling type %d", ptype);
+	DB_REQUIRE(m > 0 && nf > 0, "ValueError: filter bank must not be empty (m=%u, nf=%u)", m, nf);
+	DB_REQUIRE(!argmax || ptype == DB_PT_MAX || ptype == DB_PT_ALL, "ValueError: pooledmaps_argmax can only be used for max/all pooling.");
+	if (nregion == 0) return;
+	DB_REQUIRE(W && X && regions && pooled, "ValueError: db_scanpool_fwd got a NULL pointer");
+	fwd_args a;
+	a.W = W; a.bias = bias; a.X = X; a.R = regions; a.pooled = pooled; a.argmax = argmax; a.actmask = actmask;
+	a.m = m; a.nf = nf; a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion;
+	a.relu = relu; a.ptype = ptype;
+	a.FB = pick_fb(nf, m, 32, 120 * 1024);
+	DB_REQUIRE((size_t)m * a.FB * 32 <= 160 * 1024, "ValueError: filter length %u is too long for the fused kernel", m);
+	unsigned nfb = divup(nf, a.FB);
+	a.G = pick_group(nregion, nfb);
+	size_t smem = (size_t)m * a.FB * 32 + (size_t)a.FB * (TR + 1) * 4 + TR + m + 16;
+	dim3 grid(divup(nregion, a.G), nfb), block(TR * a.FB / 16);
+	auto launch = [&](auto kern) {
+		DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+		kern<<<grid, block, smem, state().stream>>>(a);
+	};
+	if (m == 24) launch(scanpool_fwd_kernel<24>);
+	else if (m == 16) launch(scanpool_fwd_kernel<16>);
+	else launch(scanpool_fwd_kernel<0>);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
+                               const uint32_t* regions, uint32_t nregion, int ptype,
+                               const float* dpooled, const uint32_t* argmax, const uint16_t* actmask,
+                               float* dW, float* dbias)
+{
+	DB_API_TRY
+	DB_REQUIRE(ptype >= DB_PT_MAX && ptype <= DB_PT_ALL, "ValueError: unknown pooling type %d", ptype);
+	DB_REQUIRE(m > 0 && nf > 0, "ValueError: filter bank must not be empty (m=%u, nf=%u)", m, nf);
+	DB_REQUIRE(dW != nullptr, "ValueError: db_scanpool_bwd needs dW");
+	size_t wcount = (size_t)4 * m * nf;
+	if (nregion == 0) {
+		DB_CUDA(cudaMemsetAsync(dW, 0, wcount * 4, state().stream));
+		if (dbias) DB_CUDA(cudaMemsetAsync(dbias, 0, (size_t)nf * 4, state().stream));
+		return;
+	}
+	DB_REQUIRE(X && regions && dpooled && actmask, "ValueError: db_scanpool_bwd got a NULL pointer");
+	DB_REQUIRE(argmax || (ptype != DB_PT_MAX && ptype != DB_PT_ALL), "ValueError: pooledmaps_argmax must be specified for max pooling.");
+	bwd_args a;
+	a.X = X; a.R = regions; a.dpooled = dpooled; a.argmax = argmax; a.actmask = actmask;
+	a.m = m; a.nf = nf; a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.ptype = ptype;
+	a.FB = nf <= 16 ? 16 : 32;
+	unsigned nfb = divup(nf, a.FB);
+	a.G = pick_group(nregion, nfb);
+	unsigned threads = 256;
+	while (threads < 512 && 2 * threads < m * a.FB) threads *= 2;
+	DB_REQUIRE(m * a.FB <= 2 * threads, "ValueError: filter length %u is too long for the fused backward kernel", m);
+	unsigned ncta = divup(nregion, a.G);
+	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
+	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + TR + m + 16;
+	DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
+	DB_LAUNCH_CHECK();
+	scanpool_bwd_reduce<<<elemwise_grid(wcount + nf), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}

@@ -1,0 +1,56 @@
+"""Fused hot-path entry points (plain device pointers through the C ABI).
+
+``scanpool`` is the chain  corr1ord -> bias -> rectify -> poolrgn  of a
+DeepBind convolutional stage in one kernel; ``scanpool_bprop`` is its
+backward pass.  Tensors are CUDA ``torch.Tensor`` (memory only).
+"""
+import torch
+
+from . import _lib
+from .smat import bind_stream
+
+PT = {"max": 0, "avg": 1, "sum": 2, "all": 3}
+
+
+def _dll():
+    dll = _lib.load()
+    bind_stream()
+    return dll
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check(t, dtype, name):
+    if not (t.is_cuda and t.is_contiguous() and t.dtype == dtype):
+        raise TypeError("%s must be a contiguous CUDA tensor of %s" % (name, dtype))
+
+
+def scanpool(W, bias, X, R, ptype="max", relu=True, want_argmax=False, want_actmask=False):
+    """W [4m, nf] f32, bias [nf] f32 or None, X [npos] uint8, R [nregion, 2] int32
+    (uint32 bit pattern).  Returns (pooled, argmax, actmask): pooled f32
+    [nregion, nf] (or [nregion, 2nf] interleaved max, mean for "all"); argmax int32
+    (uint32 bit pattern) flat indices row*nf+f or None; actmask int16 words
+    [npos, ceil(nf/16)] or None."""
+    _check(W, torch.float32, "W"); _check(X, torch.uint8, "X"); _check(R, torch.int32, "R")
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    m, nf = W.shape[0] // 4, W.shape[1]
+    nregion, npos = R.shape[0], X.numel()
+    pooled = torch.empty((nregion, nf * (2 if ptype == "all" else 1)), dtype=torch.float32, device=W.device)
+    argmax = torch.empty((nregion, nf), dtype=torch.int32, device=W.device) if (want_argmax and ptype in ("max", "all")) else None
+    actmask = torch.empty((npos, (nf + 15) // 16), dtype=torch.int16, device=W.device) if want_actmask else None
+    _dll().db_scanpool_fwd(_ptr(W), m, nf, _ptr(bias), int(bool(relu)), _ptr(X), npos, _ptr(R), nregion,
+                           PT[ptype], _ptr(pooled), _ptr(argmax), _ptr(actmask))
+    return pooled, argmax, actmask
+
+
+def scanpool_bprop(m, nf, X, R, ptype, dpooled, argmax, actmask):
+    """Returns (dW [4m, nf], dbias [nf]) of the fused stage."""
+    _check(dpooled, torch.float32, "dpooled")
+    dW = torch.empty((4 * m, nf), dtype=torch.float32, device=dpooled.device)
+    db = torch.empty((nf,), dtype=torch.float32, device=dpooled.device)
+    _dll().db_scanpool_bwd(m, nf, _ptr(X), X.numel(), _ptr(R), R.shape[0], PT[ptype], _ptr(dpooled),
+                           _ptr(argmax), _ptr(actmask), _ptr(dW), _ptr(db))
+    return dW, db

@@ -1,0 +1,155 @@
+/*
+ * deepbind_b200 -- C ABI of libdeepbind_b200.so
+ *
+ * A from-scratch sm_100a implementation of DeepBind's data-parallel hot path
+ * (motif scan over ordinal DNA/RNA, rectify + region pooling, the small dense
+ * layers and the momentum update) behind the entry points the reference's
+ * ctypes layer binds.  Citations name files of the reference tree
+ * (jisraeli/DeepBind, paths relative to its root).
+ *
+ * Conventions kept from the reference (code/libs/smat/src/smat/smat.cpp:608-760,
+ * code/libs/smat/py/smat/smat_dll.py:85-92,166-183):
+ *   - every function is extern "C", returns void (or a plain value), never throws;
+ *   - failures leave a message that api_get_last_error() returns until
+ *     api_clear_last_error(); messages start with a Python exception name
+ *     ("ValueError: ...", "TypeError: ...", "AssertionError: CUDA error ...");
+ *   - arrays are 2-D, row-major; shape.x = columns, shape.y = rows;
+ *   - calls are asynchronous on one CUDA stream; api_sync() waits for it;
+ *   - accumulating operations (corr1ord's tail rows, corr1ord_bprop_W's dW,
+ *     corr1ord_bprop_X's dX, poolrgn_bprop's unpooled) add into memory the
+ *     caller has zeroed (code/libs/kangaroo/kangaroo/_ext/corr1ord.py:101,121,132;
+ *     poolrgn.py:79,123,177).
+ * There is no CPU fallback: without a CUDA device every compute call fails with
+ * an error message.
+ */
+#ifndef DEEPBIND_B200_H
+#define DEEPBIND_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes: code/libs/smat/src/smat/dtypes.h:67-80 */
+enum db_dtype { DB_B8 = 0, DB_I8 = 1, DB_U8 = 2, DB_I16 = 3, DB_U16 = 4, DB_I32 = 5,
+                DB_U32 = 6, DB_I64 = 7, DB_U64 = 8, DB_F32 = 9, DB_F64 = 10 };
+
+/* value-type codes: code/libs/smat/src/smat/vm/argument.h:48-55 */
+enum db_vtype { DB_VT_NONE = 0, DB_VT_HARRAY = 1, DB_VT_DARRAY = 2 };
+
+typedef struct db_shape  { int32_t x, y, z; } db_shape;   /* smat/shape.h:62-74 */
+typedef struct db_coord  { int32_t x, y, z; } db_coord;
+
+/* Array handle.  The first four members are the prefix Python mirrors
+ * (smat_dll.py:85-92); the rest is private to the library. */
+typedef struct smat {
+	int32_t  vtype;
+	int32_t  dtype;
+	db_shape shape;      /* x = columns, y = rows, z = 1 */
+	db_coord strides;    /* in elements: x = 1, y = row stride */
+	void*    data;       /* device address */
+	int32_t  owns_data;  /* 1: api_delete frees data; 0: borrowed (api_wrap) */
+	int32_t  device;
+} smat;
+
+/* option structs: kangaroo_smat.cpp:84-96, kangaroo_smat.h:38-47 */
+typedef struct corr1ord_options_t { int32_t padmode; uint32_t nchannel; } corr1ord_options_t;
+typedef struct poolrgn_options_t  { int32_t ptype; } poolrgn_options_t;
+enum db_pooltype { DB_PT_MAX = 0, DB_PT_AVG = 1, DB_PT_SUM = 2, DB_PT_ALL = 3 };
+
+/* ---- error channel, stream, handles (smat.cpp:612-613,622-660) ----------- */
+const char* api_get_last_error(void);
+void        api_clear_last_error(void);
+void        api_sync(void);                         /* cuda_context.cpp:198-202 */
+void        api_set_stream(void* cuda_stream);      /* no counterpart: lets the host share its stream */
+void*       api_get_stream(void);
+int         api_device_count(void);
+void        api_set_device(int device);             /* "device=" backend option, cuda_context.cpp:184-188 */
+smat*       api_empty(const db_shape* shape, int dtype);
+smat*       api_zeros(const db_shape* shape, int dtype);
+smat*       api_wrap(void* device_ptr, int rows, int cols, int dtype); /* borrowed memory; no counterpart */
+void        api_delete(const smat* M);
+int32_t     api_nrow(const smat* M);
+int32_t     api_ncol(const smat* M);
+size_t      api_size(const smat* M);
+int         api_dtype(const smat* M);
+void*       api_data(const smat* M);
+void        api_copy_from(smat* M, const void* host_src, int32_t row_stride_bytes, int32_t col_stride_bytes);
+void        api_copy_to(const smat* M, void* host_dst, int32_t row_stride_bytes, int32_t col_stride_bytes);
+void        api_fill_zero(smat* M);
+void        api_set_seed(uint64_t seed);            /* "seed=" backend option */
+void        register_ext(void);                     /* extension.cpp:159-169; nothing to register here */
+void        api_autotune(void);                     /* kangaroo_smat.cpp (autotune.cu:91-113): no-op */
+
+/* ---- kangaroo_smat (kangaroo_smat.cpp:333-418) ---------------------------- */
+void api_corr1ord(const smat* W, const smat* X, smat* Z, const corr1ord_options_t* options);
+void api_corr1ord_bprop_W(smat* dW, const smat* X, const smat* dZ, const corr1ord_options_t* options);
+void api_corr1ord_bprop_X(smat* dX, const smat* W, const smat* dZ, const corr1ord_options_t* options);
+void api_poolrgn(const smat* unpooledmaps, const smat* regions, smat* pooledmaps,
+                 smat* pooledmaps_argmax /* nullable */, const poolrgn_options_t* options);
+void api_poolrgn_bprop(smat* unpooledmaps, const smat* regions, const smat* pooledmaps,
+                       const smat* pooledmaps_argmax /* nullable */, const poolrgn_options_t* options);
+void api_dropoutord_fp_tr(const smat* X, smat* Z, smat* M, float rate);
+/* same, with the uniform draws supplied (f32, one per element): reproducible masks */
+void api_dropoutord_fp_tr_u(const smat* X, const smat* U, smat* Z, smat* M, float rate);
+
+/* ---- deepity_smat (deepity_smat.cpp:497-607) ------------------------------ */
+void api_gradstep(smat* P, const smat* dP, const smat* drate, smat* mP, const smat* mrate);
+void api_gradstep_nesterov1(smat* P, const smat* mP, const smat* mrate);
+void api_gradstep_nesterov2(smat* P, const smat* dP, const smat* drate, smat* mP, const smat* mrate);
+void api_madd_bcast(const smat* A, const smat* b, uint32_t k, smat* dst);
+void api_maskout(const smat* M, smat* A);
+void api_calc_zmask(const smat* Z, smat* M);
+void api_dropout_fp_tr(const smat* X, const smat* rate, smat* Z, smat* M, int matchrows);
+void api_dropout_fp_tr_u(const smat* X, const smat* rate, const smat* U, smat* Z, smat* M, int matchrows);
+void api_dropout_fp_te(const smat* X, const smat* rate, smat* Z);
+void api_dropout_bp_tr(const smat* dZ, const smat* M, smat* dX);
+void api_dropout_bp_te(const smat* dZ, const smat* rate, smat* dX);
+void api_blockwise_dot(int nblock, const smat* X, const smat* W, smat* Z);
+void api_blockwise_dot_nt(int nblock, const smat* dZ, const smat* W, smat* dX);
+void api_blockwise_dot_tn(int nblock, const smat* X, const smat* dZ, smat* dW);
+void api_blockwise_dot_combined(int nblock, int Xoffset, int Xbroadcast, const smat* X, const smat* W, smat* Z);
+void api_blockwise_dot_nt_combined(int nblock, int Xoffset, int Xbroadcast, smat* dX, const smat* W, const smat* dZ);
+void api_blockwise_dot_tn_combined(int nblock, int Xoffset, int Xbroadcast, const smat* X, smat* dW, const smat* dZ);
+
+/* ---- layer arithmetic the reference runs through generic smat ops ---------
+ * (code/libs/deepity/deepity/std/elemwise.py:71-82,162-180, softmax.py:50-77,
+ * loss.py:52-155; smat_cuda/elemwise3.cuh, elemwise2.cuh, reduce_y.cuh:52-126).
+ * Plain device pointers, f32, row-major. */
+void db_bias_add(float* Z, const float* X, const float* b, uint32_t nrow, uint32_t ncol);        /* Z = X + b   */
+void db_relu(float* Z, const float* X, size_t n);                                                /* max(0,X)    */
+void db_relu_bprop(float* dX, const float* dZ, const float* Z, size_t n);                        /* dZ*sign(Z)  */
+void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t ncol);                        /* sum(A,axis=0), fixed order */
+void db_logistic(float* Z, const float* X, size_t n);
+/* loss_node forward+backward (loss.py:52-112): kind 0 = mse, 1 = nll.  Z,Y [nrow,ncol];
+ * Ymask/Zmask nullable bool [nrow,ncol]; loss_out [ncol] = scaled column means;
+ * dZ (nullable) = maskout(Z-Y) / nrow. */
+void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, const uint8_t* Zmask,
+             uint32_t nrow, uint32_t ncol, float* loss_out, float* dZ);
+
+/* ---- fused hot path (no counterpart as one call; replaces the chain
+ * api_corr1ord -> bias -> rectify -> api_poolrgn of corr1ord.py:97-102,
+ * elemwise.py:171,74-78, poolrgn.py:59,153) --------------------------------
+ * W [4m, nf] f32, bias [nf] (nullable), X [npos] u8, regions u32 [nregion,2],
+ * pooled [nregion, nf] (max/avg/sum) or [nregion, 2nf] (all, interleaved),
+ * argmax u32 [nregion, nf] (nullable; flat index row*nf+f as api_poolrgn),
+ * actmask (nullable) u16 [npos, ceil(nf/16)]: bit f%16 of word f/16 of row i is
+ * set iff the rectified activation is > 0 (what the backward pass needs instead
+ * of Z).  Regions may lie anywhere in X; the backward pass needs them disjoint. */
+void db_scanpool_fwd(const float* W, uint32_t m, uint32_t nf, const float* bias, int relu,
+                     const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion,
+                     int ptype, float* pooled, uint32_t* argmax, uint16_t* actmask);
+/* Fused backward of the same chain: given dpooled (layout of pooled), argmax and
+ * actmask from the forward call, accumulates dW [4m,nf] and dbias [nf] (both
+ * overwritten, not accumulated) with a fixed summation order. */
+void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
+                     const uint32_t* regions, uint32_t nregion, int ptype,
+                     const float* dpooled, const uint32_t* argmax, const uint16_t* actmask,
+                     float* dW, float* dbias);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPBIND_B200_H */
