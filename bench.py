@@ -1,0 +1,264 @@
+#!/usr/bin/env python
+"""Benchmark of the DeepBind hot path on B200.
+
+Workload (``config.workload``): the many-model genome scan -- ``--nmodel``
+independent DeepBind models (16 motifs x 24 taps each, max+mean pooling, linear
+head) score ``--nseq`` 101-nt sequences per GPU into a [nseq, nmodel] matrix.
+Synthetic, seeded inputs in the reference's batch layout.  One "step" is one
+pass over the whole batch.  With several GPUs every rank scores its own
+sequences (weak scaling) and the score shards are all-gathered with NCCL.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference        # the CPU restatement, all host threads
+
+Prints ONE JSON line (rank 0).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, NMOTIF, L = 24, 16, 101
+UNIT = "sequences/s"
+METRIC = "sequences/sec scored"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--nseq", type=int, default=1000000, help="sequences per GPU")
+    ap.add_argument("--nmodel", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=16384)
+    ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def config(args, world):
+    return {"workload": "many-model genome scan: %d models x %d motifs x %d taps, %d-nt uniform ACGT, max+avg pooling, "
+                        "linear head, score matrix [nseq, %d]" % (args.nmodel, NMOTIF, M, L, args.nmodel),
+            "nseq_per_gpu": args.nseq, "global_nseq": args.nseq * world, "nmodel": args.nmodel,
+            "parallelism": "sequences sharded over %d GPU(s), NCCL all-gather of score shards" % world,
+            "l2": "working set per step (input + score matrix) exceeds the 126 MB L2; no explicit flush"}
+
+
+def adds_per_seq(nmodel):
+    return (L + M - 1) * NMOTIF * nmodel * M
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_run(args, nsample, steps, warmup):
+    """Times the CPU restatement of the path (the reference has no CPU code for it)
+    with every host thread, on a bounded sample of the same workload."""
+    from oracle import oracle as orc
+    from deepbind_b200 import synth
+    cores = len(os.sched_getaffinity(0))
+    orc.set_num_threads(cores)
+    params = synth.model_params(args.nmodel, M, 7, "all")
+    X, R = synth.uniform_batch(nsample, L, M, seed=11)
+    for _ in range(warmup):
+        orc.score_net(params, X[:R[min(63, nsample - 1), 1] + M - 1], R[:64], "all", args.nmodel)
+    times = []
+    for _ in range(steps):
+        t = time.perf_counter()
+        orc.score_net(params, X, R, "all", args.nmodel)
+        times.append(time.perf_counter() - t)
+    dt = sum(times)
+    return {"value": nsample * steps / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": "%d of the workload's sequences x %d models per step, %d step(s), OpenMP over sequences"
+                      % (nsample, args.nmodel, steps)}, dt / steps
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, sec = cpu_run(args, args.cpu_sample, max(1, args.steps), min(args.warmup, 1))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config(args, world), "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+            "note": "the reference has no CPU implementation of this path (CUDA-only); this arm times the CPU "
+                    "restatement used as the parity oracle"}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler(object):
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ GPU arm
+def main():
+    args = parse()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+    from deepbind_b200 import _lib, synth
+    from deepbind_b200.model import DeepBindNet
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dll = _lib.load()
+
+    I, nseq = args.nmodel, args.nseq
+    params = synth.model_params(I, M, 7, "all")
+    net = DeepBindNet(params, I, "all")
+    Xh, Rh = synth.uniform_batch(nseq, L, M, seed=1000 + rank)
+    X_host = torch.from_numpy(Xh).pin_memory()
+    R_host = torch.from_numpy(Rh.view(np.int32)).pin_memory()
+    out_host = torch.empty((nseq, I), dtype=torch.float32).pin_memory()
+    X = X_host.to(dev); R = R_host.to(dev)
+    scores = torch.empty((nseq, I), dtype=torch.float32, device=dev)
+    gathered = torch.empty((nseq * world, I), dtype=torch.float32, device=dev) if world > 1 else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        net.score_chunked(X, R, scores, args.chunk)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, scores)
+
+    def e2e_step():
+        net.predict_host(X_host, R_host, out_host, args.chunk, dev_bufs=(X, R, scores))
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, scores)
+
+    def timed(fn, nstep):
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(nstep):
+            fn()
+        ev1.record()
+        barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    l0 = dll.api_launch_count()
+    ms = timed(step, args.steps)
+    launches = int(dll.api_launch_count() - l0)
+    clocks = sampler.stop() if sampler else None
+    e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+
+    # dominant kernel alone: the fused scan+pool launches of one step, CUDA events on the launch stream
+    from deepbind_b200 import fused
+    Wd, bd = net.view("Wscan"), net.view("bscan").view(-1)
+    nchunk = (nseq + args.chunk - 1) // args.chunk
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ktime = 0.0
+    reps = min(args.steps, 2)
+    for _ in range(reps):
+        for s in range(0, nseq, args.chunk):
+            Rc = R[s:min(nseq, s + args.chunk)]
+            k0.record()
+            fused.scanpool(Wd, bd, X, Rc, "all", relu=True)
+            k1.record()
+            k1.synchronize()
+            ktime += k0.elapsed_time(k1)
+    kernel_ms_per_launch = ktime / (reps * nchunk)
+    adds_per_launch = adds_per_seq(I) * min(args.chunk, nseq)
+    peaks = {}
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peaks = json.load(open(pk))
+    prop = torch.cuda.get_device_properties(dev)
+    sm_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz") or 1965.0
+    # One 4-byte table operand per add comes back from shared memory at 128 B/clk/SM:
+    # 32 adds/clk/SM.  The FP32 add-issue ceiling (128 lanes/clk/SM) is 4x that.
+    lut_peak = prop.multi_processor_count * 32 * sm_max * 1e6
+    achieved = adds_per_launch / (kernel_ms_per_launch * 1e-3)
+    roofline = {"bound": "smem-lookup", "kernel": "scanpool_fwd_kernel<24> (FP32 lookup-add)",
+                "achieved": achieved / 1e12, "peak": lut_peak / 1e12, "unit": "Tadd/s", "frac": achieved / lut_peak,
+                "peak_source": "SMs x 32 table operands/clk x max SM clock (shared-memory return path); "
+                               "FP32 add issue would be 4x this", "traffic": None,
+                "ms_per_launch": kernel_ms_per_launch,
+                "hbm_gbs_algorithmic": (min(args.chunk, nseq) * ((L + M - 1) + I * 32 * 4)) / (kernel_ms_per_launch * 1e-3) / 1e9}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": nseq * world * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config(args, world), "clocks": clocks,
+                "e2e": {"value": nseq * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                        "h2d_bytes_per_step": int(X_host.numel() + R_host.numel() * 4),
+                        "d2h_bytes_per_step": int(out_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
+                "gpu_launches": launches, "roofline": roofline}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_run(args, args.cpu_sample, 1, 1)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -63,6 +63,7 @@ _PROTOTYPES = {
     "api_copy_to": (None, [c_smat_p, c_void_p, c_int32, c_int32]),
     "api_fill_zero": (None, [c_smat_p]),
     "api_set_seed": (None, [c_uint64]),
+    "api_launch_count": (c_uint64, []),
     "register_ext": (None, []),
     "api_autotune": (None, []),
     "api_corr1ord": (None, [c_smat_p, c_smat_p, c_smat_p, POINTER(c_corr1ord_options_t)]),
@@ -99,7 +100,7 @@ _PROTOTYPES = {
     "db_scanpool_bwd": (None, [c_uint32, c_uint32, P, c_uint32, P, c_uint32, c_int, P, P, P, P, P]),
 }
 
-_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream"}
+_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count"}
 
 
 class _SafeFunc(object):

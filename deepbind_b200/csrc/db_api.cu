@@ -127,6 +127,8 @@ DB_EXPORT void api_set_device(int device)
 	DB_API_CATCH
 }
 
+DB_EXPORT uint64_t api_launch_count(void) { return state().launches; }
+
 DB_EXPORT void api_set_seed(uint64_t seed)
 {
 	state().seed = seed;

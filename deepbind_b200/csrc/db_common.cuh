@@ -25,6 +25,7 @@ struct state_t {
 	uint64_t     rng_calls = 0;     // advances per random-mask call
 	void*        scratch = nullptr; // grow-only device scratch for two-stage reductions
 	size_t       scratch_bytes = 0;
+	uint64_t     launches = 0;      // kernels launched by this library on this thread
 };
 state_t& state();
 
@@ -47,7 +48,7 @@ inline void cuda_check(cudaError_t e, const char* what, const char* file, int li
 }  // namespace db
 
 #define DB_CUDA(call) ::db::cuda_check((call), #call, __FILE__, __LINE__)
-#define DB_LAUNCH_CHECK() ::db::cuda_check(cudaGetLastError(), "kernel launch", __FILE__, __LINE__)
+#define DB_LAUNCH_CHECK() do { ++::db::state().launches; ::db::cuda_check(cudaGetLastError(), "kernel launch", __FILE__, __LINE__); } while (0)
 #define DB_REQUIRE(cond, ...) do { if (!(cond)) throw ::db::error(::db::format(__VA_ARGS__)); } while (0)
 #define DB_ASSERT(cond) DB_REQUIRE(cond, "AssertionError: ASSERT FAILED: %s", #cond)
 

@@ -1,0 +1,187 @@
+"""DeepBind networks assembled from the hot-path operators.
+
+``DeepBindNet`` holds ``nmodel`` independent models (the reference's "instance"
+axis, code/libs/deepity/deepity/hypertrain.py:576) in one flat parameter vector
+``P`` with its gradient ``dP``, momentum ``mP`` and per-element rates, as
+``sgd._train_setup`` lays them out (code/libs/deepity/deepity/sgd.py:287-354),
+and runs
+
+    scan -> bias -> rectify -> pool -> [dropout] -> full -> bias
+         [-> rectify -> full -> bias] [-> logistic] -> loss
+
+forward, backward and the Nesterov update entirely through libdeepbind_b200.so.
+It is the composite the benchmark and parity tests drive; the node/plug graph
+engine of the reference is not reproduced here.
+"""
+import numpy as np
+import torch
+
+from . import _lib, fused
+from . import deepity_smat as dsm
+from .smat import sarray, bind_stream
+
+ORDER = ("Wscan", "bscan", "W1", "b1", "W2", "b2")
+
+
+def _as_f32(t):
+    return sarray(t, np.float32)
+
+
+class DeepBindNet(object):
+    def __init__(self, params, nmodel, pool="max", loss="nll", device=None):
+        self.dev = device or torch.device("cuda", torch.cuda.current_device())
+        self.I = int(nmodel)
+        self.pool = pool
+        self.loss = loss
+        self.m = params["Wscan"].shape[0] // 4
+        self.nf = params["Wscan"].shape[1]
+        self.hidden = params["W1"].shape[1] if "W2" in params else 0
+        self.names = [k for k in ORDER if k in params]
+        self.shapes = {k: tuple(np.atleast_1d(params[k]).shape) for k in self.names}
+        sizes = [int(np.prod(self.shapes[k])) for k in self.names]
+        self.offsets = np.concatenate([[0], np.cumsum(sizes)])
+        n = int(self.offsets[-1])
+        host = np.concatenate([np.asarray(params[k], np.float32).ravel() for k in self.names])
+        self.P = torch.from_numpy(host).to(self.dev)
+        self.dP = torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self.mP = torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self.drate = torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self.mrate = torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self._s = {k: _as_f32(getattr(self, k)) for k in ("P", "dP", "mP", "drate", "mrate")}
+
+    # ------------------------------------------------------------- parameters
+    def view(self, name, of="P"):
+        i = self.names.index(name)
+        t = getattr(self, of)[int(self.offsets[i]):int(self.offsets[i + 1])]
+        shp = self.shapes[name]
+        return t.view(shp) if len(shp) == 2 else t.view(1, -1)
+
+    def set_rates(self, rate, momentum):
+        """Per-model learning / momentum rates broadcast over each parameter block
+        with madd_bcast, as sgd.py:322-329 does (instance axis 0 for dense
+        weights, 1 elsewhere)."""
+        rate = np.broadcast_to(np.asarray(rate, np.float32), (self.I,)).copy()
+        momentum = np.broadcast_to(np.asarray(momentum, np.float32), (self.I,)).copy()
+        self.drate.zero_(); self.mrate.zero_()
+        for name in self.names:
+            shp = self.shapes[name]
+            inst_axis0 = name in ("W1", "W2")
+            k = int(np.prod(shp)) // self.I if inst_axis0 else (shp[-1] // self.I)
+            for vec, val in ((self.drate, rate), (self.mrate, momentum)):
+                i = self.names.index(name)
+                seg = vec[int(self.offsets[i]):int(self.offsets[i + 1])]
+                ones = torch.ones_like(seg)
+                dsm.madd_bcast(_as_f32(ones), val, k, _as_f32(seg))
+
+    # ---------------------------------------------------------------- forward
+    def _head(self, pooled):
+        """Dense layers on pooled features [B, npool*I] -> pre-activation output [B, I]."""
+        I = self.I
+        dll = _lib.load()
+        W1, b1 = self.view("W1"), self.view("b1")
+        h1 = dsm.blockwise_dot(_as_f32(pooled), _as_f32(W1), I).tensor
+        dll.db_bias_add(h1.data_ptr(), h1.data_ptr(), b1.data_ptr(), h1.shape[0], h1.shape[1])
+        if not self.hidden:
+            return h1, None, None
+        a1 = torch.empty_like(h1)
+        dll.db_relu(a1.data_ptr(), h1.data_ptr(), h1.numel())
+        W2, b2 = self.view("W2"), self.view("b2")
+        out = dsm.blockwise_dot(_as_f32(a1), _as_f32(W2), I).tensor
+        dll.db_bias_add(out.data_ptr(), out.data_ptr(), b2.data_ptr(), out.shape[0], out.shape[1])
+        return out, h1, a1
+
+    def score(self, X, R, strand_max=False):
+        """Scores [nseq, I] (no output non-linearity).  With strand_max, rows are
+        fwd/rc pairs and the larger score of each pair is kept, forward on ties
+        (code/libs/kangaroo/kangaroo/predict.py:145-164)."""
+        bind_stream()
+        pooled, _, _ = fused.scanpool(self.view("Wscan"), self.view("bscan").view(-1), X, R, self.pool, relu=True)
+        out, _, _ = self._head(pooled)
+        if strand_max:
+            out = out.view(-1, 2, self.I)
+            out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
+        return out
+
+    # --------------------------------------------------------------- backward
+    def grads(self, X, R, Y, dropmask=None):
+        """Fills dP with the gradient of the mean loss at P; returns loss [I].
+        Y is [B, I] f32; dropmask (optional, bool [B, npool*I]) is the dropout
+        keep-mask applied to the pooled features."""
+        bind_stream()
+        I = self.I
+        dll = _lib.load()
+        pooled, amax, actmask = fused.scanpool(self.view("Wscan"), self.view("bscan").view(-1), X, R, self.pool,
+                                               relu=True, want_argmax=True, want_actmask=True)
+        if dropmask is not None:
+            pd = pooled.clone()
+            dsm.maskout(sarray(dropmask, np.bool_), _as_f32(pd))
+        else:
+            pd = pooled
+        out, h1, a1 = self._head(pd)
+        B = out.shape[0]
+        lossv = torch.empty(I, dtype=torch.float32, device=self.dev)
+        dout = torch.empty_like(out)
+        if self.loss == "nll":
+            z = torch.empty_like(out)
+            dll.db_logistic(z.data_ptr(), out.data_ptr(), out.numel())
+            dll.db_loss(1, z.data_ptr(), Y.data_ptr(), None, None, B, I, lossv.data_ptr(), dout.data_ptr())
+        else:
+            dll.db_loss(0, out.data_ptr(), Y.data_ptr(), None, None, B, I, lossv.data_ptr(), dout.data_ptr())
+        if self.hidden:
+            W2 = self.view("W2")
+            dll.db_colsum(self.view("b2", "dP").data_ptr(), dout.data_ptr(), B, I)
+            dW2 = dsm.blockwise_dot_tn(_as_f32(a1), _as_f32(dout), I, _as_f32(W2)).tensor
+            self.view("W2", "dP").copy_(dW2)
+            da1 = dsm.blockwise_dot_nt(_as_f32(dout), _as_f32(W2), I).tensor
+            dh1 = torch.empty_like(da1)
+            dll.db_relu_bprop(dh1.data_ptr(), da1.data_ptr(), a1.data_ptr(), a1.numel())
+        else:
+            dh1 = dout
+        W1 = self.view("W1")
+        dll.db_colsum(self.view("b1", "dP").data_ptr(), dh1.data_ptr(), B, dh1.shape[1])
+        dW1 = dsm.blockwise_dot_tn(_as_f32(pd), _as_f32(dh1), I, _as_f32(W1)).tensor
+        self.view("W1", "dP").copy_(dW1)
+        dpd = dsm.blockwise_dot_nt(_as_f32(dh1), _as_f32(W1), I).tensor
+        if dropmask is not None:
+            dsm.maskout(sarray(dropmask, np.bool_), _as_f32(dpd))
+        dW, db = fused.scanpool_bprop(self.m, self.nf, X, R, self.pool, dpd, amax, actmask)
+        self.view("Wscan", "dP").copy_(dW)
+        self.view("bscan", "dP").view(-1).copy_(db)
+        return lossv
+
+    def train_step(self, X, R, Y, dropmask=None):
+        """One Nesterov step (deepity_smat.py:98-109): look-ahead, gradient, update."""
+        out = {}
+        dsm.gradstep(self._s["P"], self._s["dP"], self._s["drate"], self._s["mP"], self._s["mrate"],
+                     grad=lambda: out.setdefault("loss", self.grads(X, R, Y, dropmask)), nesterov=True)
+        return out["loss"]
+
+    def score_chunked(self, X, R, out, chunk=16384):
+        """Scores every region of a device-resident batch into ``out`` [nseq, I],
+        ``chunk`` sequences at a time so that the pooled features (npool*I floats
+        per sequence) never need more than one chunk of HBM."""
+        nseq = R.shape[0]
+        for s in range(0, nseq, chunk):
+            e = min(nseq, s + chunk)
+            out[s:e].copy_(self.score(X, R[s:e]))
+        return out
+
+    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None):
+        """The call a user makes for scoring: ordinal batch in (pinned) host
+        memory -> scores in (pinned) host memory.  Mirrors what
+        kangaroo.predict does per batch (code/libs/kangaroo/kangaroo/predict.py:168-176):
+        upload X and R, run the model, read the scores back."""
+        if dev_bufs is None:
+            dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.dev),
+                        torch.empty(R_host.shape, dtype=torch.int32, device=self.dev),
+                        torch.empty(out_host.shape, dtype=torch.float32, device=self.dev))
+        X, R, out = dev_bufs
+        X.copy_(X_host, non_blocking=True)
+        R.copy_(R_host, non_blocking=True)
+        self.score_chunked(X, R, out, chunk)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host
+
+    def params_numpy(self, of="P"):
+        return {k: self.view(k, of).detach().cpu().numpy().reshape(self.shapes[k]) for k in self.names}

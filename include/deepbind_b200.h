@@ -80,6 +80,7 @@ void        api_copy_from(smat* M, const void* host_src, int32_t row_stride_byte
 void        api_copy_to(const smat* M, void* host_dst, int32_t row_stride_bytes, int32_t col_stride_bytes);
 void        api_fill_zero(smat* M);
 void        api_set_seed(uint64_t seed);            /* "seed=" backend option */
+uint64_t    api_launch_count(void);                 /* kernels launched so far by this thread; no counterpart */
 void        register_ext(void);                     /* extension.cpp:159-169; nothing to register here */
 void        api_autotune(void);                     /* kangaroo_smat.cpp (autotune.cu:91-113): no-op */
 

@@ -1,0 +1,153 @@
+"""Parity of the fused scan+bias+rectify+pool kernels with the CPU oracle.
+
+Forward: pooled values (max, mean, sum) and argmax indices are compared bit for
+bit -- the kernel keeps the reference's tap order, row order and first-maximum
+rule.  Backward: sums whose order the reference leaves to atomicAdd are compared
+within 1e-5 of the magnitude of the summed terms."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+def to_dev(*arrs):
+    import torch
+    out = []
+    for a in arrs:
+        if a is None:
+            out.append(None)
+        elif a.dtype == np.uint32:
+            out.append(torch.from_numpy(a.view(np.int32)).cuda())
+        else:
+            out.append(torch.from_numpy(a).cuda())
+    return out
+
+
+def u32(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+CASES = [
+    # m, nf, nseq, lmin, lmax, n_frac
+    (24, 16, 64, 40, 40, 0.0),       # PBM-like
+    (24, 16, 128, 101, 101, 0.0),    # ChIP-like minibatch
+    (16, 16, 200, 20, 200, 0.05),    # ragged RNA with N
+    (24, 48, 33, 1, 60, 0.1),        # sequences shorter than the filter
+    (5, 7, 50, 1, 300, 0.2),         # generic filter length, nf not a multiple of 16
+    (24, 130, 40, 30, 130, 0.0),     # several filter blocks, ragged tail block
+    (11, 64, 9, 500, 900, 0.0),      # regions much longer than a tile
+]
+
+
+@pytest.mark.parametrize("ptype", ["max", "avg", "sum", "all"])
+@pytest.mark.parametrize("m,nf,nseq,lmin,lmax,n_frac", CASES)
+def test_forward_bit_exact(cuda, orc, ptype, m, nf, nseq, lmin, lmax, n_frac):
+    from deepbind_b200 import fused, synth
+    X, R = synth.ragged_batch(nseq, lmin, lmax, m, seed=m * 7 + nf, n_frac=n_frac)
+    rng = np.random.default_rng(nf)
+    X[rng.random(X.size) < 0.02] = 254
+    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(f32)
+    b = rng.uniform(-0.1, 0.0, nf).astype(f32)
+    P, A = orc.scanpool(W, b, True, X, R, ptype, True)
+    tW, tb, tX, tR = to_dev(W, b, X, R)
+    gP, gA, gM = fused.scanpool(tW, tb, tX, tR, ptype, relu=True, want_argmax=True, want_actmask=True)
+    assert np.array_equal(gP.cpu().numpy(), P)
+    if A is not None:
+        assert np.array_equal(u32(gA), A)
+    # activity mask against the unfused chain
+    Z = orc.corr1ord(W, X)
+    act = np.maximum(Z + b, 0) > 0
+    words = gM.cpu().numpy().view(np.uint16)
+    bits = ((words[:, :, None] >> np.arange(16)) & 1).reshape(X.size, -1)[:, :nf].astype(bool)
+    rows = np.zeros(X.size, bool)
+    for r0, r1 in R:
+        rows[r0:r1] = True
+    assert np.array_equal(bits[rows], act[rows])
+
+
+def test_forward_without_bias_or_rectifier(cuda, orc):
+    from deepbind_b200 import fused, synth
+    X, R = synth.ragged_batch(40, 5, 80, 8, seed=3)
+    W = (np.random.default_rng(0).standard_normal((32, 20))).astype(f32)
+    for bias, relu in ((None, False), (None, True)):
+        P, A = orc.scanpool(W, bias, relu, X, R, "all", True)
+        tW, tX, tR = to_dev(W, X, R)
+        gP, gA, _ = fused.scanpool(tW, None, tX, tR, "all", relu=relu, want_argmax=True)
+        assert np.array_equal(gP.cpu().numpy(), P) and np.array_equal(u32(gA), A)
+
+
+def test_forward_regions_in_any_layout(cuda, orc):
+    """Gaps, reversed order, overlaps and an empty region; rows past npos-m+1
+    read as the zeros the unfused path leaves there."""
+    from deepbind_b200 import fused
+    rng = np.random.default_rng(8)
+    m, nf, npos = 6, 16, 3000
+    X = rng.integers(0, 4, size=npos, dtype=np.uint8)
+    W = (rng.standard_normal((4 * m, nf)) * 0.2).astype(f32)
+    b = rng.uniform(-0.2, 0.1, nf).astype(f32)
+    R = np.array([[2900, 3000], [10, 50], [40, 45], [2000, 2001], [700, 1500], [60, 60], [0, 3], [2990, 2999],
+                  [100, 101], [1500, 1501]], np.uint32)
+    for ptype in ("max", "sum", "all"):
+        P, A = orc.scanpool(W, b, True, X, R, ptype, True)
+        tW, tb, tX, tR = to_dev(W, b, X, R)
+        gP, gA, _ = fused.scanpool(tW, tb, tX, tR, ptype, want_argmax=True)
+        assert np.array_equal(gP.cpu().numpy(), P, equal_nan=True)
+        if A is not None:
+            assert np.array_equal(u32(gA), A)
+
+
+def test_all_zero_maps_pick_first_row(cuda):
+    from deepbind_b200 import fused, synth
+    X, R = synth.uniform_batch(10, 30, 24, seed=1)
+    W = np.zeros((96, 16), f32); b = np.full(16, -1.0, f32)
+    tW, tb, tX, tR = to_dev(W, b, X, R)
+    gP, gA, _ = fused.scanpool(tW, tb, tX, tR, "max", want_argmax=True)
+    assert np.all(gP.cpu().numpy() == 0)
+    assert np.array_equal(u32(gA), R[:, :1] * 16 + np.arange(16, dtype=np.uint32))
+
+
+@pytest.mark.parametrize("ptype", ["max", "avg", "sum", "all"])
+@pytest.mark.parametrize("m,nf,nseq,lmin,lmax,n_frac", CASES[:6])
+def test_backward(cuda, orc, ptype, m, nf, nseq, lmin, lmax, n_frac):
+    from deepbind_b200 import fused, synth
+    X, R = synth.ragged_batch(nseq, lmin, lmax, m, seed=m + nf, n_frac=n_frac)
+    rng = np.random.default_rng(nf + 1)
+    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(f32)
+    b = rng.uniform(-0.1, 0.0, nf).astype(f32)
+    # oracle chain in float64 on the float32 forward values
+    Z = orc.corr1ord(W, X)
+    act = np.maximum(Z + b, 0)
+    P, A = orc.poolrgn(act, R, ptype, True)
+    dP = rng.standard_normal(P.shape).astype(f32)
+    dA = orc.poolrgn_bprop(np.zeros(act.shape, np.float64), R, dP.astype(np.float64), A, ptype)
+    dZ = dA * np.sign(act)
+    want_db = dZ.sum(axis=0)
+    want_dW = orc.corr1ord_bprop_W(np.zeros((4 * m, nf)), X, dZ)
+    tW, tb, tX, tR, tdP = to_dev(W, b, X, R, dP)
+    gP, gA, gM = fused.scanpool(tW, tb, tX, tR, ptype, want_argmax=True, want_actmask=True)
+    dW, db = fused.scanpool_bprop(m, nf, tX, tR, ptype, tdP, gA, gM)
+    scale = np.abs(dZ).sum(axis=0).max() + 1e-30
+    assert np.max(np.abs(dW.cpu().numpy() - want_dW)) <= 1e-5 * scale
+    assert np.max(np.abs(db.cpu().numpy() - want_db)) <= 1e-5 * scale
+    dW2, db2 = fused.scanpool_bprop(m, nf, tX, tR, ptype, tdP, gA, gM)
+    assert np.array_equal(dW2.cpu().numpy(), dW.cpu().numpy()) and np.array_equal(db2.cpu().numpy(), db.cpu().numpy())
+
+
+def test_fused_equals_unfused_device_chain(cuda):
+    """The fused kernel and the drop-in operator chain agree bit for bit on the device."""
+    import torch
+    from deepbind_b200 import fused, synth, smat as sm, kangaroo_smat as ks, _lib
+    X, R = synth.ragged_batch(300, 20, 200, 16, seed=12, n_frac=0.05)
+    rng = np.random.default_rng(0)
+    W = (rng.standard_normal((64, 16)) * 0.05).astype(f32); b = rng.uniform(-0.1, 0, 16).astype(f32)
+    sW, sX, sR = sm.asarray(W), sm.asarray(X), sm.asarray(R)
+    Z = sm.zeros((X.size, 16), f32)
+    ks.corr1ord(sW, sX, Z, 4)
+    tb = torch.from_numpy(b).cuda()
+    dll = _lib.load()
+    dll.db_bias_add(Z.data_ptr(), Z.data_ptr(), tb.data_ptr(), X.size, 16)
+    dll.db_relu(Z.data_ptr(), Z.data_ptr(), Z.size)
+    P, A = ks.poolrgn(Z, sR, "all", want_argmax=True)
+    gP, gA, _ = fused.scanpool(sW.tensor, tb, sX.tensor.view(-1), sR.tensor, "all", want_argmax=True)
+    assert torch.equal(gP, P.tensor) and torch.equal(gA, A.tensor)
