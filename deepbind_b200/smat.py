@@ -105,9 +105,10 @@ class sarray(object):
 def asarray(a, dtype=None):
     if isinstance(a, sarray):
         return a if dtype is None or np.dtype(dtype) == a.dtype else asarray(a.asnumpy(), dtype)
+    from_numpy = isinstance(a, np.ndarray)
     a = np.asarray(a, dtype=dtype)
-    if a.dtype == np.float64 and dtype is None:
-        a = a.astype(_default_dtype)
+    if a.dtype == np.float64 and dtype is None and not from_numpy:
+        a = a.astype(_default_dtype)      # Python lists and scalars take the default dtype
     dt = a.dtype
     if a.ndim == 1:
         a = a.reshape(-1, 1)
