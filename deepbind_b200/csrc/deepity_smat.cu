@@ -167,32 +167,33 @@ blockwise_nt_kernel(T* __restrict__ dX, const T* __restrict__ W, const T* __rest
 	}
 }
 
-// One CTA per block b.  The n rows are cut into 8 interleaved slices summed by
-// 8 thread groups, then the 8 partials are added in slice order.
+// One CTA per block b.  The n rows are cut into blockDim/32 interleaved slices,
+// each summed by one warp, then the partials are added in slice order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 blockwise_tn_kernel(const T* __restrict__ X, T* __restrict__ dW, const T* __restrict__ dZ,
                     int n, int m, int k, int p, int xoff, int xbroadcast, int nblock)
 {
 	extern __shared__ __align__(16) unsigned char smem_raw[];
-	T* part = reinterpret_cast<T*>(smem_raw);       // [8][k*m]
+	T* part = reinterpret_cast<T*>(smem_raw);       // [nslice][k*m]
+	const int nslice = blockDim.x / 32;
 	const int b = blockIdx.x;
 	const int ldx = k * (xbroadcast ? 1 : nblock), ldz = m * nblock;
 	const T* Xb = X + (xbroadcast ? 0 : (size_t)b * k);
 	const T* Zb = dZ + (size_t)b * m;
 	T* Wb = dW + ((size_t)b * p + xoff) * m;
 	const int km = k * m;
-	const int slice = threadIdx.x / 32, lane = threadIdx.x % 32;   // 8 slices of 32 threads
+	const int slice = threadIdx.x / 32, lane = threadIdx.x % 32;
 	for (int o = lane; o < km; o += 32) {
 		int u = o / m, c = o % m;
 		T s = 0;
-		for (int i = slice; i < n; i += 8) s = fma(Xb[(size_t)i * ldx + u], Zb[(size_t)i * ldz + c], s);
+		for (int i = slice; i < n; i += nslice) s = fma(Xb[(size_t)i * ldx + u], Zb[(size_t)i * ldz + c], s);
 		part[slice * km + o] = s;
 	}
 	__syncthreads();
 	for (int o = threadIdx.x; o < km; o += blockDim.x) {
 		T s = part[o];
-		for (int sl = 1; sl < 8; ++sl) s += part[sl * km + o];
+		for (int sl = 1; sl < nslice; ++sl) s += part[sl * km + o];
 		Wb[o] = s;
 	}
 }
@@ -218,10 +219,12 @@ static void launch_blockwise(int mode, int dtype, int nblock, int xoff, bool xbr
 		if (dtype == DB_F32) blockwise_nt_kernel<float><<<grid, 256, smem, st>>>((float*)X, (const float*)W, (const float*)Z, n, m, k, p, xoff, nblock);
 		else                 blockwise_nt_kernel<double><<<grid, 256, smem, st>>>((double*)X, (const double*)W, (const double*)Z, n, m, k, p, xoff, nblock);
 	} else {
-		size_t smem = (size_t)8 * k * m * es;
+		int nslice = 8;
+		while (nslice > 1 && (size_t)nslice * k * m * es > 48 * 1024) nslice /= 2;
+		size_t smem = (size_t)nslice * k * m * es;
 		DB_REQUIRE(smem <= 48 * 1024, "ValueError: blockwise_dot_tn block of %d x %d exceeds the shared-memory tile", k, m);
-		if (dtype == DB_F32) blockwise_tn_kernel<float><<<nblock, 256, smem, st>>>((const float*)X, (float*)W, (const float*)Z, n, m, k, p, xoff, xbroadcast, nblock);
-		else                 blockwise_tn_kernel<double><<<nblock, 256, smem, st>>>((const double*)X, (double*)W, (const double*)Z, n, m, k, p, xoff, xbroadcast, nblock);
+		if (dtype == DB_F32) blockwise_tn_kernel<float><<<nblock, 32 * nslice, smem, st>>>((const float*)X, (float*)W, (const float*)Z, n, m, k, p, xoff, xbroadcast, nblock);
+		else                 blockwise_tn_kernel<double><<<nblock, 32 * nslice, smem, st>>>((const double*)X, (double*)W, (const double*)Z, n, m, k, p, xoff, xbroadcast, nblock);
 	}
 	DB_LAUNCH_CHECK();
 }
