@@ -98,6 +98,10 @@ _PROTOTYPES = {
     "db_loss": (None, [c_int, P, P, P, P, c_uint32, c_uint32, P, P]),
     "db_scanpool_fwd": (None, [P, c_uint32, c_uint32, P, c_int, P, c_uint32, P, c_uint32, c_int, P, P, P]),
     "db_scanpool_bwd": (None, [c_uint32, c_uint32, P, c_uint32, P, c_uint32, c_int, P, P, P, P, P]),
+    "db_tc_weights_bytes": (c_size_t, [c_uint32, c_uint32, c_int]),
+    "db_tc_prepare": (None, [P, c_uint32, c_uint32, c_int, P]),
+    "db_scanpool_tc": (None, [P, c_uint32, c_uint32, c_int, P, c_int, P, c_uint32, P, c_uint32, c_int,
+                              P, P, P, c_uint32, P, P]),
 }
 
 _NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count"}

@@ -54,3 +54,41 @@ def scanpool_bprop(m, nf, X, R, ptype, dpooled, argmax, actmask):
     _dll().db_scanpool_bwd(m, nf, _ptr(X), X.numel(), _ptr(R), R.shape[0], PT[ptype], _ptr(dpooled),
                            _ptr(argmax), _ptr(actmask), _ptr(dW), _ptr(db))
     return dW, db
+
+
+class TCWeights(object):
+    """Filter bank prepared for the tensor-core scan: bf16 operand tiles with
+    ``nsplit`` pieces per weight (1: bf16, 2: ~16 significant bits, 3: ~24 bits)."""
+
+    def __init__(self, W, bias=None, nsplit=3):
+        _check(W, torch.float32, "W")
+        self.m, self.nf, self.nsplit = W.shape[0] // 4, W.shape[1], int(nsplit)
+        self.bias = bias
+        dll = _dll()
+        nbytes = dll.db_tc_weights_bytes(self.m, self.nf, self.nsplit)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
+        dll.db_tc_prepare(_ptr(W), self.m, self.nf, self.nsplit, _ptr(self.buf))
+
+
+def scanpool_tc(tcw, X, R, ptype="all", relu=True, headW=None, headB=None, want_pooled=None, check=True):
+    """Tensor-core scan + bias + rectify + pooling of a prepared filter bank.
+
+    Returns (pooled, scores): pooled as :func:`scanpool` (or None), scores
+    [nregion, nmodel] when a linear head (headW [(16|32)*nmodel], headB [nmodel])
+    is given.  ``check`` reads the kernel's status word back (one sync)."""
+    _check(X, torch.uint8, "X"); _check(R, torch.int32, "R")
+    nregion, npos, nf = R.shape[0], X.numel(), tcw.nf
+    if want_pooled is None:
+        want_pooled = headW is None
+    pooled = torch.empty((nregion, nf * (2 if ptype == "all" else 1)), dtype=torch.float32, device=X.device) if want_pooled else None
+    nmodel = nf // 16 if headW is not None else 0
+    scores = torch.empty((nregion, nmodel), dtype=torch.float32, device=X.device) if headW is not None else None
+    status = torch.zeros(1, dtype=torch.int32, device=X.device)
+    _dll().db_scanpool_tc(_ptr(tcw.buf), tcw.m, nf, tcw.nsplit, _ptr(tcw.bias), int(bool(relu)), _ptr(X), npos, _ptr(R),
+                          nregion, PT[ptype], _ptr(pooled), _ptr(headW), _ptr(headB), nmodel, _ptr(scores), _ptr(status))
+    if check:
+        code = int(status.item())
+        if code:
+            raise _lib.SmatException("scanpool_tc(...) raised an exception\nRuntimeError: tensor-core scan failed: %s" %
+                                     {1: "a device-side wait timed out", 2: "a region is longer than the kernel supports"}.get(code, code))
+    return pooled, scores

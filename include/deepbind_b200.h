@@ -150,6 +150,26 @@ void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
                      const float* dpooled, const uint32_t* argmax, const uint16_t* actmask,
                      float* dW, float* dbias);
 
+/* ---- many-model scan on tcgen05 tensor cores (no counterpart: replaces `nf/16`
+ * passes of kangaroo.predict over the same sequences, predict.py:394-420, and
+ * deepity's instance batching, hypertrain.py:576) ---------------------------
+ * The scan is the dense contraction Z[f,p] = sum_k W[k,f] * onehot(X)[p,k], K = 4m.
+ * Weights are prepared once per weight set into bf16 operand tiles; nsplit = 1, 2
+ * or 3 bf16 pieces per weight give 8, 16 or 24 significant bits (max relative
+ * error about 2e-3, 1e-5, 1e-6 of the largest activation).  Pooled values follow
+ * db_scanpool_fwd's layout; argmax is not produced (use the FP32 path to train).
+ * If `scores` is given, each model's linear head (16 filters per model; headW
+ * [(16|32)*nmodel] in the row order of full.W, headB [nmodel]) is applied in the
+ * kernel and scores [nregion, nmodel] is written; `pooled` may then be NULL.
+ * Regions must be at most 2100 rows long.  status: device int, 0 = ok,
+ * 1 = a wait timed out, 2 = a region is too long. */
+size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int nsplit);
+void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int nsplit, void* prepared);
+void db_scanpool_tc(const void* prepared, uint32_t m, uint32_t nf, int nsplit, const float* bias, int relu,
+                    const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion, int ptype,
+                    float* pooled, const float* headW, const float* headB, uint32_t nmodel, float* scores,
+                    int* status);
+
 #ifdef __cplusplus
 }
 #endif

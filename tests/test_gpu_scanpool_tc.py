@@ -1,0 +1,104 @@
+"""Parity of the tensor-core (tcgen05) many-model scan with the CPU oracle.
+
+The one-hot operand is exact in bf16; the weights carry 8, 16 or 24 significant
+bits (nsplit 1, 2, 3), so the tolerance is stated relative to the largest
+activation: 2e-3 for one bf16 piece (the bound BASELINE sets for bf16/TF32
+paths), 1e-5 for two and three pieces (the fp32 bound)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+TOL = {1: 2e-3, 2: 1e-5, 3: 1e-5}
+
+
+def dev(a):
+    import torch
+    if a is None:
+        return None
+    return torch.from_numpy(np.ascontiguousarray(a.view(np.int32) if a.dtype == np.uint32 else a)).cuda()
+
+
+CASES = [
+    # m, nmodel, nseq, lmin, lmax, n_frac
+    (24, 8, 64, 101, 101, 0.0),      # one filter tile, ChIP-like
+    (24, 20, 50, 40, 40, 0.0),       # three tiles, the last one half empty
+    (16, 8, 80, 20, 200, 0.05),      # ragged RNA with N: tiles of 36..215 positions
+    (24, 9, 30, 200, 400, 0.0),      # regions spanning several 128-column tiles
+    (10, 8, 40, 5, 60, 0.1),         # filter length not a multiple of 4 (zero-padded taps)
+]
+
+
+@pytest.mark.parametrize("nsplit", [1, 2, 3])
+@pytest.mark.parametrize("ptype", ["max", "avg", "sum", "all"])
+@pytest.mark.parametrize("m,nmodel,nseq,lmin,lmax,n_frac", CASES)
+def test_pooled_matches_oracle(cuda, orc, nsplit, ptype, m, nmodel, nseq, lmin, lmax, n_frac):
+    from deepbind_b200 import fused, synth
+    nf = 16 * nmodel
+    X, R = synth.ragged_batch(nseq, lmin, lmax, m, seed=m + nmodel, n_frac=n_frac)
+    rng = np.random.default_rng(nmodel)
+    X[rng.random(X.size) < 0.01] = 254
+    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(f32)
+    b = rng.uniform(-0.1, 0.0, nf).astype(f32)
+    want, _ = orc.scanpool(W.astype(np.float64), b.astype(np.float64), True, X, R, ptype)
+    tcw = fused.TCWeights(dev(W), dev(b), nsplit)
+    got, _ = fused.scanpool_tc(tcw, dev(X), dev(R), ptype)
+    got = got.cpu().numpy()
+    assert got.shape == want.shape
+    scale = np.abs(want).max()
+    assert np.max(np.abs(got - want)) <= TOL[nsplit] * scale, (np.max(np.abs(got - want)), scale)
+
+
+@pytest.mark.parametrize("nsplit", [1, 3])
+@pytest.mark.parametrize("ptype", ["max", "all"])
+def test_fused_linear_head_scores(cuda, orc, nsplit, ptype):
+    from deepbind_b200 import fused, synth
+    m, I = 24, 24
+    X, R = synth.uniform_batch(300, 101, m, seed=3)
+    p = synth.model_params(I, m, 4, ptype)
+    p64 = {k: v.astype(np.float64) for k, v in p.items()}
+    want = orc.score_net(p64, X, R, ptype, I)
+    tcw = fused.TCWeights(dev(p["Wscan"]), dev(p["bscan"]), nsplit)
+    pooled, scores = fused.scanpool_tc(tcw, dev(X), dev(R), ptype, headW=dev(p["W1"].ravel()), headB=dev(p["b1"]),
+                                       want_pooled=True)
+    scale = np.abs(want).max()
+    assert np.max(np.abs(scores.cpu().numpy() - want)) <= TOL[nsplit] * scale
+    wp, _ = orc.scanpool(p64["Wscan"], p64["bscan"], True, X, R, ptype)
+    assert np.max(np.abs(pooled.cpu().numpy() - wp)) <= TOL[nsplit] * np.abs(wp).max()
+
+
+def test_three_pieces_agree_with_fp32_kernel(cuda):
+    """bf16x3 against the bit-exact FP32 lookup-add kernel on the device."""
+    import torch
+    from deepbind_b200 import fused, synth
+    m, I = 24, 40
+    X, R = synth.uniform_batch(2000, 101, m, seed=9)
+    p = synth.model_params(I, m, 10, "all")
+    W, b, dX, dR = dev(p["Wscan"]), dev(p["bscan"]), dev(X), dev(R)
+    ref, _, _ = fused.scanpool(W, b, dX, dR, "all")
+    got, _ = fused.scanpool_tc(fused.TCWeights(W, b, 3), dX, dR, "all")
+    assert float((got - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+
+
+def test_regions_in_any_order_and_tail_rows(cuda, orc):
+    from deepbind_b200 import fused
+    rng = np.random.default_rng(8)
+    m, nf, npos = 8, 128, 3000
+    X = rng.integers(0, 4, size=npos, dtype=np.uint8)
+    W = (rng.standard_normal((4 * m, nf)) * 0.2).astype(f32)
+    b = rng.uniform(-0.2, 0.1, nf).astype(f32)
+    R = np.array([[2900, 3000], [10, 50], [40, 45], [2000, 2001], [700, 1500], [0, 3], [2990, 2999], [1500, 1501]], np.uint32)
+    want, _ = orc.scanpool(W.astype(np.float64), b.astype(np.float64), True, X, R, "all")
+    got, _ = fused.scanpool_tc(fused.TCWeights(dev(W), dev(b), 3), dev(X), dev(R), "all")
+    assert np.max(np.abs(got.cpu().numpy() - want)) <= 1e-5 * np.abs(want).max()
+
+
+def test_region_too_long_is_reported(cuda):
+    from deepbind_b200 import fused, SmatException
+    X = np.zeros(5000, np.uint8); R = np.array([[0, 4000]], np.uint32)
+    W = np.zeros((96, 16), f32)
+    with pytest.raises(SmatException, match="longer than the kernel supports"):
+        fused.scanpool_tc(fused.TCWeights(dev(W), None, 1), dev(X), dev(R), "max")
+    # the device is still usable
+    got, _ = fused.scanpool_tc(fused.TCWeights(dev(W), None, 1), dev(X), dev(np.array([[0, 100]], np.uint32)), "max")
+    assert float(got.abs().max()) == 0.0
