@@ -12,19 +12,22 @@
 // Layout of one CTA (256 threads, 1 CTA per SM):
 //   M = 128 filters of one filter tile (A operand: prepared bf16 weights, K-major,
 //       resident in shared memory for the CTA's lifetime, loaded by one bulk copy);
-//   N = up to 128 positions of one sequence (B operand);
-//   D = FP32 accumulator in tensor memory, 4 slots of 128 columns.
-// The B operand is never expanded: the im2col matrix of a sequence is Toeplitz
-// (row p, chunk kc of 8 K-values = bases p+2kc, p+2kc+1), so a flat array E of
-// 16-byte chunks, E[q] = one-hot pair of bases (q, q+1), IS the K-major operand
-// when the shared-memory descriptor uses an 8-row group stride of 128 bytes and a
-// K-chunk stride of 32 bytes: row p, chunk kc lives at E + 16*(p + 2*kc).
-// Warp roles: warp 0 issues tcgen05.mma; warps 1-3 encode E for the next block of
-// sequences (double buffered); warps 4-7 drain the accumulators: each thread owns
-// one filter (one TMEM lane) and reduces its row over the positions in registers
-// (bias, rectify, max / mean), then either stores the pooled features or folds
-// them through each model's linear head (16 lanes = one model, warp shuffles).
-// Per-position activations never leave the SM.
+//   N = 256 consecutive rows of the ordinal buffer (B operand), whatever sequences
+//       they belong to: the regions of a batch abut, so tiling the flat rows wastes
+//       nothing on padding and keeps the MMA at its widest N;
+//   D = FP32 accumulator in tensor memory, 2 slots of 256 columns.
+// The B operand is never expanded: the im2col matrix is Toeplitz (row p, chunk kc
+// of 8 K-values = bases p+2kc, p+2kc+1), so a flat array E of 16-byte chunks,
+// E[q] = one-hot pair of bases (q, q+1), IS the K-major operand when the
+// shared-memory descriptor uses an 8-row group stride of 128 bytes and a K-chunk
+// stride of 32 bytes: row p, chunk kc lives at E + 16*(p + 2*kc).
+// Warp roles: warp 0 issues tcgen05.mma; warps 1-3 encode E for the next stage of
+// 8 tiles (double buffered); warps 4-7 drain the accumulators: each thread owns one
+// filter (one TMEM lane), walks the tile's columns in step with the region table
+// and reduces its row in registers (bias, rectify, max / mean); when a region ends
+// it either stores the pooled features or folds them through the model's linear
+// head (16 lanes = one model, warp shuffles).  Per-position activations never
+// leave the SM.  Regions must ascend without overlap (the batch layout).
 //
 // Every wait on an mbarrier is bounded by a clock deadline; on expiry the CTA sets
 // a status word, releases its tensor memory and returns.
@@ -33,10 +36,8 @@
 
 namespace db {
 
-static constexpr int TC_NSLOT = 4;          // accumulator slots of 128 TMEM columns
-static constexpr int TC_ECAP = 2304;        // 16-byte chunks per E stage (36 KB)
-static constexpr int TC_BLKMAX = 64;        // regions per staged block
-static constexpr int TC_SLACK = 160;        // chunks past the last row a tile may touch (N padding + K reach)
+static constexpr int TC_STAGE_TILES = 8;    // tiles of 256 flat rows per E stage
+static constexpr int TC_ECHUNKS = TC_STAGE_TILES * 256 + 128;   // 16-byte chunks per stage incl. the K reach of the last row
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // clock cycles (about 0.1 s)
 
 struct tc_args {
@@ -78,6 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
 		if (mbar_try_wait(bar, parity)) return true;
 		if (*abort_flag) return false;
 		if (clock64() - t0 > TC_TIMEOUT) { *abort_flag = 1; return false; }
+		__nanosleep(40);        // a spinning warp would take issue slots from the epilogue warp of its scheduler
 	}
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar)
@@ -144,20 +146,206 @@ __device__ __forceinline__ unsigned long long base_pattern(unsigned x)
 	return 0x3E803E803E803E80ull;                      // bf16(0.25) in every channel
 }
 
-__device__ __forceinline__ unsigned region_rows(const uint32_t* R, unsigned g) { unsigned a = R[2*g], b = R[2*g+1]; return b > a ? b - a : 0u; }
 
-__global__ void __launch_bounds__(256, 1)
+#define COMMA ,
+// Narrow TMEM loads for the tail of a region segment (32 lanes x N columns, one
+// register per column).
+#define DB_TMEM_LD_SMALL(NAME, N, REGS_OUT, REGS_FMT)                                              \
+__device__ __forceinline__ void NAME(uint32_t taddr, float (&v)[N])                                \
+{                                                                                                  \
+	uint32_t* r = reinterpret_cast<uint32_t*>(v);                                                  \
+	asm volatile("tcgen05.ld.sync.aligned.32x32b.x" #N ".b32 {" REGS_FMT "}, [%" #N "];"            \
+	             : REGS_OUT : "r"(taddr) : "memory");                                              \
+}
+DB_TMEM_LD_SMALL(tmem_ld16, 16,
+	"=r"(r[0]) COMMA "=r"(r[1]) COMMA "=r"(r[2]) COMMA "=r"(r[3]) COMMA "=r"(r[4]) COMMA "=r"(r[5]) COMMA "=r"(r[6]) COMMA "=r"(r[7]) COMMA
+	"=r"(r[8]) COMMA "=r"(r[9]) COMMA "=r"(r[10]) COMMA "=r"(r[11]) COMMA "=r"(r[12]) COMMA "=r"(r[13]) COMMA "=r"(r[14]) COMMA "=r"(r[15]),
+	"%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15")
+DB_TMEM_LD_SMALL(tmem_ld8, 8,
+	"=r"(r[0]) COMMA "=r"(r[1]) COMMA "=r"(r[2]) COMMA "=r"(r[3]) COMMA "=r"(r[4]) COMMA "=r"(r[5]) COMMA "=r"(r[6]) COMMA "=r"(r[7]),
+	"%0, %1, %2, %3, %4, %5, %6, %7")
+DB_TMEM_LD_SMALL(tmem_ld4, 4, "=r"(r[0]) COMMA "=r"(r[1]) COMMA "=r"(r[2]) COMMA "=r"(r[3]), "%0, %1, %2, %3")
+DB_TMEM_LD_SMALL(tmem_ld2, 2, "=r"(r[0]) COMMA "=r"(r[1]), "%0, %1")
+DB_TMEM_LD_SMALL(tmem_ld1, 1, "=r"(r[0]), "%0")
+
+// Running pooling state of one filter over the rows of one region.  Four
+// independent chains keep a lone warp issuing; there are no per-column tests:
+// the columns of a region are fetched from tensor memory starting at the
+// region's own first column, in pieces of 64/32/16/8/4/2/1.
+struct pool_state {
+	float mx[4], sm[4];
+	__device__ __forceinline__ void reset()
+	{
+		#pragma unroll
+		for (int j = 0; j < 4; ++j) { mx[j] = -INFINITY; sm[j] = 0.f; }
+	}
+	template <bool WANT_MAX, bool WANT_SUM, bool RELU, int N>
+	__device__ __forceinline__ void add(const float (&v)[N], float nb)
+	{
+		if (N >= 8) {
+			#pragma unroll
+			for (int i = 0; i < N; i += 8) {
+				#pragma unroll
+				for (int j = 0; j < 4; ++j) {
+					const float x0 = v[i + 2 * j], x1 = v[i + 2 * j + 1];
+					if (WANT_MAX) mx[j] = fmaxf(mx[j], fmaxf(x0, x1));
+					if (WANT_SUM) sm[j] += (RELU ? fmaxf(x0, nb) : x0) + (RELU ? fmaxf(x1, nb) : x1);
+				}
+			}
+		} else {
+			#pragma unroll
+			for (int i = 0; i < N; ++i) {
+				if (WANT_MAX) mx[i & 3] = fmaxf(mx[i & 3], v[i]);
+				if (WANT_SUM) sm[i & 3] += RELU ? fmaxf(v[i], nb) : v[i];
+			}
+		}
+	}
+	// `cnt` rows whose scan output is zero
+	template <bool WANT_MAX, bool WANT_SUM, bool RELU>
+	__device__ __forceinline__ void add_zero_rows(unsigned cnt, float nb)
+	{
+		if (WANT_MAX) mx[0] = fmaxf(mx[0], 0.f);
+		if (WANT_SUM) sm[0] += (float)cnt * (RELU ? fmaxf(0.f, nb) : 0.f);
+	}
+	__device__ __forceinline__ float max_all() const { return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])); }
+	__device__ __forceinline__ float sum_all() const { return (sm[0] + sm[1]) + (sm[2] + sm[3]); }
+};
+
+template <bool WANT_MAX, bool WANT_SUM, bool RELU>
+__device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base, uint64_t* t_full, uint64_t* t_empty,
+                                            volatile int* abort_flag, unsigned tile, unsigned g_first, unsigned g_last,
+                                            unsigned row_lo, unsigned row_hi, unsigned warp, unsigned lane)
+{
+	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
+	const unsigned set = (warp - 4) >> 2;               // two warps share a quarter: one owns the even regions, one the odd
+	const unsigned f = tile * 128 + q4 * 32 + lane;     // this thread's filter = its TMEM lane
+	const float b = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
+	const float nb = -b;
+	// linear head of the model this filter belongs to (16 filters per model)
+	float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
+	const unsigned model = f / 16;
+	if (a.scores && f < a.nf) {
+		const unsigned npool = a.ptype == DB_PT_ALL ? 32u : 16u, k = f % 16;
+		if (a.ptype == DB_PT_ALL) { hw_max = a.headW[model * npool + 2 * k]; hw_sum = a.headW[model * npool + 2 * k + 1]; }
+		else if (a.ptype == DB_PT_MAX) hw_max = a.headW[model * npool + k];
+		else hw_sum = a.headW[model * npool + k];
+		hb = a.headB ? a.headB[model] : 0.f;
+	}
+	pool_state ps;
+	ps.reset();
+	unsigned g = g_first;
+	unsigned r0 = a.R[2 * g], r1 = max(a.R[2 * g + 1], r0);
+	unsigned nr0 = 0, nr1 = 0;                          // the next region's bounds, loaded one region ahead
+	if (g + 1 < g_last) { nr0 = a.R[2 * (g + 1)]; nr1 = a.R[2 * (g + 1) + 1]; }
+	bool own = set == 0;
+
+	// Writes region g's outputs (if this warp owns it) and moves to the next region.
+	auto finish_region = [&]() -> bool {
+		if (own) {
+			const unsigned P = r1 - r0;
+			float pmax = ps.max_all() + b;             // max_p relu(z_p + b) = relu(max_p z_p + b)
+			if (RELU) pmax = fmaxf(pmax, 0.f);
+			const float psum = ps.sum_all() + (float)P * b;      // sum_p max(z_p, -b) + P*b
+			const float second = a.ptype == DB_PT_SUM ? psum : psum / (float)P;
+			if (a.pooled && f < a.nf) {
+				const size_t o = (size_t)g * a.nf + f;
+				if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
+				else a.pooled[o] = WANT_MAX ? pmax : second;
+			}
+			if (a.scores) {
+				float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
+				part += __shfl_xor_sync(0xffffffffu, part, 8);
+				part += __shfl_xor_sync(0xffffffffu, part, 4);
+				part += __shfl_xor_sync(0xffffffffu, part, 2);
+				part += __shfl_xor_sync(0xffffffffu, part, 1);
+				if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
+			}
+			ps.reset();
+		}
+		++g;
+		own = !own;
+		if (g >= g_last) return true;
+		const unsigned prev_end = r1;
+		r0 = nr0; r1 = max(nr1, nr0);
+		if (g + 1 < g_last) { nr0 = a.R[2 * (g + 1)]; nr1 = a.R[2 * (g + 1) + 1]; }
+		if (r0 < prev_end) {                           // regions must ascend without overlap
+			if (lane == 0) { *abort_flag = 1; atomicExch(a.status, 3); }
+			return false;
+		}
+		return true;
+	};
+
+	const unsigned ntile = (row_hi - row_lo + 255u) / 256u;
+	bool ok = true;
+	for (unsigned t = 0; ok && t < ntile; ++t) {       // every tile is consumed, so the issuer never waits on us in vain
+		const unsigned slot = t & 1;
+		// lane 0 waits (bounded); the warp stays converged for the aligned TMEM loads
+		unsigned okv = 0;
+		if (lane == 0) okv = mbar_wait(&t_full[slot], (t >> 1) & 1, abort_flag) ? 1u : 0u;
+		ok = __shfl_sync(0xffffffffu, okv, 0) != 0;
+		if (!ok) break;
+		mbar_try_wait(&t_full[slot], (t >> 1) & 1);    // completed: every lane observes the phase
+		tc_fence_after();
+		const unsigned tile_lo = row_lo + t * 256u, tile_hi = min(tile_lo + 256u, row_hi);
+		const uint32_t taddr = tmem_base + ((q4 * 32u) << 16) + slot * 256u;
+		unsigned pos = tile_lo;
+		while (ok && pos < tile_hi && g < g_last) {
+			if (pos >= r1) { ok = finish_region(); continue; }
+			if (pos < r0) { pos = min(r0, tile_hi); continue; }        // rows between regions belong to nobody
+			const unsigned end = min(r1, tile_hi);
+			if (own) {
+				// rows at or past n have no scan output (kangaroo_smat.cpp:105): they read as zero
+				const unsigned live_end = min(end, max(pos, a.n));
+				uint32_t ta = taddr + (pos - tile_lo);
+				unsigned left = live_end - pos;
+				float va[32], vb[32];
+				while (left >= 64) {                 // two groups per TMEM round trip
+					tmem_ld32(ta, va); tmem_ld32(ta + 32, vb);
+					tmem_ld_wait();
+					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
+					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(vb, nb);
+					ta += 64; left -= 64;
+				}
+				// the remaining 0..63 columns in pieces of 32, 16, 8, 4, 2, 1: all requested, then one wait
+				float t16[16], t8[8], t4[4], t2[2], t1[1];
+				if (left & 32) { tmem_ld32(ta, va); ta += 32; }
+				if (left & 16) { tmem_ld16(ta, t16); ta += 16; }
+				if (left & 8)  { tmem_ld8(ta, t8); ta += 8; }
+				if (left & 4)  { tmem_ld4(ta, t4); ta += 4; }
+				if (left & 2)  { tmem_ld2(ta, t2); ta += 2; }
+				if (left & 1)  { tmem_ld1(ta, t1); }
+				tmem_ld_wait();
+				if (left & 32) ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
+				if (left & 16) ps.add<WANT_MAX, WANT_SUM, RELU, 16>(t16, nb);
+				if (left & 8)  ps.add<WANT_MAX, WANT_SUM, RELU, 8>(t8, nb);
+				if (left & 4)  ps.add<WANT_MAX, WANT_SUM, RELU, 4>(t4, nb);
+				if (left & 2)  ps.add<WANT_MAX, WANT_SUM, RELU, 2>(t2, nb);
+				if (left & 1)  ps.add<WANT_MAX, WANT_SUM, RELU, 1>(t1, nb);
+				if (live_end < end) ps.add_zero_rows<WANT_MAX, WANT_SUM, RELU>(end - live_end, nb);
+			}
+			pos = end;
+		}
+		tc_fence_before();
+		__syncwarp();
+		if (lane == 0) mbar_arrive(&t_empty[slot]);
+	}
+	// regions that end exactly where the data ends (and empty regions after it)
+	while (ok && g < g_last) ok = finish_region();
+}
+
+#undef COMMA
+
+__global__ void __launch_bounds__(384, 1)
 scanpool_tc_kernel(const tc_args a)
 {
 	extern __shared__ __align__(128) unsigned char smem[];
 	const unsigned KC = a.KC, NK = KC / 2;
 	const unsigned a_bytes = a.nsplit * KC * 2048u;
 	unsigned char* As = smem;                                    // [nsplit][KC][128][8] bf16
-	unsigned char* Es = smem + a_bytes;                          // [2][TC_ECAP] 16-byte chunks
-	__shared__ __align__(8) uint64_t bar_a, e_full[2], e_empty[2], t_full[TC_NSLOT], t_empty[TC_NSLOT];
+	unsigned char* Es = smem + a_bytes;                          // [2][TC_ECHUNKS] 16-byte chunks
+	__shared__ __align__(8) uint64_t bar_a, e_full[2], e_empty[2], t_full[2], t_empty[2];
 	__shared__ uint32_t tmem_base_s;
-	__shared__ unsigned blk_lo[2], blk_hi[2], blk_count[2], blk_ok[2];
-	__shared__ unsigned blk_r0[2][TC_BLKMAX], blk_rows[2][TC_BLKMAX];   // region table of each staged block
+	__shared__ unsigned rows_s[2], blk_ok[2];
 	__shared__ int abort_s;
 	volatile int* abort_flag = &abort_s;
 
@@ -168,18 +356,26 @@ scanpool_tc_kernel(const tc_args a)
 
 	// A CTA of a launch that has already failed returns at once.  One thread reads
 	// the status word so that the whole CTA takes the same decision.
-	if (threadIdx.x == 0) abort_s = *reinterpret_cast<volatile int*>(a.status);
+	if (threadIdx.x == 0) {
+		abort_s = *reinterpret_cast<volatile int*>(a.status);
+		rows_s[0] = a.R[2 * g_first];
+		rows_s[1] = max(a.R[2 * (g_last - 1) + 1], rows_s[0]);
+	}
 	__syncthreads();
 	if (abort_s != 0) return;
+	// The CTA scans the flat rows [row_lo, row_hi) of its regions in tiles of 256.
+	const unsigned row_lo = rows_s[0], row_hi = rows_s[1];
+	const unsigned ntile = (row_hi - row_lo + 255u) / 256u;
 	__syncthreads();
 	if (threadIdx.x == 0) {
-		abort_s = 0;
 		mbar_init(&bar_a, 1);
-		for (int i = 0; i < 2; ++i) { mbar_init(&e_full[i], 3); mbar_init(&e_empty[i], 1); }
-		for (int i = 0; i < TC_NSLOT; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 4); }
+		for (int i = 0; i < 2; ++i) {
+			mbar_init(&e_full[i], 3); mbar_init(&e_empty[i], 1);
+			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 8);
+		}
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
-	if (warp == 0) tmem_alloc(&tmem_base_s, TC_NSLOT * 128);
+	if (warp == 0) tmem_alloc(&tmem_base_s, 512);
 	tc_fence_before();
 	__syncthreads();
 	tc_fence_after();
@@ -192,182 +388,93 @@ scanpool_tc_kernel(const tc_args a)
 			bulk_g2s(As, reinterpret_cast<const unsigned char*>(a.Wt) + (size_t)tile * a_bytes, a_bytes, &bar_a);
 			bool ok = mbar_wait(&bar_a, 0, abort_flag);
 			const uint32_t a_addr = smem_u32(As), e_addr = smem_u32(Es);
-			unsigned g = g_first, blk = 0, t = 0;
-			while (ok && g < g_last) {
-				const unsigned st = blk & 1;
-				ok = mbar_wait(&e_full[st], (blk >> 1) & 1, abort_flag);
+			const uint32_t desc_hi = (128u >> 4) | (1u << 14);                         // 8-row group stride 128 B; descriptor version 1
+			const uint32_t a_lo0 = ((a_addr >> 4) & 0x3fffu) | ((2048u >> 4) << 16);   // K-chunk stride 2048 B
+			for (unsigned t = 0; ok && t < ntile; ++t) {
+				const unsigned stage = t / TC_STAGE_TILES, st = stage & 1, tt = t % TC_STAGE_TILES;
+				if (tt == 0) {
+					ok = mbar_wait(&e_full[st], (stage >> 1) & 1, abort_flag);
+					if (!ok) break;
+				}
+				const unsigned slot = t & 1;
+				ok = mbar_wait(&t_empty[slot], ((t >> 1) & 1) ^ 1, abort_flag);
 				if (!ok) break;
 				tc_fence_after();
-				const unsigned lo = blk_lo[st], cnt = blk_count[st];
-				for (unsigned i = 0; ok && i < cnt; ++i, ++g) {
-					const unsigned r0 = blk_r0[st][i], P = blk_rows[st][i];
-					for (unsigned c0 = 0; c0 < P; c0 += 128, ++t) {
-						const unsigned slot = t % TC_NSLOT;
-						ok = mbar_wait(&t_empty[slot], ((t / TC_NSLOT) & 1) ^ 1, abort_flag);
-						if (!ok) break;
-						tc_fence_after();
-						const unsigned ncols = min(128u, P - c0), N = (ncols + 15u) & ~15u;
-						const uint32_t idesc = instr_desc(N);
-						const uint32_t d = tmem_base + slot * 128;
-						const uint32_t b0 = e_addr + st * (TC_ECAP * 16) + (r0 - lo + c0) * 16;
-						unsigned acc = 0;
-						for (unsigned s = 0; s < a.nsplit; ++s)
-							for (unsigned kk = 0; kk < NK; ++kk) {
-								umma_bf16(d, smem_desc(a_addr + s * KC * 2048 + kk * 4096, 2048, 128),
-								          smem_desc(b0 + kk * 64, 32, 128), idesc, acc);
-								acc = 1;
-							}
-						umma_commit(&t_full[slot]);
+				const unsigned ncols = min(256u, row_hi - (row_lo + t * 256u)), N = (ncols + 15u) & ~15u;
+				const uint32_t idesc = instr_desc(N);
+				const uint32_t d = tmem_base + slot * 256u;
+				const uint32_t b0 = e_addr + st * (TC_ECHUNKS * 16) + tt * (256 * 16);
+				// Descriptors differ only in the start-address field of their low word:
+				// the A tiles of all splits are contiguous (4096 bytes per MMA), B advances
+				// 64 bytes per MMA and restarts for each split.
+				uint32_t a_lo = a_lo0;
+				const uint32_t b_lo0 = ((b0 >> 4) & 0x3fffu) | ((32u >> 4) << 16);
+				unsigned acc = 0;
+				for (unsigned s = 0; s < a.nsplit; ++s) {
+					uint32_t b_lo = b_lo0;
+					for (unsigned kk = 0; kk < NK; ++kk) {
+						umma_bf16(d, ((uint64_t)desc_hi << 32) | a_lo, ((uint64_t)desc_hi << 32) | b_lo, idesc, acc);
+						acc = 1; a_lo += 4096u >> 4; b_lo += 64u >> 4;
 					}
 				}
-				umma_commit(&e_empty[st]);      // the stage may be rewritten once these MMAs have read it
-				++blk;
+				umma_commit(&t_full[slot]);
+				// the stage may be rewritten once the MMAs that read it have finished
+				if (tt == TC_STAGE_TILES - 1 || t + 1 == ntile) umma_commit(&e_empty[st]);
 			}
 		}
 	} else if (warp < 4) {
 		// ---------------------------------------------------------- E builders
 		const unsigned bt = threadIdx.x - 32;     // 0..95
-		unsigned g = g_first, blk = 0;
-		bool ok = true;
-		while (ok && g < g_last) {
-			const unsigned st = blk & 1;
+		const unsigned nstage = (ntile + TC_STAGE_TILES - 1) / TC_STAGE_TILES;
+		for (unsigned stage = 0; stage < nstage; ++stage) {
+			const unsigned st = stage & 1;
 			// One thread waits (bounded) and publishes the outcome, so that all 96
-			// builder threads take the same path to the named barriers below.
-			if (bt == 0) blk_ok[st] = mbar_wait(&e_empty[st], ((blk >> 1) & 1) ^ 1, abort_flag) ? 1u : 0u;
+			// builder threads take the same path to the named barrier.
+			if (bt == 0) blk_ok[st] = mbar_wait(&e_empty[st], ((stage >> 1) & 1) ^ 1, abort_flag) ? 1u : 0u;
 			asm volatile("bar.sync 1, 96;" ::: "memory");
-			ok = blk_ok[st] != 0;
-			if (!ok) break;
-			// The next TC_BLKMAX regions go to shared memory in parallel; one thread then
-			// takes the longest run whose rows, plus the reach of the last tile, fit in
-			// one stage.  Regions normally abut (the batch layout).
-			if (bt < TC_BLKMAX) {
-				const unsigned h = g + bt;
-				unsigned r0 = 0, r1 = 0;
-				if (h < g_last) { r0 = a.R[2 * h]; r1 = max(a.R[2 * h + 1], r0); }
-				blk_r0[st][bt] = r0; blk_rows[st][bt] = r1 - r0;
-			}
-			asm volatile("bar.sync 1, 96;" ::: "memory");
-			if (bt == 0) {
-				unsigned lo = blk_r0[st][0], hi = lo, cnt = 0;
-				const unsigned avail = min((unsigned)TC_BLKMAX, g_last - g);
-				for (unsigned i = 0; i < avail; ++i) {
-					unsigned r0 = blk_r0[st][i], r1 = r0 + blk_rows[st][i];
-					unsigned nlo = min(lo, r0), nhi = max(hi, r1);
-					if (nhi - nlo + TC_SLACK > TC_ECAP) break;
-					lo = nlo; hi = nhi; ++cnt;
+			if (blk_ok[st] == 0) break;
+			const unsigned base_row = row_lo + stage * (TC_STAGE_TILES * 256u);
+			uint4* E = reinterpret_cast<uint4*>(Es + (size_t)st * TC_ECHUNKS * 16);
+			// A thread encodes 16 consecutive chunks from 20 bytes fetched as aligned words.
+			for (unsigned q = bt * 16; q < TC_ECHUNKS; q += 96 * 16) {
+				const unsigned i0 = base_row + q;
+				const size_t addr = (size_t)a.X + i0;
+				const uint32_t* wp = reinterpret_cast<const uint32_t*>(addr & ~(size_t)3);
+				const unsigned sh = (unsigned)(addr & 3) * 8;
+				uint32_t w[6];
+				#pragma unroll
+				for (int k = 0; k < 6; ++k)      // a word is read only if its first byte lies inside the buffer
+					w[k] = ((long long)i0 + 4 * k - (long long)(addr & 3) < (long long)a.npos) ? wp[k] : 0xfefefefeu;
+				uint32_t win[5];
+				#pragma unroll
+				for (int k = 0; k < 5; ++k) win[k] = __funnelshift_r(w[k], w[k + 1], sh);
+				unsigned long long prev = base_pattern(i0 < a.npos ? (win[0] & 0xffu) : 254u);
+				#pragma unroll
+				for (int c = 0; c < 16; ++c) {
+					const unsigned x1 = (i0 + c + 1 < a.npos) ? ((win[(c + 1) >> 2] >> (8 * ((c + 1) & 3))) & 0xffu) : 254u;
+					const unsigned long long p1 = base_pattern(x1);
+					E[q + c] = make_uint4((unsigned)prev, (unsigned)(prev >> 32), (unsigned)p1, (unsigned)(p1 >> 32));
+					prev = p1;
 				}
-				blk_lo[st] = lo; blk_hi[st] = hi; blk_count[st] = cnt;
-			}
-			asm volatile("bar.sync 1, 96;" ::: "memory");
-			const unsigned lo = blk_lo[st], hi = blk_hi[st], cnt = blk_count[st];
-			if (cnt == 0) { if (bt == 0) { *abort_flag = 1; atomicExch(a.status, 2); } ok = false; break; }   // region longer than a stage
-			const unsigned nchunk = min((unsigned)TC_ECAP, hi - lo + TC_SLACK);
-			uint4* E = reinterpret_cast<uint4*>(Es + (size_t)st * TC_ECAP * 16);
-			for (unsigned q = bt; q < nchunk; q += 96) {
-				const unsigned i0 = lo + q;
-				const unsigned x0 = i0 < a.npos ? a.X[i0] : 254u, x1 = i0 + 1 < a.npos ? a.X[i0 + 1] : 254u;
-				const unsigned long long p0 = base_pattern(x0), p1 = base_pattern(x1);
-				E[q] = make_uint4((unsigned)p0, (unsigned)(p0 >> 32), (unsigned)p1, (unsigned)(p1 >> 32));
 			}
 			fence_async_smem();
 			__syncwarp();
 			if (lane == 0) mbar_arrive(&e_full[st]);
-			g += cnt; ++blk;
 		}
 	} else {
 		// ------------------------------------------------------------ epilogue
-		const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
-		const unsigned fl = q4 * 32 + lane;                 // filter within the tile
-		const unsigned f = tile * 128 + fl;
-		const float b = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
-		const float nb = -b;
-		const bool want_max = a.ptype == DB_PT_MAX || a.ptype == DB_PT_ALL;
-		const bool want_sum = a.ptype != DB_PT_MAX;
-		// linear head of the model this filter belongs to (16 filters per model)
-		float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
-		const unsigned model = f / 16;
-		if (a.scores && f < a.nf) {
-			const unsigned npool = a.ptype == DB_PT_ALL ? 32u : 16u;
-			const unsigned k = f % 16;
-			if (a.ptype == DB_PT_ALL) { hw_max = a.headW[model * npool + 2 * k]; hw_sum = a.headW[model * npool + 2 * k + 1]; }
-			else if (a.ptype == DB_PT_MAX) hw_max = a.headW[model * npool + k];
-			else hw_sum = a.headW[model * npool + k];
-			hb = a.headB ? a.headB[model] : 0.f;
-		}
-		unsigned t = 0;
-		bool ok = true;
-		unsigned nr0 = 0, nr1 = 0;                      // bounds of the next region, loaded one region ahead
-		if (g_first < g_last) { nr0 = a.R[2 * g_first]; nr1 = a.R[2 * g_first + 1]; }
-		for (unsigned g = g_first; ok && g < g_last; ++g) {
-			const unsigned r0 = nr0, P = nr1 > nr0 ? nr1 - nr0 : 0u;
-			if (g + 1 < g_last) { nr0 = a.R[2 * (g + 1)]; nr1 = a.R[2 * (g + 1) + 1]; }
-			float mx = -INFINITY, s0 = 0.f, s1 = 0.f;
-			for (unsigned c0 = 0; c0 < P; c0 += 128, ++t) {
-				const unsigned slot = t % TC_NSLOT;
-				// lane 0 waits (bounded); the warp stays converged for the aligned TMEM loads
-				unsigned okv = 0;
-				if (lane == 0) okv = mbar_wait(&t_full[slot], (t / TC_NSLOT) & 1, abort_flag) ? 1u : 0u;
-				ok = __shfl_sync(0xffffffffu, okv, 0) != 0;
-				if (!ok) break;
-				mbar_try_wait(&t_full[slot], (t / TC_NSLOT) & 1);     // completed: every lane observes the phase
-				tc_fence_after();
-				const unsigned ncols = min(128u, P - c0);
-				// rows at or past n have no scan output (kangaroo_smat.cpp:105): they read as zero
-				const unsigned nvalid = a.n > r0 + c0 ? min(ncols, a.n - (r0 + c0)) : 0u;
-				const uint32_t taddr = tmem_base + ((q4 * 32u) << 16) + slot * 128;
-				for (unsigned c = 0; c < ncols; c += 32) {
-					float v[32];
-					tmem_ld32(taddr + c, v);
-					tmem_ld_wait();
-					const unsigned rem = ncols - c;
-					if (rem >= 32 && nvalid >= c + 32) {
-						#pragma unroll
-						for (int i = 0; i < 32; i += 2) {
-							if (want_max) mx = fmaxf(mx, fmaxf(v[i], v[i + 1]));
-							if (want_sum) { s0 += a.relu ? fmaxf(v[i], nb) : v[i]; s1 += a.relu ? fmaxf(v[i + 1], nb) : v[i + 1]; }
-						}
-					} else {
-						#pragma unroll
-						for (int i = 0; i < 32; ++i) {
-							if ((unsigned)i < rem) {
-								const float x = (c + i < nvalid) ? v[i] : 0.f;
-								if (want_max) mx = fmaxf(mx, x);
-								if (want_sum) s0 += a.relu ? fmaxf(x, nb) : x;
-							}
-						}
-					}
-				}
-				tc_fence_before();
-				__syncwarp();
-				if (lane == 0) mbar_arrive(&t_empty[slot]);
-			}
-			if (!ok) break;
-			// finish the region: max_p relu(z_p + b) = relu(max_p z_p + b); sum_p relu(z_p + b) = sum_p max(z_p, -b) + P*b
-			float pmax = mx + b;
-			if (a.relu) pmax = fmaxf(pmax, 0.f);
-			float psum = (s0 + s1) + (float)P * b;
-			const float pavg = psum / (float)P;
-			const float second = a.ptype == DB_PT_SUM ? psum : pavg;
-			if (a.pooled && f < a.nf) {
-				const size_t o = (size_t)g * a.nf + f;
-				if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, pavg);
-				else a.pooled[o] = want_max ? pmax : second;
-			}
-			if (a.scores) {
-				float part = hw_max * (want_max ? pmax : 0.f) + hw_sum * (want_sum ? second : 0.f);
-				part += __shfl_xor_sync(0xffffffffu, part, 8);
-				part += __shfl_xor_sync(0xffffffffu, part, 4);
-				part += __shfl_xor_sync(0xffffffffu, part, 2);
-				part += __shfl_xor_sync(0xffffffffu, part, 1);
-				if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
-			}
-		}
+		#define TC_EPI(MX, SM, RL) tc_epilogue<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, g_last, row_lo, row_hi, warp, lane)
+		const bool wm = a.ptype == DB_PT_MAX || a.ptype == DB_PT_ALL, ws = a.ptype != DB_PT_MAX;
+		if (a.relu) { if (wm && ws) TC_EPI(true, true, true); else if (wm) TC_EPI(true, false, true); else TC_EPI(false, true, true); }
+		else        { if (wm && ws) TC_EPI(true, true, false); else if (wm) TC_EPI(true, false, false); else TC_EPI(false, true, false); }
+		#undef TC_EPI
 	}
 	tc_fence_before();
 	__syncthreads();
 	if (threadIdx.x == 0 && abort_s) atomicCAS(a.status, 0, 1);
-	if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, TC_NSLOT * 128); }
+	if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
+
 
 // Prepared weights: for each 128-filter tile, `nsplit` K-major bf16 operand tiles
 // in the shared-memory layout [split][K chunk][filter][8], zero padded.
@@ -453,10 +560,11 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int nspli
 	unsigned spc = max(64u, divup(nregion, want_chunks));
 	a.seqs_per_cta = spc;
 	dim3 grid(ntile, divup(nregion, spc));
-	size_t smem = (size_t)nsplit * KC * 2048 + 2 * (size_t)TC_ECAP * 16 + 128;
-	DB_REQUIRE(smem <= 220 * 1024, "ValueError: filter length %u is too long for the tensor-core kernel", m);
+	size_t smem = (size_t)nsplit * KC * 2048 + 2 * (size_t)TC_ECHUNKS * 16 + 128;
+	if (smem < 120 * 1024) smem = 120 * 1024;       // one CTA per SM: each CTA takes all 512 TMEM columns
+	DB_REQUIRE(smem <= 220 * 1024 && 2 * KC + 16 <= 128, "ValueError: filter length %u is too long for the tensor-core kernel", m);
 	DB_CUDA(cudaFuncSetAttribute(scanpool_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-	scanpool_tc_kernel<<<grid, 256, smem, state().stream>>>(a);
+	scanpool_tc_kernel<<<grid, 384, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }

@@ -156,6 +156,28 @@ class DeepBindNet(object):
                      grad=lambda: out.setdefault("loss", self.grads(X, R, Y, dropmask)), nesterov=True)
         return out["loss"]
 
+    # ------------------------------------------------------ tensor-core scoring
+    def prepare_tc(self, nsplit=3):
+        """Prepares the filter bank for the tcgen05 scan (redo after a weight change)."""
+        self._tcw = fused.TCWeights(self.view("Wscan").contiguous(), self.view("bscan").view(-1), nsplit)
+        return self._tcw
+
+    def score_tc(self, X, R, strand_max=False, check=True):
+        """Scores [nseq, I] through the tensor-core scan.  With a linear head the
+        head is applied inside the kernel and no pooled features reach HBM."""
+        bind_stream()
+        tcw = getattr(self, "_tcw", None) or self.prepare_tc()
+        if not self.hidden and self.nf == 16 * self.I:
+            _, out = fused.scanpool_tc(tcw, X, R, self.pool, headW=self.view("W1").reshape(-1),
+                                       headB=self.view("b1").view(-1), check=check)
+        else:
+            pooled, _ = fused.scanpool_tc(tcw, X, R, self.pool, check=check)
+            out, _, _ = self._head(pooled)
+        if strand_max:
+            out = out.view(-1, 2, self.I)
+            out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
+        return out
+
     def score_chunked(self, X, R, out, chunk=16384):
         """Scores every region of a device-resident batch into ``out`` [nseq, I],
         ``chunk`` sequences at a time so that the pooled features (npool*I floats

@@ -161,8 +161,9 @@ void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
  * If `scores` is given, each model's linear head (16 filters per model; headW
  * [(16|32)*nmodel] in the row order of full.W, headB [nmodel]) is applied in the
  * kernel and scores [nregion, nmodel] is written; `pooled` may then be NULL.
- * Regions must be at most 2100 rows long.  status: device int, 0 = ok,
- * 1 = a wait timed out, 2 = a region is too long. */
+ * Regions must ascend without overlap (the batch layout of data.py:329-334); rows
+ * between regions are scanned and discarded.  status: device int the caller
+ * zeroes; 0 = ok, 1 = a device-side wait timed out, 3 = regions out of order. */
 size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int nsplit);
 void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int nsplit, void* prepared);
 void db_scanpool_tc(const void* prepared, uint32_t m, uint32_t nf, int nsplit, const float* bias, int relu,
