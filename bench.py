@@ -40,7 +40,9 @@ def parse():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--nseq", type=int, default=1000000, help="sequences per GPU")
     ap.add_argument("--nmodel", type=int, default=512)
-    ap.add_argument("--chunk", type=int, default=16384)
+    ap.add_argument("--chunk", type=int, default=16384, help="sequences per launch of the FP32 variant")
+    ap.add_argument("--variant", default="bf16x3", choices=["bf16x3", "bf16x2", "bf16", "f32"],
+                    help="arithmetic of the scan: bf16 pieces on tcgen05 (x3 = fp32-grade) or FP32 lookup-add")
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -139,6 +141,15 @@ class ClockSampler(object):
 
 
 # ------------------------------------------------------------------ GPU arm
+VARIANTS = {
+    # name: (nsplit or None for the FP32 lookup-add kernel, dtype string, stated tolerance)
+    "bf16x3": (3, "bf16x3 (three bf16 pieces per weight on tcgen05, fp32 accumulate; <=1e-5 of the fp32 reference)", 1e-5),
+    "bf16x2": (2, "bf16x2 (two bf16 pieces per weight, fp32 accumulate; <=1e-5)", 1e-5),
+    "bf16":   (1, "bf16 (fp32 accumulate; <=2e-3)", 2e-3),
+    "f32":    (None, "f32 (lookup-add, bit-exact pooling)", 0.0),
+}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -146,7 +157,7 @@ def main():
         return
     import torch
     import torch.distributed as dist
-    from deepbind_b200 import _lib, synth
+    from deepbind_b200 import _lib, fused, synth
     from deepbind_b200.model import DeepBindNet
 
     rank = int(os.environ.get("RANK", "0"))
@@ -161,6 +172,7 @@ def main():
     dll = _lib.load()
 
     I, nseq = args.nmodel, args.nseq
+    nsplit, dtype_name, tol = VARIANTS[args.variant]
     params = synth.model_params(I, M, 7, "all")
     net = DeepBindNet(params, I, "all")
     Xh, Rh = synth.uniform_batch(nseq, L, M, seed=1000 + rank)
@@ -170,19 +182,28 @@ def main():
     X = X_host.to(dev); R = R_host.to(dev)
     scores = torch.empty((nseq, I), dtype=torch.float32, device=dev)
     gathered = torch.empty((nseq * world, I), dtype=torch.float32, device=dev) if world > 1 else None
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    if nsplit:
+        net.prepare_tc(nsplit)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def score():
+        if nsplit:
+            net.score_tc(X, R, check=False, out=scores, status=status)
+        else:
+            net.score_chunked(X, R, scores, args.chunk)
+
     def step():
-        net.score_chunked(X, R, scores, args.chunk)
+        score()
         if world > 1:
             dist.all_gather_into_tensor(gathered, scores)
 
     def e2e_step():
-        net.predict_host(X_host, R_host, out_host, args.chunk, dev_bufs=(X, R, scores))
+        net.predict_host(X_host, R_host, out_host, args.chunk, dev_bufs=(X, R, scores), tc=bool(nsplit))
         if world > 1:
             dist.all_gather_into_tensor(gathered, scores)
 
@@ -199,7 +220,8 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(3, args.warmup)):
+    warm = max(3, args.warmup)
+    for _ in range(warm):
         step()
     sampler = ClockSampler(local) if rank == 0 else None
     l0 = dll.api_launch_count()
@@ -208,47 +230,64 @@ def main():
     clocks = sampler.stop() if sampler else None
     e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
+    if int(status.item()) != 0:
+        raise SystemExit("tensor-core scan reported status %d" % int(status.item()))
 
-    # dominant kernel alone: the fused scan+pool launches of one step, CUDA events on the launch stream
-    from deepbind_b200 import fused
-    Wd, bd = net.view("Wscan"), net.view("bscan").view(-1)
-    nchunk = (nseq + args.chunk - 1) // args.chunk
-    barrier()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ktime = 0.0
-    reps = min(args.steps, 2)
-    for _ in range(reps):
-        for s in range(0, nseq, args.chunk):
-            Rc = R[s:min(nseq, s + args.chunk)]
-            k0.record()
-            fused.scanpool(Wd, bd, X, Rc, "all", relu=True)
-            k1.record()
-            k1.synchronize()
-            ktime += k0.elapsed_time(k1)
-    kernel_ms_per_launch = ktime / (reps * nchunk)
-    adds_per_launch = adds_per_seq(I) * min(args.chunk, nseq)
+    # dominant kernel alone: CUDA events on the launch stream around the scan launches of one step
     peaks = {}
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
         peaks = json.load(open(pk))
     prop = torch.cuda.get_device_properties(dev)
-    sm_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz") or 1965.0
-    # One 4-byte table operand per add comes back from shared memory at 128 B/clk/SM:
-    # 32 adds/clk/SM.  The FP32 add-issue ceiling (128 lanes/clk/SM) is 4x that.
-    lut_peak = prop.multi_processor_count * 32 * sm_max * 1e6
-    achieved = adds_per_launch / (kernel_ms_per_launch * 1e-3)
-    roofline = {"bound": "smem-lookup", "kernel": "scanpool_fwd_kernel<24> (FP32 lookup-add)",
-                "achieved": achieved / 1e12, "peak": lut_peak / 1e12, "unit": "Tadd/s", "frac": achieved / lut_peak,
-                "peak_source": "SMs x 32 table operands/clk x max SM clock (shared-memory return path); "
-                               "FP32 add issue would be 4x this", "traffic": None,
-                "ms_per_launch": kernel_ms_per_launch,
-                "hbm_gbs_algorithmic": (min(args.chunk, nseq) * ((L + M - 1) + I * 32 * 4)) / (kernel_ms_per_launch * 1e-3) / 1e9}
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = min(args.steps, 3)
+    if nsplit:
+        k0.record()
+        for _ in range(reps):
+            net.score_tc(X, R, check=False, out=scores, status=status)
+        k1.record(); k1.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / reps
+        dense_flop = 2.0 * 4 * M * (L + M - 1) * NMOTIF * I * nseq          # 2*K*rows*filters
+        exec_flop = nsplit * dense_flop
+        peak = peaks.get("bf16_tflops_sustained") or 1400.0
+        src = "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS bf16 GEMM run back to back under the power cap)" \
+            if "bf16_tflops_sustained" in peaks else "fallback 1.4 PFLOP/s sustained"
+        roofline = {"bound": "tensor", "kernel": "scanpool_tc_kernel (tcgen05 bf16, %d piece(s) per weight)" % nsplit,
+                    "achieved": exec_flop / (kernel_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                    "frac": exec_flop / (kernel_ms * 1e-3) / 1e12 / peak, "peak_source": src,
+                    "flops_counted": "executed tensor flops = %d x dense-equivalent 2*K*rows*filters (K=96); the pieces are what "
+                                     "fp32-grade results cost on bf16 tensor cores" % nsplit,
+                    "dense_equiv_tflops": dense_flop / (kernel_ms * 1e-3) / 1e12,
+                    "burst_peak": peaks.get("bf16_tflops"), "traffic": None, "ms_per_launch": kernel_ms,
+                    "hbm_gbs_algorithmic": (nseq * ((L + M - 1) + I * 4)) / (kernel_ms * 1e-3) / 1e9}
+    else:
+        Wd, bd = net.view("Wscan"), net.view("bscan").view(-1)
+        nchunk = (nseq + args.chunk - 1) // args.chunk
+        ktime = 0.0
+        for _ in range(min(reps, 2)):
+            for s in range(0, nseq, args.chunk):
+                Rc = R[s:min(nseq, s + args.chunk)]
+                k0.record()
+                fused.scanpool(Wd, bd, X, Rc, "all", relu=True)
+                k1.record(); k1.synchronize()
+                ktime += k0.elapsed_time(k1)
+        kernel_ms = ktime / (min(reps, 2) * nchunk)
+        adds = adds_per_seq(I) * min(args.chunk, nseq)
+        sm_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz") or 1965.0
+        lut_peak = prop.multi_processor_count * 32 * sm_max * 1e6
+        roofline = {"bound": "smem-lookup", "kernel": "scanpool_fwd_kernel<24> (FP32 lookup-add)",
+                    "achieved": adds / (kernel_ms * 1e-3) / 1e12, "peak": lut_peak / 1e12, "unit": "Tadd/s",
+                    "frac": adds / (kernel_ms * 1e-3) / lut_peak,
+                    "peak_source": "SMs x 32 table operands/clk x max SM clock (shared-memory return path, one 4-byte operand "
+                                   "per add); FP32 add issue would be 4x this", "traffic": None, "ms_per_launch": kernel_ms}
 
     if rank == 0:
         line = {"metric": METRIC, "value": nseq * world * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": config(args, world), "clocks": clocks,
+                "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+                "config": dict(config(args, world), variant=args.variant, tolerance_vs_fp32_reference=tol),
+                "clocks": clocks,
                 "e2e": {"value": nseq * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": int(X_host.numel() + R_host.numel() * 4),
                         "d2h_bytes_per_step": int(out_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},

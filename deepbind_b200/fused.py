@@ -70,20 +70,28 @@ class TCWeights(object):
         dll.db_tc_prepare(_ptr(W), self.m, self.nf, self.nsplit, _ptr(self.buf))
 
 
-def scanpool_tc(tcw, X, R, ptype="all", relu=True, headW=None, headB=None, want_pooled=None, check=True):
+def scanpool_tc(tcw, X, R, ptype="all", relu=True, headW=None, headB=None, want_pooled=None, check=True,
+                scores_out=None, status=None):
     """Tensor-core scan + bias + rectify + pooling of a prepared filter bank.
 
     Returns (pooled, scores): pooled as :func:`scanpool` (or None), scores
     [nregion, nmodel] when a linear head (headW [(16|32)*nmodel], headB [nmodel])
-    is given.  ``check`` reads the kernel's status word back (one sync)."""
+    is given.  ``check`` reads the kernel's status word back (one sync);
+    ``scores_out`` / ``status`` let a caller reuse its buffers (status must be a
+    zeroed int32 tensor of one element)."""
     _check(X, torch.uint8, "X"); _check(R, torch.int32, "R")
     nregion, npos, nf = R.shape[0], X.numel(), tcw.nf
     if want_pooled is None:
         want_pooled = headW is None
     pooled = torch.empty((nregion, nf * (2 if ptype == "all" else 1)), dtype=torch.float32, device=X.device) if want_pooled else None
     nmodel = nf // 16 if headW is not None else 0
-    scores = torch.empty((nregion, nmodel), dtype=torch.float32, device=X.device) if headW is not None else None
-    status = torch.zeros(1, dtype=torch.int32, device=X.device)
+    scores = None
+    if headW is not None:
+        scores = scores_out if scores_out is not None else torch.empty((nregion, nmodel), dtype=torch.float32, device=X.device)
+        _check(scores, torch.float32, "scores_out")
+        assert tuple(scores.shape) == (nregion, nmodel)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=X.device)
     _dll().db_scanpool_tc(_ptr(tcw.buf), tcw.m, nf, tcw.nsplit, _ptr(tcw.bias), int(bool(relu)), _ptr(X), npos, _ptr(R),
                           nregion, PT[ptype], _ptr(pooled), _ptr(headW), _ptr(headB), nmodel, _ptr(scores), _ptr(status))
     if check:

@@ -162,14 +162,14 @@ class DeepBindNet(object):
         self._tcw = fused.TCWeights(self.view("Wscan").contiguous(), self.view("bscan").view(-1), nsplit)
         return self._tcw
 
-    def score_tc(self, X, R, strand_max=False, check=True):
+    def score_tc(self, X, R, strand_max=False, check=True, out=None, status=None):
         """Scores [nseq, I] through the tensor-core scan.  With a linear head the
         head is applied inside the kernel and no pooled features reach HBM."""
         bind_stream()
         tcw = getattr(self, "_tcw", None) or self.prepare_tc()
         if not self.hidden and self.nf == 16 * self.I:
             _, out = fused.scanpool_tc(tcw, X, R, self.pool, headW=self.view("W1").reshape(-1),
-                                       headB=self.view("b1").view(-1), check=check)
+                                       headB=self.view("b1").view(-1), check=check, scores_out=out, status=status)
         else:
             pooled, _ = fused.scanpool_tc(tcw, X, R, self.pool, check=check)
             out, _, _ = self._head(pooled)
@@ -188,7 +188,7 @@ class DeepBindNet(object):
             out[s:e].copy_(self.score(X, R[s:e]))
         return out
 
-    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None):
+    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False):
         """The call a user makes for scoring: ordinal batch in (pinned) host
         memory -> scores in (pinned) host memory.  Mirrors what
         kangaroo.predict does per batch (code/libs/kangaroo/kangaroo/predict.py:168-176):
@@ -200,7 +200,10 @@ class DeepBindNet(object):
         X, R, out = dev_bufs
         X.copy_(X_host, non_blocking=True)
         R.copy_(R_host, non_blocking=True)
-        self.score_chunked(X, R, out, chunk)
+        if tc:
+            self.score_tc(X, R, check=False, out=out)
+        else:
+            self.score_chunked(X, R, out, chunk)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return out_host
