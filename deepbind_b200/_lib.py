@@ -94,6 +94,7 @@ _PROTOTYPES = {
     "db_relu": (None, [P, P, c_size_t]),
     "db_relu_bprop": (None, [P, P, P, c_size_t]),
     "db_colsum": (None, [P, P, c_uint32, c_uint32]),
+    "db_colsum_static": (None, [P, P, c_uint32, c_uint32]),
     "db_logistic": (None, [P, P, c_size_t]),
     "db_loss": (None, [c_int, P, P, P, P, c_uint32, c_uint32, P, P]),
     "db_scanpool_fwd": (None, [P, c_uint32, c_uint32, P, c_int, P, c_uint32, P, c_uint32, c_int, P, P, P]),

@@ -149,6 +149,55 @@ DB_EXPORT void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t nco
 	DB_API_CATCH
 }
 
+// ---------------------------------------------------------------------------
+// Column sums without any allocation.  Some hosts may not create device memory
+// when they call us: a process that has handed every byte of the GPU to its own
+// pool, a real-time loop that must not take the allocator's locks, or code
+// running where cudaMalloc is forbidden altogether.  For them the per-block
+// partial sums live in a fixed array that is part of the library image itself.
+// Every GPU that loads the library carries these 1 MiB until the process exits.
+static constexpr unsigned COLSUM_STATIC_FLOATS = 1u << 18;           // 1 MiB of partial sums
+static __device__ __align__(256) float g_colsum_static_scratch[COLSUM_STATIC_FLOATS];
+
+// In host code the array's name is only a handle for the runtime, not an address
+// a kernel may use.  The real device address is asked for once per device, with
+// that device current, and cached.
+static float* colsum_static_scratch_ptr()
+{
+	static float* ptrs[64] = {nullptr};
+	int dev = 0;
+	DB_CUDA(cudaGetDevice(&dev));
+	DB_REQUIRE(dev >= 0 && dev < 64, "RuntimeError: device index %d out of range", dev);
+	if (!ptrs[dev]) {
+		void* p = nullptr;
+		cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);
+		DB_REQUIRE(e == cudaSuccess && p != nullptr, "AssertionError: CUDA error: cudaGetSymbolAddress failed: %s",
+		           cudaGetErrorString(e));
+		ptrs[dev] = (float*)p;
+	}
+	return ptrs[dev];
+}
+
+DB_EXPORT void db_colsum_static(float* out, const float* A, uint32_t nrow, uint32_t ncol)
+{
+	DB_API_TRY
+	if (!ncol) return;
+	DB_REQUIRE(out && (A || !nrow), "ValueError: db_colsum_static got a NULL pointer");
+	unsigned parts = divup(nrow, 256u);
+	DB_REQUIRE((size_t)parts * ncol <= COLSUM_STATIC_FLOATS,
+	           "ValueError: db_colsum_static supports ceil(nrow/256)*ncol <= %u partial sums (got %u x %u); "
+	           "use db_colsum for larger inputs", COLSUM_STATIC_FLOATS, parts, ncol);
+	float* partial = colsum_static_scratch_ptr();
+	if (!nrow) { DB_CUDA(cudaMemsetAsync(out, 0, (size_t)ncol * 4, state().stream)); return; }
+	// Stage 1 writes every partial that stage 2 reads, so what an earlier call left
+	// in the array does not matter and nothing has to be cleared.
+	colsum_stage1<<<dim3(parts, divup(ncol, 32u)), 256, 0, state().stream>>>(A, nrow, ncol, partial);
+	DB_LAUNCH_CHECK();
+	colsum_stage2<<<divup(ncol, 128u), 128, 0, state().stream>>>(out, partial, ncol, parts);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
 DB_EXPORT void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, const uint8_t* Zmask,
                        uint32_t nrow, uint32_t ncol, float* loss_out, float* dZ)
 {

@@ -123,6 +123,15 @@ void db_bias_add(float* Z, const float* X, const float* b, uint32_t nrow, uint32
 void db_relu(float* Z, const float* X, size_t n);                                                /* max(0,X)    */
 void db_relu_bprop(float* dX, const float* dZ, const float* Z, size_t n);                        /* dZ*sign(Z)  */
 void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t ncol);                        /* sum(A,axis=0), fixed order */
+/* No counterpart in the reference.  Same result as db_colsum, for callers that
+ * must not allocate device memory (a host that owns all GPU memory through its
+ * own pool, or one that may not call cudaMalloc where it runs): the partial sums
+ * go to a 1 MiB array built into the library, so no cudaMalloc/cudaFree happens
+ * in this call.  Limit: ceil(nrow/256)*ncol <= 262144, else an error.  The
+ * first call on a device looks the array's address up; make that call before
+ * any stream capture.  All calls share the array: calls that overlap on the GPU
+ * (different streams) race on it. */
+void db_colsum_static(float* out, const float* A, uint32_t nrow, uint32_t ncol);
 void db_logistic(float* Z, const float* X, size_t n);
 /* loss_node forward+backward (loss.py:52-112): kind 0 = mse, 1 = nll.  Z,Y [nrow,ncol];
  * Ymask/Zmask nullable bool [nrow,ncol]; loss_out [ncol] = scaled column means;
