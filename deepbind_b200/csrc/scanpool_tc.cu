@@ -9,7 +9,7 @@
 // bits) that are accumulated into the same FP32 tensor-memory tile, so every
 // product is exact and only the summation order differs from the FP32 path.
 //
-// Layout of one CTA (256 threads, 1 CTA per SM):
+// Layout of one CTA (384 threads, 1 CTA per SM):
 //   M = 128 filters of one filter tile (A operand: prepared bf16 weights, K-major,
 //       resident in shared memory for the CTA's lifetime, loaded by one bulk copy);
 //   N = 256 consecutive rows of the ordinal buffer (B operand), whatever sequences
@@ -22,12 +22,15 @@
 // shared-memory descriptor uses an 8-row group stride of 128 bytes and a K-chunk
 // stride of 32 bytes: row p, chunk kc lives at E + 16*(p + 2*kc).
 // Warp roles: warp 0 issues tcgen05.mma; warps 1-3 encode E for the next stage of
-// 8 tiles (double buffered); warps 4-7 drain the accumulators: each thread owns one
-// filter (one TMEM lane), walks the tile's columns in step with the region table
-// and reduces its row in registers (bias, rectify, max / mean); when a region ends
-// it either stores the pooled features or folds them through the model's linear
-// head (16 lanes = one model, warp shuffles).  Per-position activations never
-// leave the SM.  Regions must ascend without overlap (the batch layout).
+// 8 tiles (double buffered); warps 4-11 drain the accumulators: each thread owns one
+// filter (one TMEM lane); two warps share a lane quarter, one taking the even
+// regions and one the odd.  A warp fetches the columns of its region starting at
+// the region's own first column, in pieces of 64/32/16/8/4/2/1 columns, so the
+// reduction (bias, rectify, max / mean, in registers) needs no per-column tests;
+// when a region ends it either stores the pooled features or folds them through
+// the model's linear head (16 lanes = one model, warp shuffles).  Per-position
+// activations never leave the SM.  Regions must ascend without overlap (the batch
+// layout).
 //
 // Every wait on an mbarrier is bounded by a clock deadline; on expiry the CTA sets
 // a status word, releases its tensor memory and returns.
