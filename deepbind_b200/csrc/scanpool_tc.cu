@@ -175,12 +175,36 @@ DB_TMEM_LD_SMALL(tmem_ld1, 1, "=r"(r[0]), "%0")
 // independent chains keep a lone warp issuing; there are no per-column tests:
 // the columns of a region are fetched from tensor memory starting at the
 // region's own first column, in pieces of 64/32/16/8/4/2/1.
+// Blackwell-only arithmetic: a three-input maximum and a packed pair of FP32 adds
+// (one issue slot each), which trim the per-column cost of the reduction.
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+	float d;
+	asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+	return d;
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+	unsigned long long r;
+	asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+	return r;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b)
+{
+	unsigned long long r;
+	asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+	return r;
+}
+
 struct pool_state {
-	float mx[4], sm[4];
+	float mx[4];
+	unsigned long long sm2[4];      // four packed pairs of partial sums
+	float sm1;                      // scalar partial sum (tails shorter than 8 columns)
 	__device__ __forceinline__ void reset()
 	{
 		#pragma unroll
-		for (int j = 0; j < 4; ++j) { mx[j] = -INFINITY; sm[j] = 0.f; }
+		for (int j = 0; j < 4; ++j) { mx[j] = -INFINITY; sm2[j] = 0ull; }
+		sm1 = 0.f;
 	}
 	template <bool WANT_MAX, bool WANT_SUM, bool RELU, int N>
 	__device__ __forceinline__ void add(const float (&v)[N], float nb)
@@ -191,15 +215,15 @@ struct pool_state {
 				#pragma unroll
 				for (int j = 0; j < 4; ++j) {
 					const float x0 = v[i + 2 * j], x1 = v[i + 2 * j + 1];
-					if (WANT_MAX) mx[j] = fmaxf(mx[j], fmaxf(x0, x1));
-					if (WANT_SUM) sm[j] += (RELU ? fmaxf(x0, nb) : x0) + (RELU ? fmaxf(x1, nb) : x1);
+					if (WANT_MAX) mx[j] = max3(mx[j], x0, x1);
+					if (WANT_SUM) sm2[j] = add2(sm2[j], pack2(RELU ? fmaxf(x0, nb) : x0, RELU ? fmaxf(x1, nb) : x1));
 				}
 			}
 		} else {
 			#pragma unroll
 			for (int i = 0; i < N; ++i) {
 				if (WANT_MAX) mx[i & 3] = fmaxf(mx[i & 3], v[i]);
-				if (WANT_SUM) sm[i & 3] += RELU ? fmaxf(v[i], nb) : v[i];
+				if (WANT_SUM) sm1 += RELU ? fmaxf(v[i], nb) : v[i];
 			}
 		}
 	}
@@ -208,10 +232,16 @@ struct pool_state {
 	__device__ __forceinline__ void add_zero_rows(unsigned cnt, float nb)
 	{
 		if (WANT_MAX) mx[0] = fmaxf(mx[0], 0.f);
-		if (WANT_SUM) sm[0] += (float)cnt * (RELU ? fmaxf(0.f, nb) : 0.f);
+		if (WANT_SUM) sm1 += (float)cnt * (RELU ? fmaxf(0.f, nb) : 0.f);
 	}
 	__device__ __forceinline__ float max_all() const { return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])); }
-	__device__ __forceinline__ float sum_all() const { return (sm[0] + sm[1]) + (sm[2] + sm[3]); }
+	__device__ __forceinline__ float sum_all() const
+	{
+		const unsigned long long t = add2(add2(sm2[0], sm2[1]), add2(sm2[2], sm2[3]));
+		float lo, hi;
+		asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(t));
+		return (lo + hi) + sm1;
+	}
 };
 
 template <bool WANT_MAX, bool WANT_SUM, bool RELU>
@@ -557,9 +587,15 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int nspli
 	a.pooled = pooled; a.scores = scores; a.status = status;
 	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.KC = KC; a.nsplit = nsplit;
 	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu;
-	// Sequence chunks: enough CTAs for about 8 waves over the SMs, at least 64 sequences each.
+	// Sequence chunks: about 8 waves of CTAs over the SMs (one CTA per SM), with the CTA
+	// count a multiple of the SM count so that the last wave is full; at least 64
+	// sequences per CTA.
 	unsigned sms = state().sm_count;
+	unsigned g = ntile, h = sms;
+	while (h) { unsigned r = g % h; g = h; h = r; }              // gcd(ntile, sms)
+	unsigned step = sms / g;                                     // chunk counts that fill whole waves
 	unsigned want_chunks = max(1u, (8 * sms + ntile - 1) / ntile);
+	want_chunks = divup(want_chunks, step) * step;
 	unsigned spc = max(64u, divup(nregion, want_chunks));
 	a.seqs_per_cta = spc;
 	dim3 grid(ntile, divup(nregion, spc));
