@@ -45,6 +45,7 @@ def parse():
                     help="arithmetic of the scan: bf16 pieces on tcgen05 (x3 = fp32-grade) or FP32 lookup-add")
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the short runs of the other benchmark configurations")
     return ap.parse_args()
 
 
@@ -148,6 +149,110 @@ VARIANTS = {
     "bf16":   (1, "bf16 (fp32 accumulate; <=2e-3)", 2e-3),
     "f32":    (None, "f32 (lookup-add, bit-exact pooling)", 0.0),
 }
+
+
+def _events_ms(fn, reps):
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record(); e1.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def side_workloads(dev, with_cpu):
+    """Short device-timed runs of the other benchmark configurations (inputs resident
+    in HBM, CUDA events, 3+ warm-up passes), each beside the CPU restatement timed on
+    a bounded sample.  They ride along in the JSON line under `other_configs`."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    from oracle import oracle as orc
+    out = {}
+
+    def to_dev(Xh, Rh):
+        return torch.from_numpy(Xh).to(dev), torch.from_numpy(Rh.view(np.int32)).to(dev)
+
+    def cpu_time(fn, units):
+        if not with_cpu:
+            return None
+        t = time.perf_counter(); fn(); dt = time.perf_counter() - t
+        return units / dt
+
+    # config 1: PBM-style forward scoring, 4096 x 40 nt, one model, exact FP32 kernel
+    p = synth.model_params(1, M, 21, "max")
+    Xh, Rh = synth.uniform_batch(4096, 40, M, seed=22)
+    net = DeepBindNet(p, 1, "max"); X, R = to_dev(Xh, Rh)
+    for _ in range(3):
+        net.score(X, R)
+    ms = _events_ms(lambda: net.score(X, R), 20)
+    out["pbm_forward"] = {"unit": "sequences/s", "value": 4096 / ms * 1e3, "ms": ms, "kernel": "f32 lookup-add, bit-exact",
+                          "cpu": cpu_time(lambda: orc.score_net(p, Xh, Rh, "max", 1), 4096)}
+
+    # config 5: ragged both-strand RNA scoring, 200000 x U{20..200} nt, 5 % N, 16 x 16 filters, strand max
+    p = synth.model_params(1, 16, 51, "max")
+    Xh, Rh = synth.ragged_batch(200000, 20, 200, 16, seed=52, n_frac=0.05, both_strands=True)
+    net = DeepBindNet(p, 1, "max"); X, R = to_dev(Xh, Rh)
+    for _ in range(3):
+        net.score(X, R, strand_max=True)
+    ms = _events_ms(lambda: net.score(X, R, strand_max=True), 10)
+    ns = 20000
+    out["ragged_rna"] = {"unit": "sequences/s", "value": 200000 / ms * 1e3, "ms": ms, "kernel": "f32 lookup-add, bit-exact",
+                         "cpu": cpu_time(lambda: orc.score_net(p, Xh[:Rh[2 * ns - 1, 1] + 15], Rh[:2 * ns], "max", 1, strand_max=True), ns)}
+    del X, R
+
+    def train(name, I, B, L, pool, hidden, loss, nbatch, reps, cpu_steps):
+        """Minibatch steps (forward, backward, Nesterov update) replayed from a CUDA
+        graph; every step first copies the next minibatch of the resident dataset
+        into the graph's input buffers."""
+        p = synth.model_params(I, M, 31, pool, hidden=hidden)
+        g = synth.rng(32)
+        Xh, Rh = synth.uniform_batch(B * nbatch, L, M, seed=33)
+        rows = B * (L + M - 1)
+        Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(M - 1, 255, np.uint8)])
+                                          for i in range(nbatch)])).to(dev)
+        R1 = torch.from_numpy(Rh[:B].view(np.int32)).to(dev)
+        Yh = g.integers(0, 2, size=(nbatch, B, 1)).astype(np.float32) if loss == "nll" else \
+            g.standard_normal((nbatch, B, 1)).astype(np.float32)
+        Yall = torch.from_numpy(np.tile(Yh, (1, 1, I))).to(dev)
+        npool = NMOTIF * (2 if pool == "all" else 1)
+        Mall = torch.from_numpy(g.random((nbatch, B, npool * I)) >= 0.5).to(dev) if hidden else None
+        net = DeepBindNet(p, I, pool, loss=loss)
+        lr = np.exp(g.uniform(np.log(1e-4), np.log(1e-1), I)).astype(np.float32) if I > 1 else 0.01
+        net.set_rates(lr, 0.9)
+        Xs, Ys = Xall[0].clone(), Yall[0].clone()
+        Ms = Mall[0].clone() if Mall is not None else None
+        graph, _ = net.capture_train_step(Xs, R1, Ys, Ms)
+        state = {"i": 0}
+
+        def step():
+            i = state["i"] = (state["i"] + 1) % nbatch
+            Xs.copy_(Xall[i]); Ys.copy_(Yall[i])
+            if Ms is not None:
+                Ms.copy_(Mall[i])
+            graph.replay()
+        for _ in range(5):
+            step()
+        ms = _events_ms(step, reps)
+        cpu = None
+        if with_cpu:
+            mk = (np.random.default_rng(1).random((B, npool * I)) >= 0.5) if hidden else None
+            Xb = np.concatenate([Xh[:rows], np.full(M - 1, 255, np.uint8)])
+            t = time.perf_counter()
+            for _ in range(cpu_steps):
+                orc.train_grads(p, Xb, Rh[:B], np.tile(Yh[0], (1, I)), pool, I, loss, mk)
+            cpu = cpu_steps * B * I / (time.perf_counter() - t)
+        out[name] = {"unit": "train samples/s (model x sample)", "value": I * B / ms * 1e3, "ms_per_step": ms,
+                     "models": I, "minibatch": B, "kernel": "f32 fused scan+pool forward/backward, CUDA-graph replay",
+                     "cpu": cpu}
+
+    # config 2: ChIP-seq-style training, one model, minibatch 128, allpool -> 32 hidden (dropout 0.5) -> sigmoid
+    train("chip_train", 1, 128, 101, "all", 32, "nll", 64, 200, 5)
+    # config 3: calibration sweep, 90 independent models trained at once on 40-nt probes, minibatch 64
+    train("calibration", 90, 64, 40, "max", 0, "mse", 64, 100, 1)
+    return out
 
 
 def main():
@@ -294,6 +399,10 @@ def main():
                 "gpu_launches": launches, "roofline": roofline}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_run(args, args.cpu_sample, 1, 1)
+        if world == 1 and not args.no_side:
+            del X, R, scores, X_host, R_host, out_host
+            torch.cuda.empty_cache()
+            line["other_configs"] = side_workloads(dev, not args.no_cpu_baseline)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

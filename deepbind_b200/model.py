@@ -208,5 +208,27 @@ class DeepBindNet(object):
         torch.cuda.current_stream().synchronize()
         return out_host
 
+    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3):
+        """Captures one Nesterov step on the static buffers X, R, Y, dropmask into a
+        CUDA graph and returns (graph, loss): refill the buffers in place (same
+        shapes) and call ``graph.replay()`` for every further step.  A minibatch
+        step is some twenty small kernels; replaying them as one graph removes the
+        per-launch host cost that otherwise dominates (the reference pays it on
+        every step, 40-60 ctypes calls each).  The warm-up steps run first on a
+        side stream so that the library's scratch buffer has its final size: no
+        allocation may happen while a stream is being captured."""
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.train_step(X, R, Y, dropmask)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            loss = self.train_step(X, R, Y, dropmask)
+        return graph, loss
+
     def params_numpy(self, of="P"):
         return {k: self.view(k, of).detach().cpu().numpy().reshape(self.shapes[k]) for k in self.names}
