@@ -1,0 +1,180 @@
+// The dense head of a DeepBind training step in one kernel.
+//
+// After pooling, the reference runs per minibatch step, each as its own launch
+// with a round trip through HBM: dropout (deepity/std/elemwise.py:128-150),
+// full -> bias -> rectify -> full -> bias (full.py:78-89, elemwise.py:171,74-78),
+// logistic (softmax.py:50-61), the loss and its gradient (loss.py:52-112), and the
+// three block-diagonal products of the backward pass (blockwise_dot_nt/_tn) plus
+// the bias sums -- about seventeen launches for a few hundred kilobytes of data.
+// Here one CTA per model keeps the minibatch of that model in shared memory and
+// does all of it: forward, loss, backward, writing the parameter gradients and
+// the gradient of the pooled features.  Every sum runs in a fixed order (rows
+// ascending), so repeated runs agree bit for bit.
+//
+// Layouts follow the reference (full.py:57, loss.py:57-65): pooled [B, npool*I],
+// W1 [(npool*I), H] stacked on rows per model, b1 [H*I], W2 [(H*I), 1], b2 [I],
+// Y [B, I]; H = 0 means a linear head W1 [(npool*I), 1], b1 [I].
+#include "db_common.cuh"
+
+namespace db {
+
+struct head_args {
+	const float* pooled; const uint8_t* mask; const float* Y;
+	const float* W1; const float* b1; const float* W2; const float* b2;
+	float* loss; float* dpooled; float* dW1; float* db1; float* dW2; float* db2;
+	unsigned B, I, npool, H;
+	int kind;
+};
+
+__global__ void __launch_bounds__(256)
+head_train_kernel(const head_args a)
+{
+	extern __shared__ __align__(16) float hs[];
+	const unsigned B = a.B, np = a.npool, H = a.H, HC = H ? H : 1u, WS = HC + 1;   // WS: padded row stride of W1
+	const unsigned b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+	float* pd  = hs;                       // [B][np]   pooled features after dropout
+	float* h1  = pd + (size_t)B * np;      // [B][HC]   hidden pre-activation, then its gradient
+	float* a1  = h1 + (size_t)B * HC;      // [B][HC]   rectified hidden activation
+	float* w1  = a1 + (size_t)B * HC;      // [np][WS]
+	float* w2  = w1 + (size_t)np * WS;     // [HC]
+	float* out = w2 + HC;                  // [B]       output, then dout
+	float* red = out + B;                  // [256]
+
+	const size_t ldp = (size_t)np * a.I;
+	for (unsigned t = tid; t < B * np; t += nt) {
+		const unsigned i = t / np, u = t % np;
+		const size_t o = (size_t)i * ldp + (size_t)b * np + u;
+		float v = a.pooled[o];
+		if (a.mask && !a.mask[o]) v = 0.f;                 // maskout semantics: a dropped feature is exactly 0
+		pd[t] = v;
+	}
+	for (unsigned t = tid; t < np * HC; t += nt) w1[(t / HC) * WS + t % HC] = a.W1[(size_t)b * np * HC + t];
+	if (H) for (unsigned t = tid; t < H; t += nt) w2[t] = a.W2[(size_t)b * H + t];
+	__syncthreads();
+
+	// hidden (or output) layer: h1 = pd . W1 + b1
+	for (unsigned t = tid; t < B * HC; t += nt) {
+		const unsigned i = t / HC, c = t % HC;
+		float s = 0.f;
+		for (unsigned u = 0; u < np; ++u) s = fmaf(pd[i * np + u], w1[u * WS + c], s);
+		s = s + a.b1[(size_t)b * HC + c];
+		h1[t] = s;
+		a1[t] = s > 0.f ? s : 0.f;
+	}
+	__syncthreads();
+	for (unsigned i = tid; i < B; i += nt) {
+		float o;
+		if (H) {
+			float s = 0.f;
+			for (unsigned c = 0; c < H; ++c) s = fmaf(a1[i * H + c], w2[c], s);
+			o = s + a.b2[b];
+		} else o = h1[i];
+		out[i] = o;
+	}
+	__syncthreads();
+
+	// loss and dout = (Z - Y) / B   (loss.py:98-112; the logistic's own derivative is not applied, softmax.py:76-77)
+	const float inv = 1.f / (float)B;
+	float ls = 0.f;
+	for (unsigned i = tid; i < B; i += nt) {
+		const float y = a.Y[(size_t)i * a.I + b];
+		float z = out[i], l;
+		if (a.kind == 1) {
+			z = 1.f / (1.f + expf(-z));
+			l = logf(fmaxf(1e-15f, z)) * y + logf(fmaxf(1e-15f, 1.f - z)) * (1.f - y);
+		} else { const float d = z - y; l = d * d; }
+		ls += l;
+		out[i] = (z - y) * inv;
+	}
+	red[tid] = ls;
+	__syncthreads();
+	for (unsigned w = nt / 2; w > 0; w >>= 1) {
+		if (tid < w) red[tid] += red[tid + w];
+		__syncthreads();
+	}
+	if (tid == 0 && a.loss) a.loss[b] = (a.kind == 0 ? 0.5f : -1.f) * (red[0] * inv);
+
+	// second layer backward; h1 becomes the gradient of the hidden pre-activation
+	if (H) {
+		for (unsigned c = tid; c < H; c += nt) {
+			float s = 0.f;
+			for (unsigned i = 0; i < B; ++i) s = fmaf(a1[i * H + c], out[i], s);
+			a.dW2[(size_t)b * H + c] = s;
+		}
+		if (tid == nt - 1) {
+			float s = 0.f;
+			for (unsigned i = 0; i < B; ++i) s += out[i];
+			a.db2[b] = s;
+		}
+		for (unsigned t = tid; t < B * H; t += nt) {
+			const unsigned i = t / H, c = t % H;
+			h1[t] = a1[t] > 0.f ? out[i] * w2[c] : 0.f;
+		}
+	} else {
+		for (unsigned i = tid; i < B; i += nt) h1[i] = out[i];
+	}
+	__syncthreads();
+
+	// first layer backward
+	for (unsigned c = tid; c < HC; c += nt) {
+		float s = 0.f;
+		for (unsigned i = 0; i < B; ++i) s += h1[i * HC + c];
+		a.db1[(size_t)b * HC + c] = s;
+	}
+	for (unsigned t = tid; t < np * HC; t += nt) {
+		const unsigned u = t / HC, c = t % HC;
+		float s = 0.f;
+		for (unsigned i = 0; i < B; ++i) s = fmaf(pd[i * np + u], h1[i * HC + c], s);
+		a.dW1[(size_t)b * np * HC + t] = s;
+	}
+	for (unsigned t = tid; t < B * np; t += nt) {
+		const unsigned i = t / np, u = t % np;
+		const size_t o = (size_t)i * ldp + (size_t)b * np + u;
+		float s = 0.f;
+		for (unsigned c = 0; c < HC; ++c) s = fmaf(h1[i * HC + c], w1[u * WS + c], s);
+		if (a.mask && !a.mask[o]) s = 0.f;
+		a.dpooled[o] = s;
+	}
+}
+
+static size_t head_smem_bytes(unsigned B, unsigned np, unsigned H)
+{
+	unsigned HC = H ? H : 1u;
+	return ((size_t)B * np + 2 * (size_t)B * HC + (size_t)np * (HC + 1) + HC + B + 256) * sizeof(float);
+}
+
+}  // namespace db
+
+using namespace db;
+
+// Largest minibatch the fused head takes for the given widths (0: never fits).
+DB_EXPORT uint32_t db_head_max_batch(uint32_t npool, uint32_t hidden)
+{
+	unsigned B = 0;
+	while (head_smem_bytes(B + 64, npool, hidden) <= 200 * 1024 && B < 65536) B += 64;
+	return B;
+}
+
+DB_EXPORT void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_kind, uint32_t B,
+                             const float* pooled, const uint8_t* dropmask, const float* Y,
+                             const float* W1, const float* b1, const float* W2, const float* b2,
+                             float* loss, float* dpooled, float* dW1, float* db1, float* dW2, float* db2)
+{
+	DB_API_TRY
+	DB_REQUIRE(loss_kind == 0 || loss_kind == 1, "ValueError: loss kind must be 0 (mse) or 1 (nll)");
+	DB_REQUIRE(npool > 0, "ValueError: the head needs at least one pooled feature per model");
+	if (!nmodel || !B) return;
+	DB_REQUIRE(pooled && Y && W1 && b1 && dpooled && dW1 && db1, "ValueError: db_head_train got a NULL pointer");
+	DB_REQUIRE(!hidden || (W2 && b2 && dW2 && db2), "ValueError: a hidden layer needs W2, b2, dW2 and db2");
+	size_t smem = head_smem_bytes(B, npool, hidden);
+	DB_REQUIRE(smem <= 200 * 1024, "ValueError: minibatch of %u rows x %u features x %u hidden units exceeds the fused head's "
+	           "shared-memory tile (at most %u rows)", B, npool, hidden, db_head_max_batch(npool, hidden));
+	head_args a;
+	a.pooled = pooled; a.mask = dropmask; a.Y = Y; a.W1 = W1; a.b1 = b1; a.W2 = W2; a.b2 = b2;
+	a.loss = loss; a.dpooled = dpooled; a.dW1 = dW1; a.db1 = db1; a.dW2 = dW2; a.db2 = db2;
+	a.B = B; a.I = nmodel; a.npool = npool; a.H = hidden; a.kind = loss_kind;
+	DB_CUDA(cudaFuncSetAttribute(head_train_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	head_train_kernel<<<nmodel, 256, smem, state().stream>>>(a);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}

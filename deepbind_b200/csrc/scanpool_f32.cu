@@ -223,7 +223,8 @@ scanpool_bwd_kernel(const bwd_args a)
 	float* davg = dz + (size_t)TR * FB;                                 // [GMAX][FB] mean share per row
 	float* dmax = davg + GMAX * FB;                                     // [GMAX][FB]
 	unsigned* amax = reinterpret_cast<unsigned*>(dmax + GMAX * FB);     // [GMAX][FB] argmax row
-	uint8_t* xs = reinterpret_cast<uint8_t*>(amax + GMAX * FB);         // TR + m codes (0..5)
+	// per input row the weight each channel's gradient receives: one-hot, 1/4 each for N, 0 for a dropped base
+	float4* oh = reinterpret_cast<float4*>(amax + GMAX * FB);           // [TR + m]
 	__shared__ unsigned rg0[GMAX], rg1[GMAX];
 	__shared__ unsigned s_lo, s_hi;
 
@@ -268,7 +269,8 @@ scanpool_bwd_kernel(const bwd_args a)
 		__syncthreads();
 		for (unsigned t = threadIdx.x; t < TR + m; t += blockDim.x) {
 			unsigned i = t0 + t, x = i < a.npos ? a.X[i] : 254u;
-			xs[t] = (uint8_t)(x < 4u ? x : (x == 254u ? 5u : 4u));
+			const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
+			oh[t] = make_float4(x == 0u ? 1.f : q, x == 1u ? 1.f : q, x == 2u ? 1.f : q, x == 3u ? 1.f : q);
 		}
 		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
 			unsigned r = t / FB, fl = t % FB, row = t0 + r;
@@ -295,11 +297,13 @@ scanpool_bwd_kernel(const bwd_args a)
 				float c0 = a0[k], c1 = a1[k], c2 = a2[k], c3 = a3[k];
 				// Rows at or past n have no scan output, hence no filter gradient.
 				unsigned rows = min((unsigned)TR, a.n > t0 ? a.n - t0 : 0u);
+				// Branch-free: the channel weights are 0, 1/4 or 1, so each product is exact and
+				// the fused multiply-add equals the reference's add of dZ (or dZ/4).
+				#pragma unroll 4
 				for (unsigned r = 0; r < rows; ++r) {
-					float v = dz[r * FB + fl];
-					unsigned c = xs[r + j];
-					if (c == 0) c0 += v; else if (c == 1) c1 += v; else if (c == 2) c2 += v; else if (c == 3) c3 += v;
-					else if (c == 4) { float q = v * 0.25f; c0 += q; c1 += q; c2 += q; c3 += q; }
+					const float v = dz[r * FB + fl];
+					const float4 w = oh[r + j];
+					c0 = fmaf(v, w.x, c0); c1 = fmaf(v, w.y, c1); c2 = fmaf(v, w.z, c2); c3 = fmaf(v, w.w, c3);
 				}
 				a0[k] = c0; a1[k] = c1; a2[k] = c2; a3[k] = c3;
 			}
@@ -415,7 +419,7 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	DB_REQUIRE(m * a.FB <= 2 * threads, "ValueError: filter length %u is too long for the fused backward kernel", m);
 	unsigned ncta = divup(nregion, a.G);
 	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
-	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + TR + m + 16;
+	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + (size_t)(TR + m) * 16 + 16;
 	DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();

@@ -46,14 +46,49 @@ def scanpool(W, bias, X, R, ptype="max", relu=True, want_argmax=False, want_actm
     return pooled, argmax, actmask
 
 
-def scanpool_bprop(m, nf, X, R, ptype, dpooled, argmax, actmask):
-    """Returns (dW [4m, nf], dbias [nf]) of the fused stage."""
+def scanpool_bprop(m, nf, X, R, ptype, dpooled, argmax, actmask, dW_out=None, db_out=None):
+    """Returns (dW [4m, nf], dbias [nf]) of the fused stage; ``dW_out`` / ``db_out``
+    (contiguous f32) receive them in place, e.g. slices of a flat gradient vector."""
     _check(dpooled, torch.float32, "dpooled")
-    dW = torch.empty((4 * m, nf), dtype=torch.float32, device=dpooled.device)
-    db = torch.empty((nf,), dtype=torch.float32, device=dpooled.device)
+    dW = dW_out if dW_out is not None else torch.empty((4 * m, nf), dtype=torch.float32, device=dpooled.device)
+    db = db_out if db_out is not None else torch.empty((nf,), dtype=torch.float32, device=dpooled.device)
+    _check(dW, torch.float32, "dW_out"); _check(db, torch.float32, "db_out")
+    assert dW.numel() == 4 * m * nf and db.numel() == nf
     _dll().db_scanpool_bwd(m, nf, _ptr(X), X.numel(), _ptr(R), R.shape[0], PT[ptype], _ptr(dpooled),
                            _ptr(argmax), _ptr(actmask), _ptr(dW), _ptr(db))
     return dW, db
+
+
+def build_batch(seqs, padding, reverse_complement=False, device="cuda"):
+    """A minibatch of sequence strings -> (X uint8 [npos], R int32 [nrow, 2]) on the
+    device, laid out as kangaroo's ``_seqdata._pack`` does (data.py:274-334): the
+    characters are uploaded once and translated, padded and (optionally)
+    reverse-complemented by one kernel.  ``seqs`` may also be a pair
+    (text uint8 tensor, offsets int32 tensor [nseq+1]) already on the device."""
+    import numpy as np
+    if isinstance(seqs, tuple):
+        text, off = seqs
+        _check(text, torch.uint8, "text"); _check(off, torch.int32, "offsets")
+        nseq = off.numel() - 1
+        total = int(off[-1].item() - off[0].item()) if nseq > 0 else 0
+    else:
+        nseq = len(seqs)
+        raw = "".join(seqs).encode("latin-1")
+        total = len(raw)
+        lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=nseq)
+        off_h = np.zeros(nseq + 1, dtype=np.int64)
+        np.cumsum(lens, out=off_h[1:])
+        text = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device) if total else torch.empty(0, dtype=torch.uint8, device=device)
+        off = torch.from_numpy(off_h.astype(np.int32)).to(device)
+    dll = _dll()
+    rc = int(bool(reverse_complement))
+    nbytes = dll.db_batch_bytes(nseq, total, padding, rc)
+    if nbytes >= 2 ** 32:
+        raise ValueError("a minibatch is addressed with 32-bit positions; split it")
+    X = torch.empty(nbytes, dtype=torch.uint8, device=text.device)
+    R = torch.empty((nseq * (2 if rc else 1), 2), dtype=torch.int32, device=text.device)
+    dll.db_build_batch(_ptr(text), _ptr(off), nseq, padding, rc, _ptr(X), _ptr(R))
+    return X, R
 
 
 class TCWeights(object):

@@ -28,8 +28,9 @@ def _as_f32(t):
 
 
 class DeepBindNet(object):
-    def __init__(self, params, nmodel, pool="max", loss="nll", device=None):
+    def __init__(self, params, nmodel, pool="max", loss="nll", device=None, fused_head=True):
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
+        self.fused_head = fused_head      # False: run the head operator by operator, as the reference's graph does
         self.I = int(nmodel)
         self.pool = pool
         self.loss = loss
@@ -112,6 +113,24 @@ class DeepBindNet(object):
         dll = _lib.load()
         pooled, amax, actmask = fused.scanpool(self.view("Wscan"), self.view("bscan").view(-1), X, R, self.pool,
                                                relu=True, want_argmax=True, want_actmask=True)
+        B = pooled.shape[0]
+        npool = pooled.shape[1] // I
+        if self.fused_head and B <= dll.db_head_max_batch(npool, self.hidden):
+            # dense head, loss and their backward pass in one launch; gradients land in dP
+            lossv = torch.empty(I, dtype=torch.float32, device=self.dev)
+            dpd = torch.empty_like(pooled)
+            has2 = bool(self.hidden)
+            dll.db_head_train(I, npool, self.hidden, 1 if self.loss == "nll" else 0, B, pooled.data_ptr(),
+                              dropmask.data_ptr() if dropmask is not None else None, Y.data_ptr(),
+                              self.view("W1").data_ptr(), self.view("b1").data_ptr(),
+                              self.view("W2").data_ptr() if has2 else None, self.view("b2").data_ptr() if has2 else None,
+                              lossv.data_ptr(), dpd.data_ptr(), self.view("W1", "dP").data_ptr(),
+                              self.view("b1", "dP").data_ptr(),
+                              self.view("W2", "dP").data_ptr() if has2 else None,
+                              self.view("b2", "dP").data_ptr() if has2 else None)
+            dW, db = fused.scanpool_bprop(self.m, self.nf, X, R, self.pool, dpd, amax, actmask,
+                                          dW_out=self.view("Wscan", "dP"), db_out=self.view("bscan", "dP").view(-1))
+            return lossv
         if dropmask is not None:
             pd = pooled.clone()
             dsm.maskout(sarray(dropmask, np.bool_), _as_f32(pd))

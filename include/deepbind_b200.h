@@ -139,6 +139,35 @@ void db_logistic(float* Z, const float* X, size_t n);
 void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, const uint8_t* Zmask,
              uint32_t nrow, uint32_t ncol, float* loss_out, float* dZ);
 
+/* The dense head of one training step in one launch (no counterpart as one call;
+ * replaces dropout -> full -> bias -> rectify -> full -> bias -> logistic -> loss and
+ * their backward passes: elemwise.py:128-150,171,74-78, full.py:78-89, softmax.py:50-61,
+ * loss.py:52-112, deepity_smat.py:169-204).  One CTA per model holds that model's
+ * minibatch in shared memory.  pooled/dpooled/dropmask [B, npool*nmodel]; Y [B, nmodel];
+ * hidden = 0: linear head W1 [(npool*nmodel),1], b1 [nmodel]; hidden = H: W1
+ * [(npool*nmodel),H], b1 [H*nmodel], W2 [(H*nmodel),1], b2 [nmodel].  loss_kind 0 = mse,
+ * 1 = nll on logistic outputs.  Writes loss [nmodel], dpooled and the four parameter
+ * gradients (overwritten).  B must not exceed db_head_max_batch(npool, hidden). */
+uint32_t db_head_max_batch(uint32_t npool, uint32_t hidden);
+void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_kind, uint32_t B,
+                   const float* pooled, const uint8_t* dropmask, const float* Y,
+                   const float* W1, const float* b1, const float* W2, const float* b2,
+                   float* loss, float* dpooled, float* dW1, float* db1, float* dW2, float* db2);
+
+/* ---- minibatch assembly on the device (replaces the host-side string joins of
+ * kangaroo/data.py:309-334 with util.py:43-74 acgt2ord / revcomp, and the strand
+ * doubling of data.py:274-283) -----------------------------------------------
+ * text: the sequences' characters back to back; offsets [nseq+1]: where each starts
+ * (a prefix sum of the lengths; offsets[0] need not be 0).  Writes
+ *     X = pad | s0 | pad | s1 | ... | pad      (pad bytes of 255; A,C,G,T/U -> 0..3,
+ *                                               either case; anything else -> 255)
+ * of db_batch_bytes(...) bytes and regions [nrow,2] = (start of the row's leading
+ * pad, end of its sequence).  reverse_complement != 0 doubles the rows: row 2b is
+ * sequence b, row 2b+1 its reverse complement.  All pointers are device pointers. */
+size_t db_batch_bytes(uint32_t nseq, size_t total_len, uint32_t pad, int reverse_complement);
+void db_build_batch(const uint8_t* text, const uint32_t* offsets, uint32_t nseq, uint32_t pad,
+                    int reverse_complement, uint8_t* X, uint32_t* regions);
+
 /* ---- fused hot path (no counterpart as one call; replaces the chain
  * api_corr1ord -> bias -> rectify -> api_poolrgn of corr1ord.py:97-102,
  * elemwise.py:171,74-78, poolrgn.py:59,153) --------------------------------
