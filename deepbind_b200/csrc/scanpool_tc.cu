@@ -41,6 +41,8 @@ namespace db {
 
 static constexpr int TC_STAGE_TILES = 8;    // tiles of 256 flat rows per E stage
 static constexpr int TC_ECHUNKS = TC_STAGE_TILES * 256 + 128;   // 16-byte chunks per stage incl. the K reach of the last row
+static constexpr int TC_EPI_SETS = 3;       // epilogue warps per TMEM lane quarter; region g is reduced by set g % TC_EPI_SETS
+static constexpr int TC_THREADS = 128 + 128 * TC_EPI_SETS;
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // clock cycles (about 0.1 s)
 
 struct tc_args {
@@ -152,9 +154,9 @@ __device__ __forceinline__ unsigned long long base_pattern(unsigned x)
 
 #define COMMA ,
 // Narrow TMEM loads for the tail of a region segment (32 lanes x N columns, one
-// register per column).
+// register per column), written into a sub-range of a 32-register buffer.
 #define DB_TMEM_LD_SMALL(NAME, N, REGS_OUT, REGS_FMT)                                              \
-__device__ __forceinline__ void NAME(uint32_t taddr, float (&v)[N])                                \
+__device__ __forceinline__ void NAME(uint32_t taddr, float* v)                                     \
 {                                                                                                  \
 	uint32_t* r = reinterpret_cast<uint32_t*>(v);                                                  \
 	asm volatile("tcgen05.ld.sync.aligned.32x32b.x" #N ".b32 {" REGS_FMT "}, [%" #N "];"            \
@@ -170,6 +172,17 @@ DB_TMEM_LD_SMALL(tmem_ld8, 8,
 DB_TMEM_LD_SMALL(tmem_ld4, 4, "=r"(r[0]) COMMA "=r"(r[1]) COMMA "=r"(r[2]) COMMA "=r"(r[3]), "%0, %1, %2, %3")
 DB_TMEM_LD_SMALL(tmem_ld2, 2, "=r"(r[0]) COMMA "=r"(r[1]), "%0, %1")
 DB_TMEM_LD_SMALL(tmem_ld1, 1, "=r"(r[0]), "%0")
+
+// Requests the next min(n, 32) columns starting at `ta` (no wait): see pool_state::add_piece.
+__device__ __forceinline__ void load_piece(uint32_t ta, unsigned n, float (&v)[32])
+{
+	if (n >= 32) { tmem_ld32(ta, v); return; }
+	if (n & 16) { tmem_ld16(ta, v); ta += 16; }
+	if (n & 8)  { tmem_ld8(ta, v + 16); ta += 8; }
+	if (n & 4)  { tmem_ld4(ta, v + 24); ta += 4; }
+	if (n & 2)  { tmem_ld2(ta, v + 28); ta += 2; }
+	if (n & 1)  { tmem_ld1(ta, v + 30); }
+}
 
 // Running pooling state of one filter over the rows of one region.  Four
 // independent chains keep a lone warp issuing; there are no per-column tests:
@@ -207,7 +220,7 @@ struct pool_state {
 		sm1 = 0.f;
 	}
 	template <bool WANT_MAX, bool WANT_SUM, bool RELU, int N>
-	__device__ __forceinline__ void add(const float (&v)[N], float nb)
+	__device__ __forceinline__ void add(const float* v, float nb)
 	{
 		if (N >= 8) {
 			#pragma unroll
@@ -226,6 +239,18 @@ struct pool_state {
 				if (WANT_SUM) sm1 += RELU ? fmaxf(v[i], nb) : v[i];
 			}
 		}
+	}
+	// A piece of n <= 32 columns in a 32-register buffer: a full piece fills it; a
+	// shorter one keeps its 16/8/4/2/1-column parts at fixed offsets 0/16/24/28/30.
+	template <bool WANT_MAX, bool WANT_SUM, bool RELU>
+	__device__ __forceinline__ void add_piece(const float (&v)[32], unsigned n, float nb)
+	{
+		if (n >= 32) { add<WANT_MAX, WANT_SUM, RELU, 32>(v, nb); return; }
+		if (n & 16) add<WANT_MAX, WANT_SUM, RELU, 16>(v, nb);
+		if (n & 8)  add<WANT_MAX, WANT_SUM, RELU, 8>(v + 16, nb);
+		if (n & 4)  add<WANT_MAX, WANT_SUM, RELU, 4>(v + 24, nb);
+		if (n & 2)  add<WANT_MAX, WANT_SUM, RELU, 2>(v + 28, nb);
+		if (n & 1)  add<WANT_MAX, WANT_SUM, RELU, 1>(v + 30, nb);
 	}
 	// `cnt` rows whose scan output is zero
 	template <bool WANT_MAX, bool WANT_SUM, bool RELU>
@@ -250,7 +275,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
                                             unsigned row_lo, unsigned row_hi, unsigned warp, unsigned lane)
 {
 	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
-	const unsigned set = (warp - 4) >> 2;               // two warps share a quarter: one owns the even regions, one the odd
+	const unsigned set = (warp - 4) >> 2;               // the warps of a quarter take the regions in turn
 	const unsigned f = tile * 128 + q4 * 32 + lane;     // this thread's filter = its TMEM lane
 	const float b = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
 	const float nb = -b;
@@ -266,42 +291,54 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	}
 	pool_state ps;
 	ps.reset();
-	unsigned g = g_first;
-	unsigned r0 = a.R[2 * g], r1 = max(a.R[2 * g + 1], r0);
-	unsigned nr0 = 0, nr1 = 0;                          // the next region's bounds, loaded one region ahead
-	if (g + 1 < g_last) { nr0 = a.R[2 * (g + 1)]; nr1 = a.R[2 * (g + 1) + 1]; }
-	bool own = set == 0;
-
-	// Writes region g's outputs (if this warp owns it) and moves to the next region.
-	auto finish_region = [&]() -> bool {
-		if (own) {
-			const unsigned P = r1 - r0;
-			float pmax = ps.max_all() + b;             // max_p relu(z_p + b) = relu(max_p z_p + b)
-			if (RELU) pmax = fmaxf(pmax, 0.f);
-			const float psum = ps.sum_all() + (float)P * b;      // sum_p max(z_p, -b) + P*b
-			const float second = a.ptype == DB_PT_SUM ? psum : psum / (float)P;
-			if (a.pooled && f < a.nf) {
-				const size_t o = (size_t)g * a.nf + f;
-				if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
-				else a.pooled[o] = WANT_MAX ? pmax : second;
-			}
-			if (a.scores) {
-				float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
-				part += __shfl_xor_sync(0xffffffffu, part, 8);
-				part += __shfl_xor_sync(0xffffffffu, part, 4);
-				part += __shfl_xor_sync(0xffffffffu, part, 2);
-				part += __shfl_xor_sync(0xffffffffu, part, 1);
-				if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
-			}
-			ps.reset();
+	// This warp reduces the regions g_first + set, + TC_EPI_SETS, ... and never looks at the others.
+	unsigned g = g_first + set;
+	unsigned r0 = 0, r1 = 0;                            // bounds of the region being reduced
+	unsigned nr0 = 0, nr1 = 0, nprev = 0;               // bounds of this warp's next region and the end of the one before it, loaded ahead
+	bool ok = true;
+	if (g < g_last) {
+		r0 = a.R[2 * g]; r1 = max(a.R[2 * g + 1], r0);
+		if (g > g_first && r0 < a.R[2 * g - 1]) {      // regions must ascend without overlap
+			if (lane == 0) { *abort_flag = 1; atomicExch(a.status, 3); }
+			ok = false;
 		}
-		++g;
-		own = !own;
+	}
+	auto fetch_next = [&]() {
+		const unsigned h = g + TC_EPI_SETS;
+		if (h < g_last) {
+			const uint2 r = reinterpret_cast<const uint2*>(a.R)[h];      // regions are (start, end) pairs: cudaMalloc alignment
+			nr0 = r.x; nr1 = r.y; nprev = a.R[2 * h - 1];
+		}
+	};
+	fetch_next();
+
+	// Writes region g's outputs and moves to this warp's next region.
+	auto finish_region = [&]() -> bool {
+		const unsigned P = r1 - r0;
+		float pmax = ps.max_all() + b;                 // max_p relu(z_p + b) = relu(max_p z_p + b)
+		if (RELU) pmax = fmaxf(pmax, 0.f);
+		const float psum = ps.sum_all() + (float)P * b;          // sum_p max(z_p, -b) + P*b
+		const float second = a.ptype == DB_PT_SUM ? psum : __fdividef(psum, (float)P);
+		if (a.pooled && f < a.nf) {
+			const size_t o = (size_t)g * a.nf + f;
+			if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
+			else a.pooled[o] = WANT_MAX ? pmax : second;
+		}
+		if (a.scores) {
+			float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
+			part += __shfl_xor_sync(0xffffffffu, part, 8);
+			part += __shfl_xor_sync(0xffffffffu, part, 4);
+			part += __shfl_xor_sync(0xffffffffu, part, 2);
+			part += __shfl_xor_sync(0xffffffffu, part, 1);
+			if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
+		}
+		ps.reset();
+		g += TC_EPI_SETS;
 		if (g >= g_last) return true;
-		const unsigned prev_end = r1;
 		r0 = nr0; r1 = max(nr1, nr0);
-		if (g + 1 < g_last) { nr0 = a.R[2 * (g + 1)]; nr1 = a.R[2 * (g + 1) + 1]; }
-		if (r0 < prev_end) {                           // regions must ascend without overlap
+		const bool bad = r0 < nprev;                   // regions must ascend without overlap
+		fetch_next();
+		if (bad) {
 			if (lane == 0) { *abort_flag = 1; atomicExch(a.status, 3); }
 			return false;
 		}
@@ -309,54 +346,48 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	};
 
 	const unsigned ntile = (row_hi - row_lo + 255u) / 256u;
-	bool ok = true;
 	for (unsigned t = 0; ok && t < ntile; ++t) {       // every tile is consumed, so the issuer never waits on us in vain
 		const unsigned slot = t & 1;
-		// lane 0 waits (bounded); the warp stays converged for the aligned TMEM loads
-		unsigned okv = 0;
-		if (lane == 0) okv = mbar_wait(&t_full[slot], (t >> 1) & 1, abort_flag) ? 1u : 0u;
-		ok = __shfl_sync(0xffffffffu, okv, 0) != 0;
-		if (!ok) break;
-		mbar_try_wait(&t_full[slot], (t >> 1) & 1);    // completed: every lane observes the phase
+		// Usually the tile is ready: every lane tests the barrier once.  Otherwise lane 0
+		// waits (bounded) and the warp stays converged for the aligned TMEM loads.
+		if (!__all_sync(0xffffffffu, mbar_try_wait(&t_full[slot], (t >> 1) & 1))) {
+			unsigned okv = 0;
+			if (lane == 0) okv = mbar_wait(&t_full[slot], (t >> 1) & 1, abort_flag) ? 1u : 0u;
+			ok = __shfl_sync(0xffffffffu, okv, 0) != 0;
+			if (!ok) break;
+			mbar_try_wait(&t_full[slot], (t >> 1) & 1);    // completed: every lane observes the phase
+		}
 		tc_fence_after();
 		const unsigned tile_lo = row_lo + t * 256u, tile_hi = min(tile_lo + 256u, row_hi);
 		const uint32_t taddr = tmem_base + ((q4 * 32u) << 16) + slot * 256u;
-		unsigned pos = tile_lo;
-		while (ok && pos < tile_hi && g < g_last) {
-			if (pos >= r1) { ok = finish_region(); continue; }
-			if (pos < r0) { pos = min(r0, tile_hi); continue; }        // rows between regions belong to nobody
-			const unsigned end = min(r1, tile_hi);
-			if (own) {
+		while (ok && g < g_last && r0 < tile_hi) {
+			const unsigned pos = max(r0, tile_lo), end = min(r1, tile_hi);
+			if (end > pos) {
 				// rows at or past n have no scan output (kangaroo_smat.cpp:105): they read as zero
 				const unsigned live_end = min(end, max(pos, a.n));
 				uint32_t ta = taddr + (pos - tile_lo);
 				unsigned left = live_end - pos;
+				// 64 columns per TMEM round trip (40-60 clocks, hidden by the other warps of
+				// the scheduler), then the remaining 0..63 columns with one more wait.
 				float va[32], vb[32];
-				while (left >= 64) {                 // two groups per TMEM round trip
+				while (left >= 64) {
 					tmem_ld32(ta, va); tmem_ld32(ta + 32, vb);
 					tmem_ld_wait();
 					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
 					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(vb, nb);
 					ta += 64; left -= 64;
 				}
-				// the remaining 0..63 columns in pieces of 32, 16, 8, 4, 2, 1: all requested, then one wait
-				float t16[16], t8[8], t4[4], t2[2], t1[1];
-				if (left & 32) { tmem_ld32(ta, va); ta += 32; }
-				if (left & 16) { tmem_ld16(ta, t16); ta += 16; }
-				if (left & 8)  { tmem_ld8(ta, t8); ta += 8; }
-				if (left & 4)  { tmem_ld4(ta, t4); ta += 4; }
-				if (left & 2)  { tmem_ld2(ta, t2); ta += 2; }
-				if (left & 1)  { tmem_ld1(ta, t1); }
-				tmem_ld_wait();
-				if (left & 32) ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
-				if (left & 16) ps.add<WANT_MAX, WANT_SUM, RELU, 16>(t16, nb);
-				if (left & 8)  ps.add<WANT_MAX, WANT_SUM, RELU, 8>(t8, nb);
-				if (left & 4)  ps.add<WANT_MAX, WANT_SUM, RELU, 4>(t4, nb);
-				if (left & 2)  ps.add<WANT_MAX, WANT_SUM, RELU, 2>(t2, nb);
-				if (left & 1)  ps.add<WANT_MAX, WANT_SUM, RELU, 1>(t1, nb);
+				if (left) {
+					if (left & 32) { tmem_ld32(ta, va); ta += 32; }
+					load_piece(ta, left & 31, vb);
+					tmem_ld_wait();
+					if (left & 32) ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
+					ps.add_piece<WANT_MAX, WANT_SUM, RELU>(vb, left & 31, nb);
+				}
 				if (live_end < end) ps.add_zero_rows<WANT_MAX, WANT_SUM, RELU>(end - live_end, nb);
 			}
-			pos = end;
+			if (r1 > tile_hi) break;                       // the region continues in the next tile
+			ok = finish_region();
 		}
 		tc_fence_before();
 		__syncwarp();
@@ -368,7 +399,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 
 #undef COMMA
 
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 scanpool_tc_kernel(const tc_args a)
 {
 	extern __shared__ __align__(128) unsigned char smem[];
@@ -404,7 +435,7 @@ scanpool_tc_kernel(const tc_args a)
 		mbar_init(&bar_a, 1);
 		for (int i = 0; i < 2; ++i) {
 			mbar_init(&e_full[i], 3); mbar_init(&e_empty[i], 1);
-			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 8);
+			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 4 * TC_EPI_SETS);
 		}
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
@@ -580,6 +611,7 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int nspli
 	if (nregion == 0) return;
 	DB_REQUIRE(Wt && X && regions, "ValueError: db_scanpool_tc got a NULL pointer");
 	DB_REQUIRE(((uintptr_t)Wt & 15) == 0, "ValueError: prepared weights must be 16-byte aligned");
+	DB_REQUIRE(((uintptr_t)regions & 7) == 0, "ValueError: the region table must be 8-byte aligned");
 	unsigned KC, ntile;
 	tc_shape(m, nf, KC, ntile);
 	tc_args a;
@@ -603,7 +635,7 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int nspli
 	if (smem < 120 * 1024) smem = 120 * 1024;       // one CTA per SM: each CTA takes all 512 TMEM columns
 	DB_REQUIRE(smem <= 220 * 1024 && 2 * KC + 16 <= 128, "ValueError: filter length %u is too long for the tensor-core kernel", m);
 	DB_CUDA(cudaFuncSetAttribute(scanpool_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-	scanpool_tc_kernel<<<grid, 384, smem, state().stream>>>(a);
+	scanpool_tc_kernel<<<grid, TC_THREADS, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }
