@@ -41,8 +41,8 @@ def parse():
     ap.add_argument("--nseq", type=int, default=1000000, help="sequences per GPU")
     ap.add_argument("--nmodel", type=int, default=512)
     ap.add_argument("--chunk", type=int, default=16384, help="sequences per launch of the FP32 variant")
-    ap.add_argument("--variant", default="bf16x3", choices=["bf16x3", "bf16x2", "bf16", "f32"],
-                    help="arithmetic of the scan: bf16 pieces on tcgen05 (x3 = fp32-grade) or FP32 lookup-add")
+    ap.add_argument("--variant", default="f16x2", choices=["f16x2", "bf16x3", "bf16x2", "f16", "bf16", "f32"],
+                    help="arithmetic of the scan: 16-bit weight pieces on tcgen05 (f16x2, bf16x3 = fp32-grade) or FP32 lookup-add")
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the short runs of the other benchmark configurations")
@@ -143,9 +143,11 @@ class ClockSampler(object):
 
 # ------------------------------------------------------------------ GPU arm
 VARIANTS = {
-    # name: (nsplit or None for the FP32 lookup-add kernel, dtype string, stated tolerance)
+    # name: (16-bit pieces per weight, or None for the FP32 lookup-add kernel; dtype string; stated tolerance)
+    "f16x2":  (2, "f16x2 (two f16 pieces per prescaled weight on tcgen05, fp32 accumulate; <=3e-6 of the fp32 reference)", 3e-6),
     "bf16x3": (3, "bf16x3 (three bf16 pieces per weight on tcgen05, fp32 accumulate; <=1e-5 of the fp32 reference)", 1e-5),
     "bf16x2": (2, "bf16x2 (two bf16 pieces per weight, fp32 accumulate; <=1e-5)", 1e-5),
+    "f16":    (1, "f16 (prescaled weights, fp32 accumulate; <=5e-4)", 5e-4),
     "bf16":   (1, "bf16 (fp32 accumulate; <=2e-3)", 2e-3),
     "f32":    (None, "f32 (lookup-add, bit-exact pooling)", 0.0),
 }
@@ -289,7 +291,7 @@ def main():
     gathered = torch.empty((nseq * world, I), dtype=torch.float32, device=dev) if world > 1 else None
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     if nsplit:
-        net.prepare_tc(nsplit)
+        net.prepare_tc(args.variant)
 
     def barrier():
         if world > 1:
@@ -358,11 +360,11 @@ def main():
         peak = peaks.get("bf16_tflops_sustained") or 1400.0
         src = "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS bf16 GEMM run back to back under the power cap)" \
             if "bf16_tflops_sustained" in peaks else "fallback 1.4 PFLOP/s sustained"
-        roofline = {"bound": "tensor", "kernel": "scanpool_tc_kernel (tcgen05 bf16, %d piece(s) per weight)" % nsplit,
+        roofline = {"bound": "tensor", "kernel": "scanpool_tc_kernel (tcgen05 kind::f16, %s: %d piece(s) per weight)" % (args.variant, nsplit),
                     "achieved": exec_flop / (kernel_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
                     "frac": exec_flop / (kernel_ms * 1e-3) / 1e12 / peak, "peak_source": src,
                     "flops_counted": "executed tensor flops = %d x dense-equivalent 2*K*rows*filters (K=96); the pieces are what "
-                                     "fp32-grade results cost on bf16 tensor cores" % nsplit,
+                                     "fp32-grade results cost on 16-bit tensor cores (f16 and bf16 run at the same rate)" % nsplit,
                     "dense_equiv_tflops": dense_flop / (kernel_ms * 1e-3) / 1e12,
                     "burst_peak": peaks.get("bf16_tflops"), "traffic": None, "ms_per_launch": kernel_ms,
                     "hbm_gbs_algorithmic": (nseq * ((L + M - 1) + I * 4)) / (kernel_ms * 1e-3) / 1e9}

@@ -36,6 +36,8 @@
 // a status word, releases its tensor memory and returns.
 #include "db_common.cuh"
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstring>
 
 namespace db {
 
@@ -51,6 +53,8 @@ struct tc_args {
 	float* pooled; float* scores; int* status;
 	unsigned npos, n, nregion, nf, KC, nsplit, seqs_per_cta, nmodel;
 	int ptype, relu;
+	unsigned f16;                   // operand type of both MMA inputs: 0 = bf16, 1 = f16 (weights prescaled by a power of two)
+	const uint32_t* maxabs;         // f16 only: bit pattern of max |W|, kept behind the prepared tiles
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -137,18 +141,37 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, unsigned lbo, unsig
 	return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
 	       ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
-// Instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N given.
-__device__ __forceinline__ uint32_t instr_desc(unsigned N)
+// Instruction descriptor: D = F32, A = B = BF16 (format 1) or F16 (format 0), both
+// K-major, M = 128, N given.
+__device__ __forceinline__ uint32_t instr_desc(unsigned N, unsigned f16)
 {
-	return (1u << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((128u >> 4) << 24);
+	const unsigned fmt = f16 ? 0u : 1u;
+	return (1u << 4) | (fmt << 7) | (fmt << 10) | ((N >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-// One-hot (or 1/4, or zero) pattern of a base as four bf16 in 64 bits, channel c at bits [16c, 16c+16).
-__device__ __forceinline__ unsigned long long base_pattern(unsigned x)
+// f16 operands: the weights are multiplied by the power of two that brings the
+// largest magnitude into [2^13, 2^14) before they are split, so that the second
+// piece stays a normal f16 number; the epilogue pools in the scaled domain (bias
+// scaled alike) and multiplies the pooled values by the inverse.  Exact: powers of two.
+__host__ __device__ __forceinline__ float tc_weight_scale(uint32_t maxabs_bits)
 {
-	if (x < 4u) return 0x3F80ull << (16u * x);        // bf16(1.0)
+	int e = (int)((maxabs_bits >> 23) & 0xffu) - 127;          // floor(log2(max |W|))
+	if ((maxabs_bits & 0x7fffffffu) == 0u || e < -60 || e > 60) return 1.f;
+	const uint32_t bits = (uint32_t)(13 - e + 127) << 23;
+#ifdef __CUDA_ARCH__
+	return __uint_as_float(bits);
+#else
+	float f; memcpy(&f, &bits, 4); return f;
+#endif
+}
+
+// One-hot (or 1/4, or zero) pattern of a base as four 16-bit floats in 64 bits, channel c at
+// bits [16c, 16c+16).  1.0 and 0.25 are 0x3F80 / 0x3E80 in bf16 and 0x3C00 / 0x3400 in f16.
+__device__ __forceinline__ unsigned long long base_pattern(unsigned x, unsigned f16)
+{
+	if (x < 4u) return (f16 ? 0x3C00ull : 0x3F80ull) << (16u * x);
 	if (x == 254u) return 0ull;                        // dropped input
-	return 0x3E803E803E803E80ull;                      // bf16(0.25) in every channel
+	return f16 ? 0x3400340034003400ull : 0x3E803E803E803E80ull;
 }
 
 
@@ -277,7 +300,8 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
 	const unsigned set = (warp - 4) >> 2;               // the warps of a quarter take the regions in turn
 	const unsigned f = tile * 128 + q4 * 32 + lane;     // this thread's filter = its TMEM lane
-	const float b = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
+	const float wscale = a.f16 ? tc_weight_scale(*a.maxabs) : 1.f, inv_wscale = 1.f / wscale;    // powers of two
+	const float b = ((a.bias && f < a.nf) ? a.bias[f] : 0.f) * wscale;
 	const float nb = -b;
 	// linear head of the model this filter belongs to (16 filters per model)
 	float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
@@ -316,8 +340,8 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	auto finish_region = [&]() -> bool {
 		const unsigned P = r1 - r0;
 		float pmax = ps.max_all() + b;                 // max_p relu(z_p + b) = relu(max_p z_p + b)
-		if (RELU) pmax = fmaxf(pmax, 0.f);
-		const float psum = ps.sum_all() + (float)P * b;          // sum_p max(z_p, -b) + P*b
+		pmax = (RELU ? fmaxf(pmax, 0.f) : pmax) * inv_wscale;
+		const float psum = (ps.sum_all() + (float)P * b) * inv_wscale;        // sum_p max(z_p, -b) + P*b
 		const float second = a.ptype == DB_PT_SUM ? psum : __fdividef(psum, (float)P);
 		if (a.pooled && f < a.nf) {
 			const size_t o = (size_t)g * a.nf + f;
@@ -465,7 +489,7 @@ scanpool_tc_kernel(const tc_args a)
 				if (!ok) break;
 				tc_fence_after();
 				const unsigned ncols = min(256u, row_hi - (row_lo + t * 256u)), N = (ncols + 15u) & ~15u;
-				const uint32_t idesc = instr_desc(N);
+				const uint32_t idesc = instr_desc(N, a.f16);
 				const uint32_t d = tmem_base + slot * 256u;
 				const uint32_t b0 = e_addr + st * (TC_ECHUNKS * 16) + tt * (256 * 16);
 				// Descriptors differ only in the start-address field of their low word:
@@ -512,11 +536,11 @@ scanpool_tc_kernel(const tc_args a)
 				uint32_t win[5];
 				#pragma unroll
 				for (int k = 0; k < 5; ++k) win[k] = __funnelshift_r(w[k], w[k + 1], sh);
-				unsigned long long prev = base_pattern(i0 < a.npos ? (win[0] & 0xffu) : 254u);
+				unsigned long long prev = base_pattern(i0 < a.npos ? (win[0] & 0xffu) : 254u, a.f16);
 				#pragma unroll
 				for (int c = 0; c < 16; ++c) {
 					const unsigned x1 = (i0 + c + 1 < a.npos) ? ((win[(c + 1) >> 2] >> (8 * ((c + 1) & 3))) & 0xffu) : 254u;
-					const unsigned long long p1 = base_pattern(x1);
+					const unsigned long long p1 = base_pattern(x1, a.f16);
 					E[q + c] = make_uint4((unsigned)prev, (unsigned)(prev >> 32), (unsigned)p1, (unsigned)(p1 >> 32));
 					prev = p1;
 				}
@@ -540,20 +564,34 @@ scanpool_tc_kernel(const tc_args a)
 }
 
 
-// Prepared weights: for each 128-filter tile, `nsplit` K-major bf16 operand tiles
-// in the shared-memory layout [split][K chunk][filter][8], zero padded.
+// Prepared weights: for each 128-filter tile, `nsplit` K-major 16-bit operand tiles
+// in the shared-memory layout [split][K chunk][filter][8], zero padded; behind the
+// tiles, 16 bytes whose first word is the bit pattern of max |W| (f16 modes).
+__global__ void tc_maxabs_kernel(const float* __restrict__ W, size_t count, uint32_t* __restrict__ out)
+{
+	uint32_t mx = 0;
+	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+		const float w = fabsf(W[i]);
+		if (w <= 3.4e38f) mx = max(mx, __float_as_uint(w));        // non-negative floats order like their bit patterns
+	}
+	mx = __reduce_max_sync(0xffffffffu, mx);
+	if ((threadIdx.x & 31) == 0 && mx) atomicMax(out, mx);
+}
+
 __global__ void tc_prepare_kernel(const float* __restrict__ W, unsigned m, unsigned nf, unsigned KC, unsigned nsplit,
-                                  unsigned ntile, __nv_bfloat16* __restrict__ out)
+                                  unsigned f16, unsigned ntile, uint16_t* __restrict__ out, const uint32_t* __restrict__ maxabs)
 {
 	const size_t total = (size_t)ntile * KC * 128 * 8;
+	const float scale = f16 ? tc_weight_scale(*maxabs) : 1.f;
 	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
 		const unsigned e = i % 8, fl = (i / 8) % 128, kc = (i / 1024) % KC, tile = (unsigned)(i / ((size_t)1024 * KC));
 		const unsigned k = kc * 8 + e, f = tile * 128 + fl;
-		float w = (k < 4 * m && f < nf) ? W[(size_t)k * nf + f] : 0.f;
+		float w = ((k < 4 * m && f < nf) ? W[(size_t)k * nf + f] : 0.f) * scale;
 		for (unsigned s = 0; s < nsplit; ++s) {
-			__nv_bfloat16 h = __float2bfloat16_rn(w);
-			out[(((size_t)tile * nsplit + s) * KC + kc) * 1024 + fl * 8 + e] = h;
-			w -= __bfloat162float(h);
+			uint16_t bits;
+			if (f16) { const __half h = __float2half_rn(w); bits = __half_as_ushort(h); w -= __half2float(h); }
+			else { const __nv_bfloat16 h = __float2bfloat16_rn(w); bits = __bfloat16_as_ushort(h); w -= __bfloat162float(h); }
+			out[(((size_t)tile * nsplit + s) * KC + kc) * 1024 + fl * 8 + e] = bits;
 		}
 	}
 }
@@ -570,38 +608,55 @@ static void tc_shape(uint32_t m, uint32_t nf, unsigned& KC, unsigned& ntile)
 	ntile = (nf + 127u) / 128u;
 }
 
-DB_EXPORT size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int nsplit)
+// precision -> (pieces per weight, f16 operands?)
+static void tc_mode(int precision, unsigned& nsplit, unsigned& f16)
+{
+	DB_REQUIRE(precision >= DB_TC_BF16 && precision <= DB_TC_F16,
+	           "ValueError: precision must be 1 (bf16), 2 (bf16x2), 3 (bf16x3), 4 (f16x2) or 5 (f16)");
+	f16 = precision >= DB_TC_F16X2;
+	nsplit = precision == DB_TC_F16X2 ? 2u : precision == DB_TC_F16 ? 1u : (unsigned)precision;
+}
+
+DB_EXPORT size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int precision)
 {
 	DB_API_TRY_NODEV
-	DB_REQUIRE(nsplit >= 1 && nsplit <= 3, "ValueError: nsplit must be 1, 2 or 3");
-	unsigned KC, ntile;
+	unsigned KC, ntile, nsplit, f16;
+	tc_mode(precision, nsplit, f16);
 	tc_shape(m, nf, KC, ntile);
-	return (size_t)ntile * nsplit * KC * 2048;
+	return (size_t)ntile * nsplit * KC * 2048 + 16;
 	DB_API_CATCH_RETURN(0)
 }
 
-DB_EXPORT void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int nsplit, void* out)
+DB_EXPORT void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int precision, void* out)
 {
 	DB_API_TRY
-	DB_REQUIRE(nsplit >= 1 && nsplit <= 3, "ValueError: nsplit must be 1, 2 or 3");
+	unsigned KC, ntile, nsplit, f16;
+	tc_mode(precision, nsplit, f16);
 	DB_REQUIRE(W && out, "ValueError: db_tc_prepare got a NULL pointer");
 	DB_REQUIRE(((uintptr_t)out & 15) == 0, "ValueError: prepared-weight buffer must be 16-byte aligned");
-	unsigned KC, ntile;
 	tc_shape(m, nf, KC, ntile);
+	uint32_t* trailer = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(out) + (size_t)ntile * nsplit * KC * 2048);
+	DB_CUDA(cudaMemsetAsync(trailer, 0, 16, state().stream));
+	if (f16) {
+		size_t count = (size_t)4 * m * nf;
+		tc_maxabs_kernel<<<elemwise_grid(count), 256, 0, state().stream>>>(W, count, trailer);
+		DB_LAUNCH_CHECK();
+	}
 	size_t total = (size_t)ntile * KC * 1024;
-	tc_prepare_kernel<<<elemwise_grid(total), 256, 0, state().stream>>>(W, m, nf, KC, (unsigned)nsplit, ntile, (__nv_bfloat16*)out);
+	tc_prepare_kernel<<<elemwise_grid(total), 256, 0, state().stream>>>(W, m, nf, KC, nsplit, f16, ntile, (uint16_t*)out, trailer);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }
 
-DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int nsplit, const float* bias, int relu,
+DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int precision, const float* bias, int relu,
                               const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion, int ptype,
                               float* pooled, const float* headW, const float* headB, uint32_t nmodel, float* scores,
                               int* status)
 {
 	DB_API_TRY
 	DB_REQUIRE(ptype >= DB_PT_MAX && ptype <= DB_PT_ALL, "ValueError: unknown pooling type %d", ptype);
-	DB_REQUIRE(nsplit >= 1 && nsplit <= 3, "ValueError: nsplit must be 1, 2 or 3");
+	unsigned nsplit, f16;
+	tc_mode(precision, nsplit, f16);
 	DB_REQUIRE(status != nullptr, "ValueError: db_scanpool_tc needs a device status word");
 	DB_REQUIRE(pooled || scores, "ValueError: db_scanpool_tc needs an output (pooled or scores)");
 	if (scores) {
@@ -618,7 +673,8 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int nspli
 	a.X = X; a.R = regions; a.Wt = (const __nv_bfloat16*)Wt; a.bias = bias; a.headW = headW; a.headB = headB;
 	a.pooled = pooled; a.scores = scores; a.status = status;
 	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.KC = KC; a.nsplit = nsplit;
-	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu;
+	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu; a.f16 = f16;
+	a.maxabs = reinterpret_cast<const uint32_t*>(static_cast<const unsigned char*>(Wt) + (size_t)ntile * nsplit * KC * 2048);
 	// Sequence chunks: about 8 waves of CTAs over the SMs (one CTA per SM), with the CTA
 	// count a multiple of the SM count so that the last wave is full; at least 64
 	// sequences per CTA.

@@ -91,18 +91,26 @@ def build_batch(seqs, padding, reverse_complement=False, device="cuda"):
     return X, R
 
 
-class TCWeights(object):
-    """Filter bank prepared for the tensor-core scan: bf16 operand tiles with
-    ``nsplit`` pieces per weight (1: bf16, 2: ~16 significant bits, 3: ~24 bits)."""
+TC_PRECISION = {"bf16": 1, "bf16x2": 2, "bf16x3": 3, "f16x2": 4, "f16": 5}
+TC_PIECES = {1: 1, 2: 2, 3: 3, 4: 2, 5: 1}     # 16-bit operand pieces per weight = tensor-core passes
 
-    def __init__(self, W, bias=None, nsplit=3):
+
+class TCWeights(object):
+    """Filter bank prepared for the tensor-core scan: 16-bit operand tiles.
+
+    ``precision``: "bf16", "bf16x2", "bf16x3" (1-3 bf16 pieces per weight: 8, 16, 24
+    significant bits) or "f16", "f16x2" (1-2 f16 pieces of power-of-two prescaled
+    weights: 11, 22 bits); the integers 1-5 of ``enum db_tc_precision`` also work."""
+
+    def __init__(self, W, bias=None, precision="f16x2"):
         _check(W, torch.float32, "W")
-        self.m, self.nf, self.nsplit = W.shape[0] // 4, W.shape[1], int(nsplit)
+        self.precision = TC_PRECISION[precision] if isinstance(precision, str) else int(precision)
+        self.m, self.nf, self.nsplit = W.shape[0] // 4, W.shape[1], TC_PIECES[self.precision]
         self.bias = bias
         dll = _dll()
-        nbytes = dll.db_tc_weights_bytes(self.m, self.nf, self.nsplit)
+        nbytes = dll.db_tc_weights_bytes(self.m, self.nf, self.precision)
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
-        dll.db_tc_prepare(_ptr(W), self.m, self.nf, self.nsplit, _ptr(self.buf))
+        dll.db_tc_prepare(_ptr(W), self.m, self.nf, self.precision, _ptr(self.buf))
 
 
 def scanpool_tc(tcw, X, R, ptype="all", relu=True, headW=None, headB=None, want_pooled=None, check=True,
@@ -127,7 +135,7 @@ def scanpool_tc(tcw, X, R, ptype="all", relu=True, headW=None, headB=None, want_
         assert tuple(scores.shape) == (nregion, nmodel)
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=X.device)
-    _dll().db_scanpool_tc(_ptr(tcw.buf), tcw.m, nf, tcw.nsplit, _ptr(tcw.bias), int(bool(relu)), _ptr(X), npos, _ptr(R),
+    _dll().db_scanpool_tc(_ptr(tcw.buf), tcw.m, nf, tcw.precision, _ptr(tcw.bias), int(bool(relu)), _ptr(X), npos, _ptr(R),
                           nregion, PT[ptype], _ptr(pooled), _ptr(headW), _ptr(headB), nmodel, _ptr(scores), _ptr(status))
     if check:
         code = int(status.item())

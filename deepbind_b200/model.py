@@ -176,9 +176,9 @@ class DeepBindNet(object):
         return out["loss"]
 
     # ------------------------------------------------------ tensor-core scoring
-    def prepare_tc(self, nsplit=3):
+    def prepare_tc(self, precision="f16x2"):
         """Prepares the filter bank for the tcgen05 scan (redo after a weight change)."""
-        self._tcw = fused.TCWeights(self.view("Wscan").contiguous(), self.view("bscan").view(-1), nsplit)
+        self._tcw = fused.TCWeights(self.view("Wscan").contiguous(), self.view("bscan").view(-1), precision)
         return self._tcw
 
     def score_tc(self, X, R, strand_max=False, check=True, out=None, status=None):

@@ -192,19 +192,27 @@ void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
  * passes of kangaroo.predict over the same sequences, predict.py:394-420, and
  * deepity's instance batching, hypertrain.py:576) ---------------------------
  * The scan is the dense contraction Z[f,p] = sum_k W[k,f] * onehot(X)[p,k], K = 4m.
- * Weights are prepared once per weight set into bf16 operand tiles; nsplit = 1, 2
- * or 3 bf16 pieces per weight give 8, 16 or 24 significant bits (max relative
- * error about 2e-3, 1e-5, 1e-6 of the largest activation).  Pooled values follow
+ * Weights are prepared once per weight set into 16-bit operand tiles; `precision`
+ * (enum db_tc_precision) picks the operand type and the pieces per weight, all
+ * accumulated in FP32 (the one-hot operand is exact in either type):
+ *   DB_TC_BF16 / _BF16X2 / _BF16X3: 1-3 bf16 pieces, 8/16/24 significant bits; max
+ *       error about 2e-3 / 1e-5 / 1e-6 of the largest activation;
+ *   DB_TC_F16 / _F16X2: 1-2 f16 pieces (11/22 bits) of the weights prescaled by a
+ *       power of two (undone in the kernel, exactly): about 3e-4 / 1e-6, at the
+ *       tensor-core cost of one / two bf16 pieces.
+ * Pooled values follow
  * db_scanpool_fwd's layout; argmax is not produced (use the FP32 path to train).
  * If `scores` is given, each model's linear head (16 filters per model; headW
  * [(16|32)*nmodel] in the row order of full.W, headB [nmodel]) is applied in the
  * kernel and scores [nregion, nmodel] is written; `pooled` may then be NULL.
- * Regions must ascend without overlap (the batch layout of data.py:329-334); rows
- * between regions are scanned and discarded.  status: device int the caller
- * zeroes; 0 = ok, 1 = a device-side wait timed out, 3 = regions out of order. */
-size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int nsplit);
-void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int nsplit, void* prepared);
-void db_scanpool_tc(const void* prepared, uint32_t m, uint32_t nf, int nsplit, const float* bias, int relu,
+ * Regions (8-byte aligned table) must ascend without overlap (the batch layout of
+ * data.py:329-334); rows between regions are scanned and discarded.  status: device
+ * int the caller zeroes; 0 = ok, 1 = a device-side wait timed out, 3 = regions out
+ * of order. */
+enum db_tc_precision { DB_TC_BF16 = 1, DB_TC_BF16X2 = 2, DB_TC_BF16X3 = 3, DB_TC_F16X2 = 4, DB_TC_F16 = 5 };
+size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int precision);
+void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int precision, void* prepared);
+void db_scanpool_tc(const void* prepared, uint32_t m, uint32_t nf, int precision, const float* bias, int relu,
                     const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion, int ptype,
                     float* pooled, const float* headW, const float* headB, uint32_t nmodel, float* scores,
                     int* status);

@@ -1,17 +1,19 @@
 """Parity of the tensor-core (tcgen05) many-model scan with the CPU oracle.
 
-The one-hot operand is exact in bf16; the weights carry 8, 16 or 24 significant
-bits (nsplit 1, 2, 3).  A weight's rounding error is the same at every position,
-so it does not average out under mean pooling: the tolerance is stated relative
-to the largest activation of the layer (the largest max-pooled value), times the
-number of rows for sum pooling: 2e-3 for one bf16 piece (the bound set for
-bf16/TF32 paths), 1e-5 for two and three pieces (the fp32 bound)."""
+The one-hot operand is exact in bf16 and f16; the weights carry 8, 16 or 24
+significant bits as 1, 2, 3 bf16 pieces (precision 1, 2, 3), or 22 / 11 bits as
+2 / 1 f16 pieces of prescaled weights (precision 4, 5).  A weight's rounding
+error is the same at every position, so it does not average out under mean
+pooling: the tolerance is stated relative to the largest activation of the layer
+(the largest max-pooled value), times the number of rows for sum pooling: 2e-3
+for one bf16 piece (the bound set for bf16/TF32 paths), 5e-4 for one f16 piece,
+1e-5 for bf16x2, bf16x3 (the fp32 bound) and 3e-6 for f16x2."""
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
 f32 = np.float32
-TOL = {1: 2e-3, 2: 1e-5, 3: 1e-5}
+TOL = {1: 2e-3, 2: 1e-5, 3: 1e-5, 4: 3e-6, 5: 5e-4}
 
 
 def dev(a):
@@ -31,7 +33,7 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("nsplit", [1, 2, 3])
+@pytest.mark.parametrize("nsplit", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("ptype", ["max", "avg", "sum", "all"])
 @pytest.mark.parametrize("m,nmodel,nseq,lmin,lmax,n_frac", CASES)
 def test_pooled_matches_oracle(cuda, orc, nsplit, ptype, m, nmodel, nseq, lmin, lmax, n_frac):
@@ -53,7 +55,7 @@ def test_pooled_matches_oracle(cuda, orc, nsplit, ptype, m, nmodel, nseq, lmin, 
     assert np.max(np.abs(got - want)) <= TOL[nsplit] * scale, (np.max(np.abs(got - want)), scale)
 
 
-@pytest.mark.parametrize("nsplit", [1, 3])
+@pytest.mark.parametrize("nsplit", [1, 3, 4, 5])
 @pytest.mark.parametrize("ptype", ["max", "all"])
 def test_fused_linear_head_scores(cuda, orc, nsplit, ptype):
     from deepbind_b200 import fused, synth
@@ -82,6 +84,22 @@ def test_three_pieces_agree_with_fp32_kernel(cuda):
     ref, _, _ = fused.scanpool(W, b, dX, dR, "all")
     got, _ = fused.scanpool_tc(fused.TCWeights(W, b, 3), dX, dR, "all")
     assert float((got - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("wscale", [1e-6, 0.05, 300.0])
+def test_f16_prescale_covers_small_and_large_weights(cuda, orc, wscale):
+    """f16 pieces hold weights of any magnitude: the bank is prescaled by a power of two."""
+    from deepbind_b200 import fused, synth
+    m, nf = 24, 128
+    X, R = synth.ragged_batch(60, 30, 120, m, seed=5, n_frac=0.03)
+    rng = np.random.default_rng(6)
+    W = (rng.standard_normal((4 * m, nf)) * wscale).astype(f32)
+    b = (rng.uniform(-2.0, 0.0, nf) * wscale).astype(f32)
+    want, _ = orc.scanpool(W.astype(np.float64), b.astype(np.float64), True, X, R, "all")
+    scale = np.abs(want[:, 0::2]).max()
+    for precision, tol in (("f16x2", 3e-6), ("f16", 5e-4)):
+        got, _ = fused.scanpool_tc(fused.TCWeights(dev(W), dev(b), precision), dev(X), dev(R), "all")
+        assert np.max(np.abs(got.cpu().numpy() - want)) <= tol * scale, precision
 
 
 def test_gaps_between_regions_and_tail_rows(cuda, orc):
