@@ -4,13 +4,14 @@
 //     Z[f, p] = sum_k  Wt[f, k] * onehot(X)[p, k],     k = 4*tap + channel,  K = 4*m
 // (corr1ord.cuh:108-164 written as a matrix product: a base selects one of the
 // four channel weights of a tap; any other byte contributes 1/4 of each; 254
-// contributes nothing).  The one-hot operand is exact in bf16 (values 0, 1/4, 1);
-// the weights are split into 1, 2 or 3 bf16 pieces (8, 16 or 24 significant
-// bits) that are accumulated into the same FP32 tensor-memory tile, so every
-// product is exact and only the summation order differs from the FP32 path.
+// contributes nothing).  The one-hot operand is exact in bf16 and f16 (values 0,
+// 1/4, 1); the weights are split into 1-3 bf16 pieces (8, 16, 24 significant bits)
+// or 1-2 f16 pieces of power-of-two prescaled weights (11, 22 bits) that are
+// accumulated into the same FP32 tensor-memory tile, so every product is exact and
+// only the summation order differs from the FP32 path.
 //
-// Layout of one CTA (384 threads, 1 CTA per SM):
-//   M = 128 filters of one filter tile (A operand: prepared bf16 weights, K-major,
+// Layout of one CTA (32 * (3 + 16) threads, 1 CTA per SM):
+//   M = 128 filters of one filter tile (A operand: prepared 16-bit weights, K-major,
 //       resident in shared memory for the CTA's lifetime, loaded by one bulk copy);
 //   N = 256 consecutive rows of the ordinal buffer (B operand), whatever sequences
 //       they belong to: the regions of a batch abut, so tiling the flat rows wastes
@@ -21,16 +22,17 @@
 // E[q] = one-hot pair of bases (q, q+1), IS the K-major operand when the
 // shared-memory descriptor uses an 8-row group stride of 128 bytes and a K-chunk
 // stride of 32 bytes: row p, chunk kc lives at E + 16*(p + 2*kc).
-// Warp roles: warp 0 issues tcgen05.mma; warps 1-3 encode E for the next stage of
-// 8 tiles (double buffered); warps 4-11 drain the accumulators: each thread owns one
-// filter (one TMEM lane); two warps share a lane quarter, one taking the even
-// regions and one the odd.  A warp fetches the columns of its region starting at
-// the region's own first column, in pieces of 64/32/16/8/4/2/1 columns, so the
-// reduction (bias, rectify, max / mean, in registers) needs no per-column tests;
-// when a region ends it either stores the pooled features or folds them through
-// the model's linear head (16 lanes = one model, warp shuffles).  Per-position
-// activations never leave the SM.  Regions must ascend without overlap (the batch
-// layout).
+// Warp roles: warp 0 issues tcgen05.mma; warps 1-2 encode E for the next stage of
+// 8 tiles (double buffered); warps 3-18 drain the accumulators: each thread owns one
+// filter (one TMEM lane); four warps share a lane quarter and take the regions in
+// turn, each walking only its own regions.  A warp fetches the columns of its region
+// starting at the region's own first column, in pieces of 32/16/8/4/2/1 columns, so
+// the reduction (in registers) needs no per-column tests.  The maximum commutes with
+// bias and rectifier, which are applied once per region; the rectified sum costs one
+// saturating FMA and half a packed add per column.  When a region ends the warp
+// either stores the pooled features or folds them through the model's linear head
+// (16 lanes = one model, warp shuffles).  Per-position activations never leave the
+// SM.  Regions must ascend without overlap (the batch layout).
 //
 // Every wait on an mbarrier is bounded by a clock deadline; on expiry the CTA sets
 // a status word, releases its tensor memory and returns.
@@ -43,18 +45,20 @@ namespace db {
 
 static constexpr int TC_STAGE_TILES = 8;    // tiles of 256 flat rows per E stage
 static constexpr int TC_ECHUNKS = TC_STAGE_TILES * 256 + 128;   // 16-byte chunks per stage incl. the K reach of the last row
-static constexpr int TC_EPI_SETS = 3;       // epilogue warps per TMEM lane quarter; region g is reduced by set g % TC_EPI_SETS
-static constexpr int TC_THREADS = 128 + 128 * TC_EPI_SETS;
+static constexpr int TC_EPI_SETS = 4;      // epilogue warps per TMEM lane quarter; region g is reduced by set g % TC_EPI_SETS
+static constexpr int TC_BUILD_WARPS = 2;   // warps that encode the B operand (one stage ahead; a stage lasts 8 tiles)
+static constexpr int TC_EPI_WARP0 = 1 + TC_BUILD_WARPS;             // first epilogue warp
+static constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + 4 * TC_EPI_SETS);
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // clock cycles (about 0.1 s)
 
 struct tc_args {
 	const uint8_t* X; const uint32_t* R; const __nv_bfloat16* Wt; const float* bias;
 	const float* headW; const float* headB;
 	float* pooled; float* scores; int* status;
-	unsigned npos, n, nregion, nf, KC, nsplit, seqs_per_cta, nmodel;
+	unsigned npos, n, nregion, nf, m, KC, nsplit, seqs_per_cta, nmodel;
 	int ptype, relu;
 	unsigned f16;                   // operand type of both MMA inputs: 0 = bf16, 1 = f16 (weights prescaled by a power of two)
-	const uint32_t* maxabs;         // f16 only: bit pattern of max |W|, kept behind the prepared tiles
+	const uint32_t* maxabs;         // bit pattern of max |W|, kept behind the prepared tiles
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -232,6 +236,22 @@ __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigne
 	return r;
 }
 
+__device__ __forceinline__ float fma_sat(float x, float m, float c)
+{
+	float d;
+	asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(x), "f"(m), "f"(c));
+	return d;
+}
+// A power of two strictly above `bound` (> 0, finite); 1 for a zero bound.
+__device__ __forceinline__ float pow2_above(float bound)
+{
+	const uint32_t bits = __float_as_uint(bound);
+	int e = (int)((bits >> 23) & 0xffu) - 127;
+	if ((bits & 0x7fffffffu) == 0u) return 1.f;
+	e = max(-100, min(100, e));
+	return __uint_as_float((uint32_t)(e + 1 + 127) << 23);
+}
+
 struct pool_state {
 	float mx[4];
 	unsigned long long sm2[4];      // four packed pairs of partial sums
@@ -242,8 +262,14 @@ struct pool_state {
 		for (int j = 0; j < 4; ++j) { mx[j] = -INFINITY; sm2[j] = 0ull; }
 		sm1 = 0.f;
 	}
+	// The maximum takes the raw accumulator x (bias and rectifier commute with it and
+	// are applied once per region).  The sum takes the rectified activation as
+	// relu_term(x) = sat(x*cm + ca) = relu(z + b) / S: one saturating FMA on the FMA
+	// pipe instead of an add and a maximum (the FP32 maximum issues at half rate),
+	// with S a power of two above any activation of this filter, so that the upper
+	// clamp of .sat never acts and the scaling is exact.
 	template <bool WANT_MAX, bool WANT_SUM, bool RELU, int N>
-	__device__ __forceinline__ void add(const float* v, float nb)
+	__device__ __forceinline__ void add(const float* v, float cm, float ca)
 	{
 		if (N >= 8) {
 			#pragma unroll
@@ -252,35 +278,35 @@ struct pool_state {
 				for (int j = 0; j < 4; ++j) {
 					const float x0 = v[i + 2 * j], x1 = v[i + 2 * j + 1];
 					if (WANT_MAX) mx[j] = max3(mx[j], x0, x1);
-					if (WANT_SUM) sm2[j] = add2(sm2[j], pack2(RELU ? fmaxf(x0, nb) : x0, RELU ? fmaxf(x1, nb) : x1));
+					if (WANT_SUM) sm2[j] = add2(sm2[j], pack2(RELU ? fma_sat(x0, cm, ca) : x0, RELU ? fma_sat(x1, cm, ca) : x1));
 				}
 			}
 		} else {
 			#pragma unroll
 			for (int i = 0; i < N; ++i) {
 				if (WANT_MAX) mx[i & 3] = fmaxf(mx[i & 3], v[i]);
-				if (WANT_SUM) sm1 += RELU ? fmaxf(v[i], nb) : v[i];
+				if (WANT_SUM) sm1 += RELU ? fma_sat(v[i], cm, ca) : v[i];
 			}
 		}
 	}
 	// A piece of n <= 32 columns in a 32-register buffer: a full piece fills it; a
 	// shorter one keeps its 16/8/4/2/1-column parts at fixed offsets 0/16/24/28/30.
 	template <bool WANT_MAX, bool WANT_SUM, bool RELU>
-	__device__ __forceinline__ void add_piece(const float (&v)[32], unsigned n, float nb)
+	__device__ __forceinline__ void add_piece(const float (&v)[32], unsigned n, float cm, float ca)
 	{
-		if (n >= 32) { add<WANT_MAX, WANT_SUM, RELU, 32>(v, nb); return; }
-		if (n & 16) add<WANT_MAX, WANT_SUM, RELU, 16>(v, nb);
-		if (n & 8)  add<WANT_MAX, WANT_SUM, RELU, 8>(v + 16, nb);
-		if (n & 4)  add<WANT_MAX, WANT_SUM, RELU, 4>(v + 24, nb);
-		if (n & 2)  add<WANT_MAX, WANT_SUM, RELU, 2>(v + 28, nb);
-		if (n & 1)  add<WANT_MAX, WANT_SUM, RELU, 1>(v + 30, nb);
+		if (n >= 32) { add<WANT_MAX, WANT_SUM, RELU, 32>(v, cm, ca); return; }
+		if (n & 16) add<WANT_MAX, WANT_SUM, RELU, 16>(v, cm, ca);
+		if (n & 8)  add<WANT_MAX, WANT_SUM, RELU, 8>(v + 16, cm, ca);
+		if (n & 4)  add<WANT_MAX, WANT_SUM, RELU, 4>(v + 24, cm, ca);
+		if (n & 2)  add<WANT_MAX, WANT_SUM, RELU, 2>(v + 28, cm, ca);
+		if (n & 1)  add<WANT_MAX, WANT_SUM, RELU, 1>(v + 30, cm, ca);
 	}
 	// `cnt` rows whose scan output is zero
 	template <bool WANT_MAX, bool WANT_SUM, bool RELU>
-	__device__ __forceinline__ void add_zero_rows(unsigned cnt, float nb)
+	__device__ __forceinline__ void add_zero_rows(unsigned cnt, float cm, float ca)
 	{
 		if (WANT_MAX) mx[0] = fmaxf(mx[0], 0.f);
-		if (WANT_SUM) sm1 += (float)cnt * (RELU ? fmaxf(0.f, nb) : 0.f);
+		if (WANT_SUM && RELU) sm1 += (float)cnt * fma_sat(0.f, cm, ca);
 	}
 	__device__ __forceinline__ float max_all() const { return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])); }
 	__device__ __forceinline__ float sum_all() const
@@ -298,11 +324,15 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
                                             unsigned row_lo, unsigned row_hi, unsigned warp, unsigned lane)
 {
 	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
-	const unsigned set = (warp - 4) >> 2;               // the warps of a quarter take the regions in turn
+	const unsigned set = (warp - TC_EPI_WARP0) >> 2;    // the warps of a quarter take the regions in turn
 	const unsigned f = tile * 128 + q4 * 32 + lane;     // this thread's filter = its TMEM lane
-	const float wscale = a.f16 ? tc_weight_scale(*a.maxabs) : 1.f, inv_wscale = 1.f / wscale;    // powers of two
-	const float b = ((a.bias && f < a.nf) ? a.bias[f] : 0.f) * wscale;
-	const float nb = -b;
+	const uint32_t maxabs_bits = *a.maxabs;
+	const float wscale = a.f16 ? tc_weight_scale(maxabs_bits) : 1.f, inv_wscale = 1.f / wscale;    // powers of two
+	const float b0 = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
+	const float b = b0 * wscale;                        // bias in the accumulator's (scaled) domain
+	// |z + b| <= m * max|W| + |b|: the scale of the saturating rectifier (see pool_state::add)
+	const float ssat = pow2_above((float)a.m * __uint_as_float(maxabs_bits) + fabsf(b0));
+	const float cm = inv_wscale / ssat, ca = b0 / ssat;
 	// linear head of the model this filter belongs to (16 filters per model)
 	float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
 	const unsigned model = f / 16;
@@ -341,7 +371,8 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 		const unsigned P = r1 - r0;
 		float pmax = ps.max_all() + b;                 // max_p relu(z_p + b) = relu(max_p z_p + b)
 		pmax = (RELU ? fmaxf(pmax, 0.f) : pmax) * inv_wscale;
-		const float psum = (ps.sum_all() + (float)P * b) * inv_wscale;        // sum_p max(z_p, -b) + P*b
+		// rectified: the terms were relu(z_p + b) / ssat; otherwise they were the raw accumulators
+		const float psum = RELU ? ps.sum_all() * ssat : ps.sum_all() * inv_wscale + (float)P * b0;
 		const float second = a.ptype == DB_PT_SUM ? psum : __fdividef(psum, (float)P);
 		if (a.pooled && f < a.nf) {
 			const size_t o = (size_t)g * a.nf + f;
@@ -393,22 +424,19 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 				unsigned left = live_end - pos;
 				// 64 columns per TMEM round trip (40-60 clocks, hidden by the other warps of
 				// the scheduler), then the remaining 0..63 columns with one more wait.
-				float va[32], vb[32];
-				while (left >= 64) {
-					tmem_ld32(ta, va); tmem_ld32(ta + 32, vb);
+				float va[32];
+				while (left >= 32) {
+					tmem_ld32(ta, va);
 					tmem_ld_wait();
-					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
-					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(vb, nb);
-					ta += 64; left -= 64;
+					ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, cm, ca);
+					ta += 32; left -= 32;
 				}
 				if (left) {
-					if (left & 32) { tmem_ld32(ta, va); ta += 32; }
-					load_piece(ta, left & 31, vb);
+					load_piece(ta, left, va);
 					tmem_ld_wait();
-					if (left & 32) ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, nb);
-					ps.add_piece<WANT_MAX, WANT_SUM, RELU>(vb, left & 31, nb);
+					ps.add_piece<WANT_MAX, WANT_SUM, RELU>(va, left, cm, ca);
 				}
-				if (live_end < end) ps.add_zero_rows<WANT_MAX, WANT_SUM, RELU>(end - live_end, nb);
+				if (live_end < end) ps.add_zero_rows<WANT_MAX, WANT_SUM, RELU>(end - live_end, cm, ca);
 			}
 			if (r1 > tile_hi) break;                       // the region continues in the next tile
 			ok = finish_region();
@@ -458,7 +486,7 @@ scanpool_tc_kernel(const tc_args a)
 	if (threadIdx.x == 0) {
 		mbar_init(&bar_a, 1);
 		for (int i = 0; i < 2; ++i) {
-			mbar_init(&e_full[i], 3); mbar_init(&e_empty[i], 1);
+			mbar_init(&e_full[i], TC_BUILD_WARPS); mbar_init(&e_empty[i], 1);
 			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 4 * TC_EPI_SETS);
 		}
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -510,29 +538,36 @@ scanpool_tc_kernel(const tc_args a)
 				if (tt == TC_STAGE_TILES - 1 || t + 1 == ntile) umma_commit(&e_empty[st]);
 			}
 		}
-	} else if (warp < 4) {
+	} else if (warp < TC_EPI_WARP0) {
 		// ---------------------------------------------------------- E builders
-		const unsigned bt = threadIdx.x - 32;     // 0..95
+		const unsigned bt = threadIdx.x - 32;     // 0 .. 32*TC_BUILD_WARPS-1
 		const unsigned nstage = (ntile + TC_STAGE_TILES - 1) / TC_STAGE_TILES;
 		for (unsigned stage = 0; stage < nstage; ++stage) {
 			const unsigned st = stage & 1;
-			// One thread waits (bounded) and publishes the outcome, so that all 96
+			// One thread waits (bounded) and publishes the outcome, so that all
 			// builder threads take the same path to the named barrier.
 			if (bt == 0) blk_ok[st] = mbar_wait(&e_empty[st], ((stage >> 1) & 1) ^ 1, abort_flag) ? 1u : 0u;
-			asm volatile("bar.sync 1, 96;" ::: "memory");
+			asm volatile("bar.sync 1, %0;" :: "n"(32 * TC_BUILD_WARPS) : "memory");
 			if (blk_ok[st] == 0) break;
 			const unsigned base_row = row_lo + stage * (TC_STAGE_TILES * 256u);
 			uint4* E = reinterpret_cast<uint4*>(Es + (size_t)st * TC_ECHUNKS * 16);
-			// A thread encodes 16 consecutive chunks from 20 bytes fetched as aligned words.
-			for (unsigned q = bt * 16; q < TC_ECHUNKS; q += 96 * 16) {
+			// A thread encodes 16 consecutive chunks from 20 bytes fetched as aligned words;
+			// the words of its next 16 chunks are requested before it encodes these.
+			constexpr unsigned QSTEP = 32 * TC_BUILD_WARPS * 16;
+			auto fetch = [&](unsigned q, uint32_t (&w)[6]) {
 				const unsigned i0 = base_row + q;
 				const size_t addr = (size_t)a.X + i0;
 				const uint32_t* wp = reinterpret_cast<const uint32_t*>(addr & ~(size_t)3);
-				const unsigned sh = (unsigned)(addr & 3) * 8;
-				uint32_t w[6];
 				#pragma unroll
 				for (int k = 0; k < 6; ++k)      // a word is read only if its first byte lies inside the buffer
 					w[k] = ((long long)i0 + 4 * k - (long long)(addr & 3) < (long long)a.npos) ? wp[k] : 0xfefefefeu;
+			};
+			uint32_t w[6], wn[6];
+			if (bt * 16 < TC_ECHUNKS) fetch(bt * 16, w);
+			for (unsigned q = bt * 16; q < TC_ECHUNKS; q += QSTEP) {
+				if (q + QSTEP < TC_ECHUNKS) fetch(q + QSTEP, wn);
+				const unsigned i0 = base_row + q;
+				const unsigned sh = (unsigned)(((size_t)a.X + i0) & 3) * 8;
 				uint32_t win[5];
 				#pragma unroll
 				for (int k = 0; k < 5; ++k) win[k] = __funnelshift_r(w[k], w[k + 1], sh);
@@ -544,6 +579,8 @@ scanpool_tc_kernel(const tc_args a)
 					E[q + c] = make_uint4((unsigned)prev, (unsigned)(prev >> 32), (unsigned)p1, (unsigned)(p1 >> 32));
 					prev = p1;
 				}
+				#pragma unroll
+				for (int k = 0; k < 6; ++k) w[k] = wn[k];
 			}
 			fence_async_smem();
 			__syncwarp();
@@ -566,7 +603,8 @@ scanpool_tc_kernel(const tc_args a)
 
 // Prepared weights: for each 128-filter tile, `nsplit` K-major 16-bit operand tiles
 // in the shared-memory layout [split][K chunk][filter][8], zero padded; behind the
-// tiles, 16 bytes whose first word is the bit pattern of max |W| (f16 modes).
+// tiles, 16 bytes whose first word is the bit pattern of max |W| (the prescale of
+// the f16 modes and the bound of the epilogue's saturating rectifier derive from it).
 __global__ void tc_maxabs_kernel(const float* __restrict__ W, size_t count, uint32_t* __restrict__ out)
 {
 	uint32_t mx = 0;
@@ -637,11 +675,9 @@ DB_EXPORT void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int precis
 	tc_shape(m, nf, KC, ntile);
 	uint32_t* trailer = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(out) + (size_t)ntile * nsplit * KC * 2048);
 	DB_CUDA(cudaMemsetAsync(trailer, 0, 16, state().stream));
-	if (f16) {
-		size_t count = (size_t)4 * m * nf;
-		tc_maxabs_kernel<<<elemwise_grid(count), 256, 0, state().stream>>>(W, count, trailer);
-		DB_LAUNCH_CHECK();
-	}
+	size_t count = (size_t)4 * m * nf;
+	tc_maxabs_kernel<<<elemwise_grid(count), 256, 0, state().stream>>>(W, count, trailer);
+	DB_LAUNCH_CHECK();
 	size_t total = (size_t)ntile * KC * 1024;
 	tc_prepare_kernel<<<elemwise_grid(total), 256, 0, state().stream>>>(W, m, nf, KC, nsplit, f16, ntile, (uint16_t*)out, trailer);
 	DB_LAUNCH_CHECK();
@@ -672,7 +708,7 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int preci
 	tc_args a;
 	a.X = X; a.R = regions; a.Wt = (const __nv_bfloat16*)Wt; a.bias = bias; a.headW = headW; a.headB = headB;
 	a.pooled = pooled; a.scores = scores; a.status = status;
-	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.KC = KC; a.nsplit = nsplit;
+	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.m = m; a.KC = KC; a.nsplit = nsplit;
 	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu; a.f16 = f16;
 	a.maxabs = reinterpret_cast<const uint32_t*>(static_cast<const unsigned char*>(Wt) + (size_t)ntile * nsplit * KC * 2048);
 	// Sequence chunks: about 8 waves of CTAs over the SMs (one CTA per SM), with the CTA
