@@ -26,7 +26,17 @@ struct head_args {
 	int kind;
 };
 
-__global__ void __launch_bounds__(256)
+// Sum over the rows i = k, k+8, ... of a column, k = lane % 8, then over the eight
+// partial sums with a fixed shuffle tree: eight lanes share one output.
+__device__ __forceinline__ float sum8(float s)
+{
+	s += __shfl_xor_sync(0xffffffffu, s, 4);
+	s += __shfl_xor_sync(0xffffffffu, s, 2);
+	s += __shfl_xor_sync(0xffffffffu, s, 1);
+	return s;
+}
+
+__global__ void __launch_bounds__(1024)
 head_train_kernel(const head_args a)
 {
 	extern __shared__ __align__(16) float hs[];
@@ -38,7 +48,7 @@ head_train_kernel(const head_args a)
 	float* w1  = a1 + (size_t)B * HC;      // [np][WS]
 	float* w2  = w1 + (size_t)np * WS;     // [HC]
 	float* out = w2 + HC;                  // [B]       output, then dout
-	float* red = out + B;                  // [256]
+	float* red = out + B;                  // [blockDim.x]
 
 	const size_t ldp = (size_t)np * a.I;
 	for (unsigned t = tid; t < B * np; t += nt) {
@@ -94,17 +104,22 @@ head_train_kernel(const head_args a)
 	}
 	if (tid == 0 && a.loss) a.loss[b] = (a.kind == 0 ? 0.5f : -1.f) * (red[0] * inv);
 
-	// second layer backward; h1 becomes the gradient of the hidden pre-activation
+	// second layer backward; h1 becomes the gradient of the hidden pre-activation.
+	// Column sums over the minibatch: eight lanes per output (nt is a multiple of 32).
+	const unsigned k8 = tid & 7;
 	if (H) {
-		for (unsigned c = tid; c < H; c += nt) {
+		for (unsigned c = tid >> 3; c < ((H + 3u) & ~3u); c += nt >> 3) {     // whole warps stay in the loop for the shuffles
 			float s = 0.f;
-			for (unsigned i = 0; i < B; ++i) s = fmaf(a1[i * H + c], out[i], s);
-			a.dW2[(size_t)b * H + c] = s;
+			if (c < H) for (unsigned i = k8; i < B; i += 8) s = fmaf(a1[i * H + c], out[i], s);
+			s = sum8(s);
+			if (c < H && k8 == 0) a.dW2[(size_t)b * H + c] = s;
 		}
-		if (tid == nt - 1) {
+		if (tid >= nt - 32) {                                 // the last warp: bias gradient of the output unit
 			float s = 0.f;
-			for (unsigned i = 0; i < B; ++i) s += out[i];
-			a.db2[b] = s;
+			for (unsigned i = tid & 31; i < B; i += 32) s += out[i];
+			s += __shfl_xor_sync(0xffffffffu, s, 16);
+			s = sum8(s + __shfl_xor_sync(0xffffffffu, s, 8));
+			if ((tid & 31) == 0) a.db2[b] = s;
 		}
 		for (unsigned t = tid; t < B * H; t += nt) {
 			const unsigned i = t / H, c = t % H;
@@ -116,10 +131,11 @@ head_train_kernel(const head_args a)
 	__syncthreads();
 
 	// first layer backward
-	for (unsigned c = tid; c < HC; c += nt) {
+	for (unsigned c = tid >> 3; c < ((HC + 3u) & ~3u); c += nt >> 3) {
 		float s = 0.f;
-		for (unsigned i = 0; i < B; ++i) s += h1[i * HC + c];
-		a.db1[(size_t)b * HC + c] = s;
+		if (c < HC) for (unsigned i = k8; i < B; i += 8) s += h1[i * HC + c];
+		s = sum8(s);
+		if (c < HC && k8 == 0) a.db1[(size_t)b * HC + c] = s;
 	}
 	for (unsigned t = tid; t < np * HC; t += nt) {
 		const unsigned u = t / HC, c = t % HC;
@@ -140,7 +156,7 @@ head_train_kernel(const head_args a)
 static size_t head_smem_bytes(unsigned B, unsigned np, unsigned H)
 {
 	unsigned HC = H ? H : 1u;
-	return ((size_t)B * np + 2 * (size_t)B * HC + (size_t)np * (HC + 1) + HC + B + 256) * sizeof(float);
+	return ((size_t)B * np + 2 * (size_t)B * HC + (size_t)np * (HC + 1) + HC + B + 1024) * sizeof(float);
 }
 
 }  // namespace db
@@ -174,7 +190,8 @@ DB_EXPORT void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, i
 	a.loss = loss; a.dpooled = dpooled; a.dW1 = dW1; a.db1 = db1; a.dW2 = dW2; a.db2 = db2;
 	a.B = B; a.I = nmodel; a.npool = npool; a.H = hidden; a.kind = loss_kind;
 	DB_CUDA(cudaFuncSetAttribute(head_train_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-	head_train_kernel<<<nmodel, 256, smem, state().stream>>>(a);
+	// few models: one large CTA each hides the latency of the short dependent phases
+	head_train_kernel<<<nmodel, nmodel <= 64 ? 1024 : 256, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }

@@ -331,14 +331,37 @@ scanpool_bwd_kernel(const bwd_args a)
 		out[(size_t)4 * m * a.nf + f0 + threadIdx.x] = bsum;
 }
 
-__global__ void scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const float* __restrict__ partial,
-                                    size_t wcount, unsigned nf, unsigned nparts)
+// Second stage: sums the per-CTA partial gradients in a fixed order.  A CTA of eight
+// warps owns 32 consecutive outputs (one coalesced row segment per part); warp w
+// adds the parts w, w+8, ... with four independent chains, and warp 0 combines the
+// eight sums.  The order depends on `nparts` only, so repeated runs agree bit for bit.
+__global__ void __launch_bounds__(256)
+scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const float* __restrict__ partial,
+                    size_t wcount, unsigned nf, unsigned nparts)
 {
+	__shared__ float part[8][32];
 	const size_t total = wcount + nf;
-	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-		float s = 0.f;
-		for (unsigned p = 0; p < nparts; ++p) s += partial[(size_t)p * total + i];
-		if (i < wcount) dW[i] = s; else if (dbias) dbias[i - wcount] = s;
+	const unsigned lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+	for (size_t base = (size_t)blockIdx.x * 32; base < total; base += (size_t)gridDim.x * 32) {
+		const size_t i = base + lane;
+		float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+		if (i < total) {
+			const float* P = partial + i;
+			unsigned p = w;
+			for (; p + 24 < nparts; p += 32) {
+				s0 += P[(size_t)p * total]; s1 += P[(size_t)(p + 8) * total];
+				s2 += P[(size_t)(p + 16) * total]; s3 += P[(size_t)(p + 24) * total];
+			}
+			for (; p < nparts; p += 8) s0 += P[(size_t)p * total];
+		}
+		part[w][lane] = (s0 + s1) + (s2 + s3);
+		__syncthreads();
+		if (w == 0 && i < total) {
+			const float s = ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane])) +
+			                ((part[4][lane] + part[5][lane]) + (part[6][lane] + part[7][lane]));
+			if (i < wcount) dW[i] = s; else if (dbias) dbias[i - wcount] = s;
+		}
+		__syncthreads();
 	}
 }
 
@@ -423,7 +446,7 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
-	scanpool_bwd_reduce<<<elemwise_grid(wcount + nf), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta);
+	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount + nf, (size_t)32), 65535), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }

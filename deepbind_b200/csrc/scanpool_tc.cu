@@ -84,6 +84,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity)
 	return ok != 0;
 }
 // Bounded wait: false when the deadline passes or another role has aborted.
+// (A try_wait with a suspend-time hint instead of the short sleep was measured
+// 10 % slower: the waiters wake later than they do from a 40 ns sleep.)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag)
 {
 	if (mbar_try_wait(bar, parity)) return true;
