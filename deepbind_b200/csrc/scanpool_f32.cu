@@ -203,16 +203,24 @@ scanpool_fwd_kernel(const fwd_args a)
 // (poolrgn_bprop.cuh:45-127 then elemwise.py:78), dbias = column sums of dZ
 // (elemwise.py:176), dW[(4j+k),f] = sum_i dZ[i,f] * [X[i+j]==k]  (+1/4 to all four
 // channels for N; corr1ord_bprop.cuh:121-132).  Regions must be disjoint.
-// A CTA owns up to 8 regions x FB filters: per tile it rebuilds dZ in shared
-// memory, then a thread per (tap, filter) adds the tile's rows in order.
-// Per-CTA partials go to scratch and are added, CTA ascending, by a second
-// kernel: fixed order, no float atomics.
+// A CTA owns up to 8 regions x FB filters: per tile of TR rows it rebuilds dZ in
+// shared memory, then a thread per (group of four taps, filter) adds the tile's rows
+// in order into 16 register accumulators: the row's dZ is read once for the four
+// taps, and the channel weights of the four rows the taps look at slide through
+// registers (one new 16-byte read per row), so the loop issues 16 FMAs for two
+// shared-memory reads.  Per-CTA partials go to scratch and are added, CTA ascending,
+// by a second kernel: fixed order, no float atomics.
 struct bwd_args {
 	const uint8_t* X; const uint32_t* R; const float* dpooled; const uint32_t* argmax; const uint16_t* actmask;
 	float* partial;
 	unsigned m, nf, npos, n, nregion, G, FB;
 	int ptype;
 };
+
+__device__ __forceinline__ void bwd_fma4(float (&c)[4], float v, const float4& w)
+{
+	c[0] = fmaf(v, w.x, c[0]); c[1] = fmaf(v, w.y, c[1]); c[2] = fmaf(v, w.z, c[2]); c[3] = fmaf(v, w.w, c[3]);
+}
 
 __global__ void __launch_bounds__(512)
 scanpool_bwd_kernel(const bwd_args a)
@@ -224,7 +232,8 @@ scanpool_bwd_kernel(const bwd_args a)
 	float* dmax = davg + GMAX * FB;                                     // [GMAX][FB]
 	unsigned* amax = reinterpret_cast<unsigned*>(dmax + GMAX * FB);     // [GMAX][FB] argmax row
 	// per input row the weight each channel's gradient receives: one-hot, 1/4 each for N, 0 for a dropped base
-	float4* oh = reinterpret_cast<float4*>(amax + GMAX * FB);           // [TR + m]
+	float4* oh = reinterpret_cast<float4*>(amax + GMAX * FB);           // [TR + m + 4]
+	int* rowg = reinterpret_cast<int*>(oh + TR + m + 4);                // [TR] region of a row within this CTA, or -1
 	__shared__ unsigned rg0[GMAX], rg1[GMAX];
 	__shared__ unsigned s_lo, s_hi;
 
@@ -257,78 +266,93 @@ scanpool_bwd_kernel(const bwd_args a)
 	}
 	__syncthreads();
 
-	// accumulator identity: pair p = (tap j, filter f); pairs beyond m*FB idle.
-	// The extra FB threads after the pairs sum dbias.
-	const unsigned npair = m * FB;
-	float a0[2] = {0.f, 0.f}, a1[2] = {0.f, 0.f}, a2[2] = {0.f, 0.f}, a3[2] = {0.f, 0.f};
+	// accumulator identity: unit u = (tap group jg, filter fl) covers taps 4jg .. 4jg+3.
+	// The FB threads after the units sum dbias.
+	const unsigned nunit = ((m + 3) / 4) * FB;
+	const bool is_unit = threadIdx.x < nunit, is_bias = threadIdx.x >= nunit && threadIdx.x < nunit + FB;
+	const unsigned j0 = 4 * (threadIdx.x / FB), fl = threadIdx.x % FB;
+	float c[4][4];
+	#pragma unroll
+	for (int t = 0; t < 4; ++t)
+		#pragma unroll
+		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
 	float bsum = 0.f;
 	const unsigned nwords = (a.nf + 15) / 16;
 
 	if (s_hi > s_lo)
 	for (unsigned t0 = s_lo; t0 < s_hi; t0 += TR) {
 		__syncthreads();
-		for (unsigned t = threadIdx.x; t < TR + m; t += blockDim.x) {
+		for (unsigned t = threadIdx.x; t < TR + m + 4; t += blockDim.x) {
 			unsigned i = t0 + t, x = i < a.npos ? a.X[i] : 254u;
 			const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
 			oh[t] = make_float4(x == 0u ? 1.f : q, x == 1u ? 1.f : q, x == 2u ? 1.f : q, x == 3u ? 1.f : q);
 		}
-		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
-			unsigned r = t / FB, fl = t % FB, row = t0 + r;
-			float v = 0.f;
-			if (row < s_hi && f0 + fl < a.nf) {
-				int g = -1;
+		for (unsigned r = threadIdx.x; r < TR; r += blockDim.x) {
+			const unsigned row = t0 + r;
+			int g = -1;
+			if (row < s_hi)
 				for (unsigned k = 0; k < ng; ++k) if (row >= rg0[k] && row < rg1[k]) g = (int)k;
-				if (g >= 0) {
-					unsigned bits = a.actmask[(size_t)row * nwords + (f0 + fl) / 16];
-					if ((bits >> ((f0 + fl) & 15)) & 1u) {
-						v = davg[g * FB + fl];
-						if (amax[g * FB + fl] == row) v = v + dmax[g * FB + fl];
-					}
+			rowg[r] = g;
+		}
+		__syncthreads();
+		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
+			const unsigned r = t / FB, e = t % FB, row = t0 + r;
+			const int g = rowg[r];
+			float v = 0.f;
+			if (g >= 0 && f0 + e < a.nf) {
+				const unsigned bits = a.actmask[(size_t)row * nwords + (f0 + e) / 16];
+				if ((bits >> ((f0 + e) & 15)) & 1u) {
+					v = davg[g * FB + e];
+					if (amax[g * FB + e] == row) v = v + dmax[g * FB + e];
 				}
 			}
 			dz[t] = v;
 		}
 		__syncthreads();
-		#pragma unroll
-		for (int k = 0; k < 2; ++k) {
-			unsigned p = threadIdx.x + k * blockDim.x;
-			if (p < npair) {
-				unsigned j = p / FB, fl = p % FB;
-				float c0 = a0[k], c1 = a1[k], c2 = a2[k], c3 = a3[k];
-				// Rows at or past n have no scan output, hence no filter gradient.
-				unsigned rows = min((unsigned)TR, a.n > t0 ? a.n - t0 : 0u);
-				// Branch-free: the channel weights are 0, 1/4 or 1, so each product is exact and
-				// the fused multiply-add equals the reference's add of dZ (or dZ/4).
-				#pragma unroll 4
-				for (unsigned r = 0; r < rows; ++r) {
-					const float v = dz[r * FB + fl];
-					const float4 w = oh[r + j];
-					c0 = fmaf(v, w.x, c0); c1 = fmaf(v, w.y, c1); c2 = fmaf(v, w.z, c2); c3 = fmaf(v, w.w, c3);
-				}
-				a0[k] = c0; a1[k] = c1; a2[k] = c2; a3[k] = c3;
+		// Rows at or past n have no scan output, hence no filter gradient.
+		const unsigned rows = min((unsigned)TR, a.n > t0 ? a.n - t0 : 0u);
+		if (is_unit) {
+			// Branch-free: the channel weights are 0, 1/4 or 1, so each product is exact and
+			// the fused multiply-add equals the reference's add of dZ (or dZ/4).
+			const float* dzc = dz + fl;
+			const float4* ohj = oh + j0;
+			float4 w0 = ohj[0], w1 = ohj[1], w2 = ohj[2], w3 = ohj[3];
+			unsigned r = 0;
+			for (; r + 4 <= rows; r += 4) {       // four rows per pass: the window rotates through its registers
+				float v = dzc[(r + 0) * FB];
+				bwd_fma4(c[0], v, w0); bwd_fma4(c[1], v, w1); bwd_fma4(c[2], v, w2); bwd_fma4(c[3], v, w3);
+				w0 = ohj[r + 4];
+				v = dzc[(r + 1) * FB];
+				bwd_fma4(c[0], v, w1); bwd_fma4(c[1], v, w2); bwd_fma4(c[2], v, w3); bwd_fma4(c[3], v, w0);
+				w1 = ohj[r + 5];
+				v = dzc[(r + 2) * FB];
+				bwd_fma4(c[0], v, w2); bwd_fma4(c[1], v, w3); bwd_fma4(c[2], v, w0); bwd_fma4(c[3], v, w1);
+				w2 = ohj[r + 6];
+				v = dzc[(r + 3) * FB];
+				bwd_fma4(c[0], v, w3); bwd_fma4(c[1], v, w0); bwd_fma4(c[2], v, w1); bwd_fma4(c[3], v, w2);
+				w3 = ohj[r + 7];
 			}
-		}
-		if (threadIdx.x < FB) {
+			for (; r < rows; ++r) {
+				const float v = dzc[r * FB];
+				bwd_fma4(c[0], v, ohj[r]); bwd_fma4(c[1], v, ohj[r + 1]); bwd_fma4(c[2], v, ohj[r + 2]); bwd_fma4(c[3], v, ohj[r + 3]);
+			}
+		} else if (is_bias) {
 			float s = bsum;
-			for (unsigned r = 0; r < TR; ++r) s += dz[r * FB + threadIdx.x];
+			for (unsigned r = 0; r < TR; ++r) s += dz[r * FB + fl];
 			bsum = s;
 		}
 	}
 	// partial[cta][(4m+1)][nf]; row 4m is dbias
 	float* out = a.partial + (size_t)blockIdx.x * (4 * m + 1) * a.nf;
-	#pragma unroll
-	for (int k = 0; k < 2; ++k) {
-		unsigned p = threadIdx.x + k * blockDim.x;
-		if (p < npair) {
-			unsigned j = p / FB, f = f0 + p % FB;
-			if (f < a.nf) {
-				out[(size_t)(4*j+0)*a.nf + f] = a0[k]; out[(size_t)(4*j+1)*a.nf + f] = a1[k];
-				out[(size_t)(4*j+2)*a.nf + f] = a2[k]; out[(size_t)(4*j+3)*a.nf + f] = a3[k];
+	if (is_unit && f0 + fl < a.nf) {
+		#pragma unroll
+		for (int t = 0; t < 4; ++t)
+			if (j0 + t < m) {
+				#pragma unroll
+				for (int k = 0; k < 4; ++k) out[(size_t)(4 * (j0 + t) + k) * a.nf + f0 + fl] = c[t][k];
 			}
-		}
 	}
-	if (threadIdx.x < FB && f0 + threadIdx.x < a.nf)
-		out[(size_t)4 * m * a.nf + f0 + threadIdx.x] = bsum;
+	if (is_bias && f0 + fl < a.nf) out[(size_t)4 * m * a.nf + f0 + fl] = bsum;
 }
 
 // Second stage: sums the per-CTA partial gradients in a fixed order.  A CTA of eight
@@ -434,15 +458,16 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	bwd_args a;
 	a.X = X; a.R = regions; a.dpooled = dpooled; a.argmax = argmax; a.actmask = actmask;
 	a.m = m; a.nf = nf; a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.ptype = ptype;
-	a.FB = nf <= 16 ? 16 : 32;
+	a.FB = nf <= 16 ? 16 : (nf <= 32 ? 32 : 64);
+	while (a.FB > 16 && ((m + 3) / 4 + 1) * a.FB > 512) a.FB /= 2;
 	unsigned nfb = divup(nf, a.FB);
 	a.G = pick_group(nregion, nfb);
-	unsigned threads = 256;
-	while (threads < 512 && 2 * threads < m * a.FB) threads *= 2;
-	DB_REQUIRE(m * a.FB <= 2 * threads, "ValueError: filter length %u is too long for the fused backward kernel", m);
+	unsigned threads = (((m + 3) / 4 + 1) * a.FB + 31u) & ~31u;       // one thread per (four taps, filter) and per bias column
+	DB_REQUIRE(threads <= 512, "ValueError: filter length %u is too long for the fused backward kernel", m);
+	if (threads < 128) threads = 128;
 	unsigned ncta = divup(nregion, a.G);
 	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
-	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + (size_t)(TR + m) * 16 + 16;
+	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + (size_t)(TR + m + 4) * 16 + (size_t)TR * 4 + 16;
 	DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
