@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--chunk", type=int, default=16384, help="sequences per launch of the FP32 variant")
     ap.add_argument("--variant", default="f16x2", choices=["f16x2", "bf16x3", "bf16x2", "f16", "bf16", "f32"],
                     help="arithmetic of the scan: 16-bit weight pieces on tcgen05 (f16x2, bf16x3 = fp32-grade) or FP32 lookup-add")
+    ap.add_argument("--gather-chunks", type=int, default=8, help="several GPUs: chunks of the shard whose all-gather overlaps the scan")
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the short runs of the other benchmark configurations")
@@ -53,7 +54,7 @@ def config(args, world):
     return {"workload": "many-model genome scan: %d models x %d motifs x %d taps, %d-nt uniform ACGT, max+avg pooling, "
                         "linear head, score matrix [nseq, %d]" % (args.nmodel, NMOTIF, M, L, args.nmodel),
             "nseq_per_gpu": args.nseq, "global_nseq": args.nseq * world, "nmodel": args.nmodel,
-            "parallelism": "sequences sharded over %d GPU(s), NCCL all-gather of score shards" % world,
+            "parallelism": "sequences sharded over %d GPU(s), NCCL all-gather of score shards%s" % (world, " in %d chunks overlapped with the scan" % args.gather_chunks if world > 1 else ""),
             "l2": "working set per step (input + score matrix) exceeds the 126 MB L2; no explicit flush"}
 
 
@@ -264,7 +265,7 @@ def main():
         return
     import torch
     import torch.distributed as dist
-    from deepbind_b200 import _lib, fused, synth
+    from deepbind_b200 import _lib, fused, shard, synth
     from deepbind_b200.model import DeepBindNet
 
     rank = int(os.environ.get("RANK", "0"))
@@ -275,6 +276,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"           # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     dll = _lib.load()
 
@@ -304,7 +307,21 @@ def main():
         else:
             net.score_chunked(X, R, scores, args.chunk)
 
+    # Several GPUs: the shard is scored in chunks and every chunk's all-gather (NCCL, its own
+    # stream) runs while the next chunk is scored; `gathered_chunks` is chunk-major, rank-major
+    # inside a chunk (shard.gathered_rows gives the flat order).
+    gathered_chunks = None
+    if world > 1 and nsplit:
+        gathered_chunks = [gathered[world * lo:world * hi] for lo, hi in
+                           (shard.shard_range(nseq, c, args.gather_chunks) for c in range(args.gather_chunks))]
+
+    def score_rows(lo, hi):
+        net.score_tc(X, R[lo:hi], check=False, out=scores[lo:hi], status=status)
+
     def step():
+        if gathered_chunks is not None:
+            shard.chunked_gather(score_rows, scores, gathered_chunks)
+            return
         score()
         if world > 1:
             dist.all_gather_into_tensor(gathered, scores)

@@ -31,6 +31,40 @@ def region_shard(R, lo, hi, m):
     return row_lo, row_hi
 
 
+def chunked_gather(produce, local, out_chunks, group=None):
+    """Computes a score shard in chunks and gathers each chunk while the next one is
+    being computed.
+
+    ``produce(lo, hi)`` enqueues, on the current stream, the work that fills
+    ``local[lo:hi]``; ``out_chunks[c]`` ([world * rows_c, ...], rows_c from
+    ``shard_range(len(local), c, len(out_chunks))``) receives chunk c of every rank,
+    rank-major.  Each all-gather is started asynchronously right after its chunk
+    was enqueued, so on NCCL it waits for that chunk only and overlaps the chunks
+    that follow; the current stream waits for all of them at the end.
+    :func:`gathered_rows` puts the chunks back into rank-major row order."""
+    nchunk, n = len(out_chunks), local.shape[0]
+    works = []
+    for c in range(nchunk):
+        lo, hi = shard_range(n, c, nchunk)
+        produce(lo, hi)
+        works.append(dist.all_gather_into_tensor(out_chunks[c], local[lo:hi], group=group, async_op=True))
+    for w in works:
+        w.wait()
+
+
+def gathered_rows(out_chunks, n, world):
+    """[world * n, ...] in rank-major row order from the chunk-major buffers of
+    :func:`chunked_gather` (a copy; scoring code can also index the chunks directly:
+    row i of rank r lies in chunk c at row r * rows_c + (i - lo_c))."""
+    nchunk = len(out_chunks)
+    parts = []
+    for r in range(world):
+        for c in range(nchunk):
+            lo, hi = shard_range(n, c, nchunk)
+            parts.append(out_chunks[c][r * (hi - lo):(r + 1) * (hi - lo)])
+    return torch.cat(parts)
+
+
 def gather_scores(local, group=None):
     """All ranks' score shards [n_r, I] -> [sum n_r, I] on every rank.  Shards may
     differ in length by one row (shard_range); shorter ones are padded for the

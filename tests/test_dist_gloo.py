@@ -78,3 +78,34 @@ def test_host_failure_reaches_the_peer(tmp_path):
     for r in range(2):
         st = np.load(os.path.join(str(tmp_path), "status_%d.npy" % r))
         assert st[0] == "ok" and st[1].startswith("error: injected host failure")
+
+
+def _chunk_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from deepbind_b200 import shard
+    n, I, nchunk = 10, 3, 3                                  # chunks of 4, 3, 3 rows
+    src = torch.arange(n * I, dtype=torch.float32).reshape(n, I) + 1000 * rank
+    local = torch.zeros_like(src)
+    calls = []
+
+    def produce(lo, hi):                                     # the "kernel": fills one chunk of the shard
+        calls.append((lo, hi))
+        local[lo:hi] = src[lo:hi]
+    outs = [torch.empty((world * (hi - lo), I)) for lo, hi in (shard.shard_range(n, c, nchunk) for c in range(nchunk))]
+    shard.chunked_gather(produce, local, outs)
+    full = shard.gathered_rows(outs, n, world)
+    np.save(os.path.join(out_dir, "chunked_%d.npy" % rank), full.numpy())
+    np.save(os.path.join(out_dir, "calls_%d.npy" % rank), np.array(calls))
+    dist.destroy_process_group()
+
+
+def test_chunked_gather_overlap_order(tmp_path):
+    """Chunk-by-chunk gather of two ranks' shards gives the rank-major matrix."""
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_chunk_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    want = np.concatenate([np.arange(30, dtype=np.float32).reshape(10, 3) + 1000 * r for r in range(2)])
+    for r in range(2):
+        assert np.array_equal(np.load(os.path.join(str(tmp_path), "chunked_%d.npy" % r)), want)
+        assert np.load(os.path.join(str(tmp_path), "calls_%d.npy" % r)).tolist() == [[0, 4], [4, 7], [7, 10]]
