@@ -26,6 +26,9 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+# stdout carries one JSON line only: keep NCCL's version banner off it (set before anything loads NCCL)
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 M, NMOTIF, L = 24, 16, 101
 UNIT = "sequences/s"
@@ -258,6 +261,57 @@ def side_workloads(dev, with_cpu):
     return out
 
 
+def calibration_sharded(dev, rank, world):
+    """Config 3 over several GPUs: the 90 independent models of the calibration sweep are
+    dealt to the ranks round robin (as hypertrain deals its samples to worker processes),
+    every rank trains its own models on the same resident 40-nt data, CUDA-graph replay,
+    and the only exchange is the all-gather of the per-model loss vector at the end.
+    Time = CUDA events on every rank, maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    from deepbind_b200 import shard, synth
+    from deepbind_b200.model import DeepBindNet
+    NMODEL, B, Lc, nbatch, reps = 90, 64, 40, 64, 100
+    ids = shard.shard_models(NMODEL, rank, world)
+    I = len(ids)
+    g = synth.rng(32)
+    p = synth.model_params(I, M, 31 + rank, "max")
+    Xh, Rh = synth.uniform_batch(B * nbatch, Lc, M, seed=33)
+    rows = B * (Lc + M - 1)
+    Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(M - 1, 255, np.uint8)])
+                                      for i in range(nbatch)])).to(dev)
+    R1 = torch.from_numpy(Rh[:B].view(np.int32)).to(dev)
+    Yall = torch.from_numpy(np.tile(g.standard_normal((nbatch, B, 1)).astype(np.float32), (1, 1, I))).to(dev)
+    lr_all = np.exp(g.uniform(np.log(1e-4), np.log(1e-1), NMODEL)).astype(np.float32)
+    net = DeepBindNet(p, I, "max", loss="mse")
+    net.set_rates(lr_all[ids], 0.9)
+    Xs, Ys = Xall[0].clone(), Yall[0].clone()
+    graph, loss = net.capture_train_step(Xs, R1, Ys, None)
+    nmax = (NMODEL + world - 1) // world
+    mine = torch.zeros(nmax, dtype=torch.float32, device=dev)
+    everyone = torch.empty(world * nmax, dtype=torch.float32, device=dev)
+
+    def run(n):
+        for s in range(n):
+            i = s % nbatch
+            Xs.copy_(Xall[i]); Ys.copy_(Yall[i])
+            graph.replay()
+        mine[:I] = loss.view(-1)[:I]
+        dist.all_gather_into_tensor(everyone, mine)
+    run(5)
+    dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); run(reps); e1.record()
+    dist.barrier(); torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    finite = bool(torch.isfinite(everyone.view(world, nmax)[rank, :I]).all().item())
+    return {"unit": "train samples/s (model x sample)", "value": NMODEL * B / ms * 1e3, "ms_per_step": ms, "models": NMODEL,
+            "models_per_gpu": [NMODEL // world, nmax], "minibatch": B, "losses_finite": finite,
+            "parallelism": "models dealt round robin to %d GPUs, no gradient exchange; all-gather of the loss vector" % world}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -276,8 +330,6 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"           # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     dll = _lib.load()
 
@@ -406,6 +458,7 @@ def main():
                     "peak_source": "SMs x 32 table operands/clk x max SM clock (shared-memory return path, one 4-byte operand "
                                    "per add); FP32 add issue would be 4x this", "traffic": None, "ms_per_launch": kernel_ms}
 
+    calib = calibration_sharded(dev, rank, world) if (world > 1 and not args.no_side) else None
     if rank == 0:
         line = {"metric": METRIC, "value": nseq * world * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
@@ -422,6 +475,8 @@ def main():
             del X, R, scores, X_host, R_host, out_host
             torch.cuda.empty_cache()
             line["other_configs"] = side_workloads(dev, not args.no_cpu_baseline)
+        if calib is not None:
+            line["other_configs"] = {"calibration": calib}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
