@@ -101,6 +101,7 @@ _PROTOTYPES = {
     "db_head_train": (None, [c_uint32, c_uint32, c_uint32, c_int, c_uint32, P, P, P, P, P, P, P, P, P, P, P, P, P]),
     "db_batch_bytes": (c_size_t, [c_uint32, c_size_t, c_uint32, c_int]),
     "db_build_batch": (None, [P, P, c_uint32, c_uint32, c_int, P, P]),
+    "db_build_windows": (None, [P, P, P, c_uint32, c_uint32, c_uint32, c_uint32, c_uint32, c_int, P, P]),
     "db_scanpool_fwd": (None, [P, c_uint32, c_uint32, P, c_int, P, c_uint32, P, c_uint32, c_int, P, P, P]),
     "db_scanpool_bwd": (None, [c_uint32, c_uint32, P, c_uint32, P, c_uint32, c_int, P, P, P, P, P]),
     "db_tc_weights_bytes": (c_size_t, [c_uint32, c_uint32, c_int]),

@@ -91,6 +91,50 @@ def build_batch(seqs, padding, reverse_complement=False, device="cuda"):
     return X, R
 
 
+def _upload_text(seqs, device):
+    import numpy as np
+    nseq = len(seqs)
+    raw = "".join(seqs).encode("latin-1")
+    lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=nseq)
+    off_h = np.zeros(nseq + 1, dtype=np.int64)
+    np.cumsum(lens, out=off_h[1:])
+    text = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device) if raw else torch.empty(0, dtype=torch.uint8, device=device)
+    return text, torch.from_numpy(off_h.astype(np.int32)).to(device), lens
+
+
+def window_counts(lens, windowsize, stride):
+    """Windows per sequence in scan mode: every ``stride``-th start in the sequence
+    padded with windowsize-1 'N' on both sides (predict.py:281-284)."""
+    import numpy as np
+    lens = np.asarray(lens, dtype=np.int64)
+    return (np.maximum(1, lens + windowsize - 1) + stride - 1) // stride
+
+
+def build_windows(seqs, windowsize, stride, padding, reverse_complement=False, device="cuda"):
+    """Scan-mode minibatch of sequence strings: every window of every sequence as a
+    row -> (X uint8, R int32 [nrow, 2], window_offsets int64 numpy [nseq+1]), built by
+    one kernel from the uploaded characters (the reference expands the windows as
+    Python strings, predict.py:270-285)."""
+    import numpy as np
+    if windowsize == 1 and any(len(s) == 0 for s in seqs):
+        raise ValueError("scan mode with windows of one character needs non-empty sequences")
+    text, off, lens = _upload_text(seqs, device)
+    nwin = window_counts(lens, windowsize, stride)
+    woff_h = np.zeros(len(seqs) + 1, dtype=np.int64)
+    np.cumsum(nwin, out=woff_h[1:])
+    total = int(woff_h[-1])
+    dll = _dll()
+    rc = int(bool(reverse_complement))
+    nbytes = dll.db_batch_bytes(total, total * windowsize, padding, rc)
+    if nbytes >= 2 ** 32:
+        raise ValueError("a minibatch is addressed with 32-bit positions; split it")
+    woff = torch.from_numpy(woff_h.astype(np.int32)).to(device)
+    X = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    R = torch.empty((total * (2 if rc else 1), 2), dtype=torch.int32, device=device)
+    dll.db_build_windows(_ptr(text), _ptr(off), _ptr(woff), len(seqs), total, windowsize, stride, padding, rc, _ptr(X), _ptr(R))
+    return X, R, woff_h
+
+
 TC_PRECISION = {"bf16": 1, "bf16x2": 2, "bf16x3": 3, "f16x2": 4, "f16": 5}
 TC_PIECES = {1: 1, 2: 2, 3: 3, 4: 2, 5: 1}     # 16-bit operand pieces per weight = tensor-core passes
 

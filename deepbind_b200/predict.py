@@ -1,0 +1,65 @@
+"""Scoring driver with the semantics of ``kangaroo.predict``.
+
+Direct mode scores every sequence once (predict.py:168-196); scan mode
+(predict.py:262-345, 434-452) slides a window along each sequence, scores every
+window as a sequence of its own and reports the maximum, mean and sum of each
+sequence's prediction map.  All models of a :class:`DeepBindNet` are scored in
+the same pass (the reference runs one worker process per model,
+predict.py:466-508).  Batch assembly, window expansion, scan, pooling, head,
+strand choice and the per-sequence reductions run on the device; the host only
+uploads the characters.
+"""
+import numpy as np
+import torch
+
+from . import fused
+from . import kangaroo_smat as ks
+from . import smat as sm
+
+
+def _score(net, X, R, reverse_complement):
+    return net.score(X, R, strand_max=bool(reverse_complement))
+
+
+def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps=False, max_windows=1 << 21):
+    """Scores the sequence strings ``seqs`` with every model of ``net``.
+
+    Returns a dict of CUDA tensors [nseq, I]: ``direct``; with ``scan`` = window
+    size also ``max``, ``avg``, ``sum`` over each sequence's windows, and ``pmaps``
+    (a list of [nwindow_b, I] tensors, one per sequence) if ``want_pmaps``.  With
+    ``reverse_complement`` both strands are scored and the larger score is kept,
+    the forward strand on ties (predict.py:145-164).  Sequences are processed in
+    groups of at most ``max_windows`` windows."""
+    seqs = list(seqs)
+    pad = net.m - 1
+    dev = net.dev
+    X, R = fused.build_batch(seqs, pad, reverse_complement, device=dev)
+    out = {"direct": _score(net, X, R, reverse_complement)}
+    if not scan:
+        return out
+    lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=len(seqs))
+    nwin = fused.window_counts(lens, scan, stride)
+    if int(nwin.max(initial=0)) > max_windows:
+        raise ValueError("a sequence has more windows than max_windows")
+    red = {"max": [], "avg": [], "sum": []}
+    pmaps = []
+    lo = 0
+    while lo < len(seqs):
+        hi, total = lo, 0
+        while hi < len(seqs) and total + int(nwin[hi]) <= max_windows:
+            total += int(nwin[hi]); hi += 1
+        Xw, Rw, woff = fused.build_windows(seqs[lo:hi], scan, stride, pad, reverse_complement, device=dev)
+        Z = _score(net, Xw, Rw, reverse_complement).contiguous()            # [windows, I]: the prediction maps, stacked
+        # per-sequence reductions = region pooling over the rows of Z
+        regions = sm.asarray(np.stack([woff[:-1], woff[1:]], axis=1).astype(np.uint32))
+        Zs = sm.sarray(Z, np.float32)
+        for kind in red:
+            red[kind].append(ks.poolrgn(Zs, regions, kind)[0].tensor)
+        if want_pmaps:
+            pmaps.extend(Z[int(woff[i]):int(woff[i + 1])] for i in range(hi - lo))
+        lo = hi
+    for kind in red:
+        out[kind] = torch.cat(red[kind]) if red[kind] else torch.empty((0, net.I), dtype=torch.float32, device=dev)
+    if want_pmaps:
+        out["pmaps"] = pmaps
+    return out

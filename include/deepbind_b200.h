@@ -167,6 +167,16 @@ void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_ki
 size_t db_batch_bytes(uint32_t nseq, size_t total_len, uint32_t pad, int reverse_complement);
 void db_build_batch(const uint8_t* text, const uint32_t* offsets, uint32_t nseq, uint32_t pad,
                     int reverse_complement, uint8_t* X, uint32_t* regions);
+/* Scan mode of kangaroo.predict (predict.py:270-285): each sequence, padded with
+ * windowsize-1 'N' on both sides, is cut into windows of `windowsize` characters
+ * every `stride` positions, and each window becomes a row of the batch (same layout
+ * as db_build_batch; every row is pad + windowsize bytes).  Sequence b has
+ * ceil(max(1, len_b + windowsize - 1) / stride) windows; window_offsets [nseq+1] is
+ * the prefix sum of these counts and nwindow its last entry.  X needs
+ * db_batch_bytes(nwindow, nwindow * windowsize, pad, reverse_complement) bytes. */
+void db_build_windows(const uint8_t* text, const uint32_t* offsets, const uint32_t* window_offsets,
+                      uint32_t nseq, uint32_t nwindow, uint32_t windowsize, uint32_t stride, uint32_t pad,
+                      int reverse_complement, uint8_t* X, uint32_t* regions);
 
 /* ---- fused hot path (no counterpart as one call; replaces the chain
  * api_corr1ord -> bias -> rectify -> api_poolrgn of corr1ord.py:97-102,

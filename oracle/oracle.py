@@ -306,6 +306,30 @@ def asbatch(seqs, padding, reverse_complement=False):
     return X, R
 
 
+def scan_windows(seq, windowsize, stride=1):
+    """kangaroo/predict.py:281-284: the windows of one sequence in scan mode."""
+    padseq = "N" * (windowsize - 1) + seq + "N" * (windowsize - 1)
+    return [padseq[i:i + windowsize] for i in range(0, max(1, len(padseq) - windowsize + 1), stride)]
+
+
+def predict(params, seqs, m, pool="max", nmodel=1, scan=None, stride=1, reverse_complement=False):
+    """kangaroo/predict.py:168-196, 262-300, 434-452: direct scores, and in scan mode
+    the per-sequence prediction maps with their max / mean / sum (NumPy reductions,
+    as the reference takes them)."""
+    X, R = asbatch(seqs, m - 1, reverse_complement)
+    out = {"direct": score_net(params, X, R, pool, nmodel, strand_max=reverse_complement)}
+    if scan:
+        pmaps = []
+        for s in seqs:
+            Xw, Rw = asbatch(scan_windows(s, scan, stride), m - 1, reverse_complement)
+            pmaps.append(score_net(params, Xw, Rw, pool, nmodel, strand_max=reverse_complement))
+        out["pmaps"] = pmaps
+        out["max"] = np.stack([p.max(axis=0) for p in pmaps])
+        out["avg"] = np.stack([p.mean(axis=0) for p in pmaps])
+        out["sum"] = np.stack([p.sum(axis=0) for p in pmaps])
+    return out
+
+
 # -------------------------------------------------------- composite networks
 def logistic(x):
     return 1.0 / (1.0 + np.exp(-x))

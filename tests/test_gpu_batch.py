@@ -60,3 +60,19 @@ def test_built_batch_scores_like_the_host_built_one(cuda, orc):
     hX, hR = orc.asbatch(seqs, m - 1, True)
     want, _ = orc.scanpool(W, b, True, hX, hR, "all")
     assert np.array_equal(got.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("rc", [False, True])
+@pytest.mark.parametrize("nseq,lmin,lmax,W,stride,pad", [(1, 30, 30, 20, 1, 23), (12, 1, 90, 20, 1, 15), (40, 5, 300, 33, 7, 23),
+                                                        (7, 0, 10, 20, 3, 23), (5, 50, 60, 1, 1, 4), (9, 10, 40, 64, 64, 0)])
+def test_windows_equal_oracle(cuda, orc, nseq, lmin, lmax, W, stride, pad, rc):
+    """Scan-mode window expansion: byte for byte the batch the reference's string slicing gives."""
+    from deepbind_b200 import fused
+    rng = np.random.default_rng(nseq * 7 + W + stride + rc)
+    seqs = random_seqs(rng, nseq, max(lmin, 1 if W == 1 else 0), lmax)
+    windows = [w for s in seqs for w in orc.scan_windows(s, W, stride)]
+    wantX, wantR = orc.asbatch(windows, pad, rc)
+    X, R, woff = fused.build_windows(seqs, W, stride, pad, rc)
+    assert woff.tolist() == np.concatenate([[0], np.cumsum([len(orc.scan_windows(s, W, stride)) for s in seqs])]).tolist()
+    assert np.array_equal(X.cpu().numpy(), wantX)
+    assert np.array_equal(R.cpu().numpy().view(np.uint32), wantR)

@@ -281,3 +281,14 @@ def test_strand_max_keeps_forward_on_ties(orc):
     s = orc.score_net(p, X, R, "max", 1, strand_max=True)
     both = orc.score_net(p, X, R, "max", 1)
     assert both[0, 0] == both[1, 0] == s[0, 0]
+
+
+def test_scan_mode_windows(orc):
+    """predict.py:281-284: W-1 'N' on both sides, every stride-th window of W characters."""
+    assert orc.scan_windows("ACGT", 3) == ["NNA", "NAC", "ACG", "CGT", "GTN", "TNN"]
+    assert orc.scan_windows("ACGT", 3, stride=4) == ["NNA", "GTN"]
+    assert orc.scan_windows("A", 1) == ["A"]
+    assert orc.scan_windows("", 3) == ["NNN", "NNN"]            # len(padseq) - W + 1 = 2 starts
+    from deepbind_b200 import fused
+    for L, W, s in [(4, 3, 1), (4, 3, 4), (1, 1, 1), (0, 3, 1), (37, 20, 7), (5, 64, 64)]:
+        assert int(fused.window_counts([L], W, s)[0]) == len(orc.scan_windows("A" * L, W, s))
