@@ -38,6 +38,8 @@ struct error : std::runtime_error {
 // Binds the calling thread's device on first use and caches its SM count.
 void ensure_device();
 void* scratch(size_t bytes);   // stream-ordered use only; grows with cudaMalloc
+// FP32 motif scan writing Z [n, nf] (scanpool_f32.cu); n = rows written, X holds n + m - 1 bytes
+void launch_corr1ord_f32(const float* W, unsigned m, unsigned nf, const uint8_t* X, unsigned n, float* Z);
 
 inline void cuda_check(cudaError_t e, const char* what, const char* file, int line)
 {

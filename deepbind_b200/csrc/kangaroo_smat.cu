@@ -291,7 +291,7 @@ DB_EXPORT void api_corr1ord(const smat* W, const smat* X, smat* Z, const corr1or
 	unsigned m = W->shape.y / nchannel, nf = W->shape.x;
 	if (size_of(X) < m) return;                      // no complete window: nothing is written
 	unsigned n = (unsigned)size_of(X) - m + 1;      // rows actually written (kangaroo_smat.cpp:105)
-	if (Z->dtype == DB_F32) launch_corr1ord((const float*)W->data, m, nf, (const uint8_t*)X->data, n, (float*)Z->data);
+	if (Z->dtype == DB_F32) launch_corr1ord_f32((const float*)W->data, m, nf, (const uint8_t*)X->data, n, (float*)Z->data);
 	else                    launch_corr1ord((const double*)W->data, m, nf, (const uint8_t*)X->data, n, (double*)Z->data);
 	DB_API_CATCH
 }

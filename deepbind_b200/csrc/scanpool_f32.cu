@@ -198,6 +198,78 @@ scanpool_fwd_kernel(const fwd_args a)
 	}
 }
 
+// ------------------------------------------------- the scan alone (api_corr1ord)
+// The same row scan, writing Z [n, nf] instead of pooling it: what the unfused
+// operator needs.  A thread owns one row x 16 filters and stores its 64 bytes of Z
+// with four 16-byte stores; a CTA keeps its lookup table and walks the row tiles.
+struct corr_args {
+	const float* W; const uint8_t* X; float* Z;
+	unsigned m, nf, npos, n, FB;
+	int vec;                     // Z rows are 16-byte aligned at every 16-filter group
+};
+
+template <int M>
+__global__ void __launch_bounds__(512)
+corr1ord_f32_kernel(const corr_args a)
+{
+	extern __shared__ __align__(16) unsigned char smem[];
+	const unsigned m = M > 0 ? (unsigned)M : a.m;
+	const unsigned FB = a.FB, NQ = FB / 4;
+	float* lut = reinterpret_cast<float*>(smem);                       // m*NQ*32 floats
+	uint8_t* xs = reinterpret_cast<uint8_t*>(lut + (size_t)m * NQ * 32);      // TR + m + 8 bytes (4-aligned)
+	const unsigned f0 = blockIdx.y * FB;
+	build_lut(lut, a.W, m, a.nf, f0, FB);
+	const unsigned rl = threadIdx.x % TR, fg = threadIdx.x / TR;
+	const unsigned char* lutp = reinterpret_cast<const unsigned char*>(lut) + fg * 512;
+	const unsigned stride = NQ * 128;
+	const unsigned fbase = f0 + fg * 16;
+	for (unsigned t0 = blockIdx.x * TR; t0 < a.n; t0 += gridDim.x * TR) {
+		__syncthreads();
+		for (unsigned t = threadIdx.x; t < TR + m + 3; t += blockDim.x) {
+			unsigned i = t0 + t;
+			xs[t] = (uint8_t)(i < a.npos ? code16_of(a.X[i]) : 80u);
+		}
+		__syncthreads();
+		const unsigned row = t0 + rl;
+		if (row < a.n && fbase < a.nf) {
+			float z[16];
+			scan_row<M>(lutp, stride, xs, rl, m, z);
+			float* out = a.Z + (size_t)row * a.nf + fbase;
+			if (a.vec && fbase + 16 <= a.nf) {
+				#pragma unroll
+				for (int v = 0; v < 16; v += 4)
+					reinterpret_cast<float4*>(out)[v / 4] = make_float4(z[v], z[v + 1], z[v + 2], z[v + 3]);
+			} else {
+				#pragma unroll
+				for (int v = 0; v < 16; ++v)
+					if (fbase + v < a.nf) out[v] = z[v];
+			}
+		}
+	}
+}
+
+void launch_corr1ord_f32(const float* W, unsigned m, unsigned nf, const uint8_t* X, unsigned n, float* Z)
+{
+	if (n == 0 || nf == 0 || m == 0) return;
+	corr_args a;
+	a.W = W; a.X = X; a.Z = Z; a.m = m; a.nf = nf; a.n = n; a.npos = n + m - 1;
+	a.FB = nf <= 16 ? 16 : (nf <= 32 ? 32 : 64);
+	while (a.FB > 16 && (size_t)m * a.FB * 32 > 120 * 1024) a.FB /= 2;
+	DB_REQUIRE((size_t)m * a.FB * 32 <= 160 * 1024, "ValueError: filter length %u is too long for this kernel", m);
+	a.vec = (nf % 4 == 0) && (((uintptr_t)Z & 15) == 0);
+	size_t smem = (size_t)m * a.FB * 32 + TR + m + 16;
+	unsigned tiles = divup(n, (unsigned)TR);
+	dim3 grid(std::min(tiles, (unsigned)state().sm_count * 4), divup(nf, a.FB)), block(TR * a.FB / 16);
+	auto launch = [&](auto kern) {
+		DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+		kern<<<grid, block, smem, state().stream>>>(a);
+	};
+	if (m == 24) launch(corr1ord_f32_kernel<24>);
+	else if (m == 16) launch(corr1ord_f32_kernel<16>);
+	else launch(corr1ord_f32_kernel<0>);
+	DB_LAUNCH_CHECK();
+}
+
 // --------------------------------------------------------------- backward
 // dZ[i,f] = active(i,f) ? (mean share of region(i) + (i is argmax ? max delta : 0)) : 0
 // (poolrgn_bprop.cuh:45-127 then elemwise.py:78), dbias = column sums of dZ
