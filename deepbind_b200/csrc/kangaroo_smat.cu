@@ -205,7 +205,22 @@ __global__ void poolrgn_kernel(const T* __restrict__ U, unsigned nf, const uint3
 	T x = U[(size_t)first * nf + f];
 	T y = x;
 	unsigned xi = first;
-	for (unsigned row = first + step; row < last; row += step) {
+	unsigned row = first + step;
+	if (step == 1) {
+		// eight independent loads in flight per thread, then the reduction in row order
+		const T* u = U + (size_t)row * nf + f;
+		for (; row + 8 <= last; row += 8, u += (size_t)8 * nf) {
+			T v[8];
+			#pragma unroll
+			for (int k = 0; k < 8; ++k) v[k] = u[(size_t)k * nf];
+			#pragma unroll
+			for (int k = 0; k < 8; ++k) {
+				if (v[k] > x) { x = v[k]; xi = row + k; }
+				y += v[k];
+			}
+		}
+	}
+	for (; row < last; row += step) {
 		T v = U[(size_t)row * nf + f];
 		if (v > x) { x = v; xi = row; }
 		y += v;
