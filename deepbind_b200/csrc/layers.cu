@@ -21,6 +21,15 @@ __global__ void relu_kernel(float* Z, const float* X, size_t n)
 }
 
 // dZ * sign(Z) with Z the rectified output, so the factor is 0 or 1 (elemwise.py:78).
+__global__ void l1_decay_kernel(float* __restrict__ dP, const float* __restrict__ P, const float* __restrict__ decay, size_t n)
+{
+	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+		const float p = P[i];
+		const float s = p > 0.f ? 1.f : (p < 0.f ? -1.f : 0.f);
+		dP[i] = dP[i] + decay[i] * s;          // the product is exact (s is -1, 0 or 1): one rounding, fused or not
+	}
+}
+
 __global__ void relu_bprop_kernel(float* dX, const float* dZ, const float* Z, size_t n)
 {
 	GRID_STRIDE(i, n) { float z = Z[i]; dX[i] = dZ[i] * (z > 0.0f ? 1.0f : (z < 0.0f ? -1.0f : 0.0f)); }
@@ -120,6 +129,19 @@ DB_EXPORT void db_relu_bprop(float* dX, const float* dZ, const float* Z, size_t 
 	if (!n) return;
 	DB_REQUIRE(dX && dZ && Z, "ValueError: db_relu_bprop got a NULL pointer");
 	relu_bprop_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(dX, dZ, Z, n);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+// L1 weight decay of the reference's trainable layers (corr1ord.py:112-126,
+// full.py:102-119): dW += decay * sign(W), with the per-model decay already spread
+// over the flat parameter vector (zero on biases), as the rates are.
+DB_EXPORT void db_l1_decay(float* dP, const float* P, const float* decay, size_t n)
+{
+	DB_API_TRY
+	if (!n) return;
+	DB_REQUIRE(dP && P && decay, "ValueError: db_l1_decay got a NULL pointer");
+	l1_decay_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(dP, P, decay, n);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }

@@ -19,6 +19,7 @@ import torch
 from . import _lib, fused
 from . import deepity_smat as dsm
 from .smat import sarray, bind_stream
+from .smat import asarray as sm_asarray
 
 ORDER = ("Wscan", "bscan", "W1", "b1", "W2", "b2")
 
@@ -49,8 +50,42 @@ class DeepBindNet(object):
         self.drate = torch.zeros(n, dtype=torch.float32, device=self.dev)
         self.mrate = torch.zeros(n, dtype=torch.float32, device=self.dev)
         self._s = {k: _as_f32(getattr(self, k)) for k in ("P", "dP", "mP", "drate", "mrate")}
+        self.decay = None                 # per-element L1 decay (set_decay); applied while decay_on
+        self.decay_on = False
+        self.dropout_rate = None          # per-model dropout rate of the pooled features (set_dropout)
 
     # ------------------------------------------------------------- parameters
+    def _spread(self, vec, name, values, k=None):
+        """vec[block of `name`] += values[model], model-wise, with madd_bcast as
+        sgd.py:322-329 does (instance axis 0 for dense weights, 1 elsewhere)."""
+        shp = self.shapes[name]
+        inst_axis0 = name in ("W1", "W2")
+        if k is None:
+            k = int(np.prod(shp)) // self.I if inst_axis0 else (shp[-1] // self.I)
+        i = self.names.index(name)
+        seg = vec[int(self.offsets[i]):int(self.offsets[i + 1])]
+        dsm.madd_bcast(_as_f32(torch.ones_like(seg)), np.array(values, np.float32), k, _as_f32(seg))
+
+    def set_decay(self, decay):
+        """L1 weight decay per model: ``decay`` maps a weight block ("Wscan", "W1",
+        "W2") to a scalar or [I] array; biases are not decayed (corr1ord.py:112-126,
+        full.py:102-119).  The term is added by grads() while ``decay_on`` is True
+        (the trainer switches it on at ``weight_decay_start``).  For the filter bank
+        the reference spreads the per-model values with k = rows / ninst
+        (corr1ord.py:126), which with several models does not follow the
+        model-major column layout; the same k is used here so that results agree."""
+        self.decay = torch.zeros_like(self.P)
+        for name, val in decay.items():
+            if name in self.names and val is not None:
+                k = max(1, self.shapes[name][0] // self.I) if name == "Wscan" else None
+                self._spread(self.decay, name, np.broadcast_to(np.asarray(val, np.float32), (self.I,)), k)
+
+    def set_dropout(self, rate):
+        """Dropout rate of the pooled features, scalar or one per model.  Training
+        masks are drawn by the trainer; scoring multiplies the pooled features by
+        1 - rate instead (elemwise.py:128-150: no rescaling while training)."""
+        rate = np.broadcast_to(np.asarray(rate, np.float32), (self.I,)).copy()
+        self.dropout_rate = rate if np.any(rate > 0) else None
     def view(self, name, of="P"):
         i = self.names.index(name)
         t = getattr(self, of)[int(self.offsets[i]):int(self.offsets[i + 1])]
@@ -91,13 +126,19 @@ class DeepBindNet(object):
         dll.db_bias_add(out.data_ptr(), out.data_ptr(), b2.data_ptr(), out.shape[0], out.shape[1])
         return out, h1, a1
 
+    def _test_dropout(self, pooled):
+        """Scoring with a dropout layer: Z = X * (1 - rate[model]) (dropout.cu:64-75)."""
+        if self.dropout_rate is None:
+            return pooled
+        return dsm.dropout_fp_test(_as_f32(pooled), sm_asarray(self.dropout_rate)).tensor
+
     def score(self, X, R, strand_max=False):
         """Scores [nseq, I] (no output non-linearity).  With strand_max, rows are
         fwd/rc pairs and the larger score of each pair is kept, forward on ties
         (code/libs/kangaroo/kangaroo/predict.py:145-164)."""
         bind_stream()
         pooled, _, _ = fused.scanpool(self.view("Wscan"), self.view("bscan").view(-1), X, R, self.pool, relu=True)
-        out, _, _ = self._head(pooled)
+        out, _, _ = self._head(self._test_dropout(pooled))
         if strand_max:
             out = out.view(-1, 2, self.I)
             out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
@@ -107,7 +148,14 @@ class DeepBindNet(object):
     def grads(self, X, R, Y, dropmask=None):
         """Fills dP with the gradient of the mean loss at P; returns loss [I].
         Y is [B, I] f32; dropmask (optional, bool [B, npool*I]) is the dropout
-        keep-mask applied to the pooled features."""
+        keep-mask applied to the pooled features.  While ``decay_on`` is set, the L1
+        weight-decay term decay * sign(W) is added (set_decay)."""
+        lossv = self._grads(X, R, Y, dropmask)
+        if self.decay_on and self.decay is not None:
+            _lib.load().db_l1_decay(self.dP.data_ptr(), self.P.data_ptr(), self.decay.data_ptr(), self.P.numel())
+        return lossv
+
+    def _grads(self, X, R, Y, dropmask=None):
         bind_stream()
         I = self.I
         dll = _lib.load()
@@ -186,12 +234,12 @@ class DeepBindNet(object):
         head is applied inside the kernel and no pooled features reach HBM."""
         bind_stream()
         tcw = getattr(self, "_tcw", None) or self.prepare_tc()
-        if not self.hidden and self.nf == 16 * self.I:
+        if not self.hidden and self.nf == 16 * self.I and self.dropout_rate is None:
             _, out = fused.scanpool_tc(tcw, X, R, self.pool, headW=self.view("W1").reshape(-1),
                                        headB=self.view("b1").view(-1), check=check, scores_out=out, status=status)
         else:
             pooled, _ = fused.scanpool_tc(tcw, X, R, self.pool, check=check)
-            out, _, _ = self._head(pooled)
+            out, _, _ = self._head(self._test_dropout(pooled))
         if strand_max:
             out = out.view(-1, 2, self.I)
             out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])

@@ -1,0 +1,137 @@
+"""Minibatch trainer with the semantics of ``deepity.sgd``.
+
+Nesterov momentum steps on the flat parameter vector of a
+:class:`deepbind_b200.model.DeepBindNet` holding any number of independent
+model instances, each with its own learning rate, momentum, dropout rate and
+L1 weight decay (code/libs/deepity/deepity/sgd.py:87-163,287-354):
+
+* minibatches are assembled once, up-front, and visited cyclically without
+  reshuffling (sgd.py:92, ``asbatches(reshuffle=False)``);
+* ``max_steps = min(max_steps, max_epochs * nbatch)`` and the checkpoint steps
+  are ``max_steps * k / checkpoints`` (sgd.py:117-118);
+* the L1 decay term is added from step ``weight_decay_start`` on
+  (corr1ord.py:112-115, full.py:102-119);
+* dropout draws one mask per step and model from the library's generator
+  (``api_dropout_fp_tr``), or from uniform draws the caller supplies, which makes
+  a run reproducible against the CPU restatement.
+
+Batches, masks, forward, backward and update all run on the device; when every
+minibatch has the same size the step is replayed from a CUDA graph.  Training
+on both strands (loss masked to the stronger strand) is not built.
+"""
+import numpy as np
+import torch
+
+from . import _lib, cfg, fused
+from . import deepity_smat as dsm
+from . import smat as sm
+
+
+def _per_model(value, rng, I):
+    if isinstance(value, cfg.paramdef):
+        return np.asarray(value.sample(rng, I), np.float32)
+    return np.broadcast_to(np.asarray(value, np.float32), (I,)).copy()
+
+
+class Trainer(object):
+    def __init__(self, net, spec=None, seed=0):
+        """``spec``: a :class:`deepbind_b200.cfg.sgd` (ranges are drawn once per model)."""
+        self.net, self.spec = net, spec or cfg.sgd()
+        rng = np.random.default_rng(seed)
+        self.rate = _per_model(self.spec.rate, rng, net.I)
+        self.momentum = _per_model(self.spec.momentum, rng, net.I)
+        net.set_rates(self.rate, self.momentum)
+        self.step = 0
+        self.history = []                 # (step, mean training loss [I]) at every checkpoint
+
+    # ------------------------------------------------------------------ data
+    def make_batches(self, seqs, Y):
+        """[(X, R, Y)] on the device, ``batchsize`` sequences each (the last one may be
+        shorter).  Y [N] or [N, 1] is shared by all models; [N, I] gives one target
+        column per model."""
+        net, B = self.net, int(self.spec.batchsize)
+        Y = np.asarray(Y, np.float32).reshape(len(seqs), -1)
+        if Y.shape[1] == 1:
+            Y = np.tile(Y, (1, net.I))
+        assert Y.shape[1] == net.I, "targets must have one column, or one per model"
+        batches = []
+        for lo in range(0, len(seqs), B):
+            X, R = fused.build_batch(seqs[lo:lo + B], net.m - 1, False, device=net.dev)
+            batches.append((X, R, torch.from_numpy(np.ascontiguousarray(Y[lo:lo + B])).to(net.dev)))
+        return batches
+
+    def _mask(self, nrow, draws):
+        """Keep-mask [nrow, npool*I] of one step, or None without dropout."""
+        net = self.net
+        if net.dropout_rate is None:
+            return None
+        ones = sm.sarray(torch.ones((nrow, self._mask_cols()), dtype=torch.float32, device=net.dev), np.float32)
+        U = None if draws is None else sm.sarray(draws, np.float32)
+        _, M = dsm.dropout_fp_train(ones, sm.asarray(net.dropout_rate), False, U)
+        return M.tensor
+
+    # ------------------------------------------------------------------- loop
+    def fit(self, seqs, Y, uniform_draws=None, on_checkpoint=None, use_graph=True):
+        """Trains for the trainer's step budget; returns the loss [I] of the last step.
+
+        ``uniform_draws(step, shape)`` (optional) returns the U(0,1) draws of that
+        step's dropout mask as a CUDA f32 tensor; ``on_checkpoint(step, trainer)`` is
+        called at every checkpoint after the mean training loss was recorded."""
+        net, spec = self.net, self.spec
+        batches = self.make_batches(seqs, Y)
+        nb = len(batches)
+        max_steps = int(min(spec.max_steps, spec.max_epochs * nb))
+        checkpoints = {int(max_steps * float(k) / spec.checkpoints) for k in range(1, int(spec.checkpoints) + 1)}
+        same = all(b[0].numel() == batches[0][0].numel() and b[1].shape == batches[0][1].shape for b in batches)
+        graphs = {}
+        static = None
+        if use_graph and same and uniform_draws is None:
+            X0, R0, Y0 = batches[0]
+            static = (X0.clone(), R0.clone(), Y0.clone(), self._mask(R0.shape[0], None))
+        loss = None
+        for step in range(max_steps):
+            X, R, Yb = batches[step % nb]
+            net.decay_on = step >= spec.weight_decay_start
+            if static is not None:
+                sX, sR, sY, sM = static
+                sX.copy_(X); sY.copy_(Yb)
+                if sM is not None:
+                    sM.copy_(self._mask(R.shape[0], None))
+                key = bool(net.decay_on)
+                if key not in graphs:
+                    # the capture's warm-up steps are real steps: put the state back afterwards
+                    P0, mP0 = net.P.clone(), net.mP.clone()
+                    graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3)
+                    net.P.copy_(P0); net.mP.copy_(mP0)
+                graphs[key][0].replay()
+                loss = graphs[key][1]
+            else:
+                draws = uniform_draws(step, (R.shape[0], self._mask_cols())) if uniform_draws else None
+                loss = net.train_step(X, R, Yb, self._mask(R.shape[0], draws))
+            self.step = step + 1
+            if self.step in checkpoints:
+                self.history.append((self.step, self.evaluate(batches[:100])))
+                if on_checkpoint:
+                    on_checkpoint(self.step, self)
+        net.decay_on = False
+        return loss
+
+    def _mask_cols(self):
+        net = self.net
+        return (net.nf // net.I) * (2 if net.pool == "all" else 1) * net.I
+
+    def evaluate(self, batches):
+        """Mean loss [I] over the batches in test mode (dropout as scaling), as the
+        progress report of sgd.py:165-188 computes it."""
+        net = self.net
+        dll = _lib.load()
+        total = torch.zeros(net.I, dtype=torch.float32, device=net.dev)
+        for X, R, Yb in batches:
+            out = net.score(X, R).contiguous()
+            lossv = torch.empty(net.I, dtype=torch.float32, device=net.dev)
+            if net.loss == "nll":
+                dll.db_logistic(out.data_ptr(), out.data_ptr(), out.numel())
+            dll.db_loss(1 if net.loss == "nll" else 0, out.data_ptr(), Yb.data_ptr(), None, None, out.shape[0], net.I,
+                        lossv.data_ptr(), None)
+            total += lossv
+        return (total / max(1, len(batches))).cpu().numpy()

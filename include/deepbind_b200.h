@@ -139,6 +139,10 @@ void db_logistic(float* Z, const float* X, size_t n);
 void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, const uint8_t* Zmask,
              uint32_t nrow, uint32_t ncol, float* loss_out, float* dZ);
 
+/* L1 weight decay (corr1ord.py:112-126, full.py:102-119): dP[i] += decay[i] * sign(P[i]);
+ * `decay` is the per-model decay spread over the flat parameter vector, zero on biases. */
+void db_l1_decay(float* dP, const float* P, const float* decay, size_t n);
+
 /* The dense head of one training step in one launch (no counterpart as one call;
  * replaces dropout -> full -> bias -> rectify -> full -> bias -> logistic -> loss and
  * their backward passes: elemwise.py:128-150,171,74-78, full.py:78-89, softmax.py:50-61,
