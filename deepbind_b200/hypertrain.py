@@ -1,0 +1,157 @@
+"""Calibration (hyper-parameter search with k-fold validation) and final training,
+following the reference's calibrate -> train workflow
+(code/libs/deepity/deepity/hypertrain.py:248-400,560-580, hpsearch.py:95-260,
+kangaroo/train.py:74-172) around the device-side trainer.
+
+* ``ncalib`` hyper-parameter samples are trained side by side as the instances of
+  one :class:`DeepBindNet` (the reference's instance batching), once per fold;
+* the data are shuffled once with a fixed seed, and fold ``f`` of ``nfold`` holds
+  out the block ``split_folds`` describes (deepity/data.py:120-145);
+* every checkpoint of every sample is scored on the held-out block; the best
+  (sample, step) by validation metric gives the hyper-parameters, including the
+  number of steps, of the final training (hpsearch.py:224-241);
+* the final training runs ``ntrial`` differently initialised instances with those
+  hyper-parameters on all the data and keeps the one that fits the training data best.
+
+The bookkeeping is host code; every model evaluation runs through the same
+kernels as training and scoring.
+"""
+import json
+import os
+
+import numpy as np
+
+from . import cfg
+from .trainer import Trainer
+
+
+# --------------------------------------------------------------------- metrics
+def calc_auc(z, y):
+    """Area under the ROC curve as deepity/report.py:56-106 computes it: stable sort
+    by decreasing score, cumulative true/false positives, trapezoidal rule; NaN if
+    a class is empty."""
+    z = np.asarray(z, np.float64).ravel(); y = np.asarray(y, np.float64).ravel()
+    assert len(z) == len(y)
+    order = np.argsort(z, kind="mergesort")[::-1]
+    y = y[order]
+    tpr = y.cumsum()
+    fpr = 1 + np.arange(len(y), dtype=np.float64) - tpr
+    if fpr[0] != 0:
+        tpr = np.r_[0, tpr]; fpr = np.r_[0, fpr]
+    if fpr[-1] == 0 or tpr[-1] == 0:
+        return np.nan
+    tpr = tpr / tpr[-1]; fpr = fpr / fpr[-1]
+    return float(np.sum((fpr[1:] - fpr[:-1]) * (tpr[1:] + tpr[:-1]) * 0.5))
+
+
+def pearson(z, y):
+    z = np.asarray(z, np.float64).ravel(); y = np.asarray(y, np.float64).ravel()
+    zc, yc = z - z.mean(), y - y.mean()
+    d = np.sqrt((zc * zc).sum() * (yc * yc).sum())
+    return float((zc * yc).sum() / d) if d > 0 else np.nan
+
+
+def split_folds(n, index=0, nsplit=1):
+    """(A, B) index arrays of ``datasource.split(index, nsplit)`` (deepity/data.py:120-145):
+    B is block nsplit - index of nsplit + 1 near-equal blocks, A is the rest."""
+    assert index <= nsplit
+    if nsplit <= 0:
+        return np.arange(n), np.arange(0)
+    at = [int(x) for x in np.linspace(0, n, nsplit + 2)]
+    r = nsplit - index
+    return np.r_[np.arange(at[0], at[r]), np.arange(at[r + 1], at[-1])], np.arange(at[r], at[r + 1])
+
+
+# ----------------------------------------------------------------- calibration
+def _metric_of(net, loss):
+    return ("auc", True) if loss == "nll" else ("pearson", True)
+
+
+def _validate(net, seqs, Y, batch=4096):
+    """Scores of every instance on held-out sequences, in test mode -> (Z [n, I])."""
+    from .predict import predict
+    out = []
+    for lo in range(0, len(seqs), batch):
+        out.append(predict(net, seqs[lo:lo + batch])["direct"].cpu().numpy())
+    return np.concatenate(out) if out else np.zeros((0, net.I), np.float32)
+
+
+def calibrate(layers, trainer_spec, seqs, Y, ncalib=30, nfold=3, seed=0, motif_len=None, shuffle_seed=1234, outdir=None,
+              allfolds=True):
+    """Draws ``ncalib`` hyper-parameter samples, trains each on every fold, validates
+    every checkpoint.  Returns a list of records
+    ``{"sample", "step", "hparams", "metric", "value", "folds"}`` (one per sample and
+    checkpoint; ``value`` is the mean of the folds' validation metric) and the best
+    record.  With ``outdir`` the records are also written to ``calib.all.json``."""
+    seqs = list(seqs)
+    Y = np.asarray(Y, np.float32).reshape(len(seqs), -1)
+    perm = np.random.default_rng(shuffle_seed).permutation(len(seqs))       # always the same shuffle, hence the same folds
+    seqs = [seqs[i] for i in perm]; Y = Y[perm]
+    records = {}
+    metric = None
+    for fold in range(nfold if allfolds else 1):
+        A, B = split_folds(len(seqs), fold, nfold - 1)
+        # the same draws for every fold: a sample is a hyper-parameter set, evaluated nfold times
+        net, drawn = cfg.instantiate(layers, ninst=ncalib, seed=seed, motif_len=motif_len)
+        tr = Trainer(net, trainer_spec, seed=seed)
+        metric, _ = _metric_of(net, net.loss)
+        vseqs, vY = ([seqs[i] for i in B], Y[B]) if len(B) else ([seqs[i] for i in A], Y[A])
+
+        def on_checkpoint(step, trainer):
+            Z = _validate(trainer.net, vseqs, vY)
+            for s in range(ncalib):
+                v = calc_auc(Z[:, s], vY[:, 0]) if metric == "auc" else pearson(Z[:, s], vY[:, 0])
+                rec = records.setdefault((s, step), {"sample": s, "step": step, "metric": metric, "folds": []})
+                rec["folds"].append(v)
+        tr.fit([seqs[i] for i in A], Y[A], on_checkpoint=on_checkpoint)
+        hp = {k: np.asarray(v).tolist() for k, v in drawn.items()}
+        hp["trainer.rate"], hp["trainer.momentum"] = tr.rate.tolist(), tr.momentum.tolist()
+    out = []
+    for (s, step), rec in sorted(records.items()):
+        rec["hparams"] = {k: v[s] for k, v in hp.items()}
+        rec["value"] = float(np.mean(rec["folds"])) if not np.any(np.isnan(rec["folds"])) else float("nan")
+        out.append(rec)
+    best = get_best_sample(out, wantmax=True)
+    if outdir:
+        os.makedirs(outdir, exist_ok=True)
+        with open(os.path.join(outdir, "calib.all.json"), "w") as f:
+            json.dump({"records": out, "best": best}, f, indent=1)
+    return out, best
+
+
+def get_best_sample(records, wantmax=False):
+    """hpsearch.py:224-241: the first record with the best non-NaN value."""
+    best = None
+    for r in records:
+        if not np.isnan(r["value"]):
+            if best is None or (r["value"] > best["value"] if wantmax else r["value"] < best["value"]):
+                best = r
+    return best
+
+
+def _fix(layers, hparams, ntrial):
+    """The layer list with every drawn range replaced by the chosen value, once per trial."""
+    import copy
+    fixed_layers = copy.deepcopy(layers)
+    for key, val in hparams.items():
+        if key.startswith("trainer."):
+            continue
+        idx, _, arg = key.split(".")
+        setattr(fixed_layers[int(idx)], arg, cfg.fixed(np.full(ntrial, val)))
+    return fixed_layers
+
+
+def train_final(layers, trainer_spec, best, seqs, Y, ntrial=3, seed=0, motif_len=None):
+    """Trains ``ntrial`` instances with the best record's hyper-parameters and step
+    count on all the data; returns (net, index of the trial with the best training
+    metric, metrics [ntrial])."""
+    import copy
+    spec = copy.copy(trainer_spec)
+    spec.rate, spec.momentum = best["hparams"]["trainer.rate"], best["hparams"]["trainer.momentum"]
+    spec.max_steps, spec.checkpoints = int(best["step"]), 1
+    net, _ = cfg.instantiate(_fix(layers, best["hparams"], ntrial), ninst=ntrial, seed=seed + 1, motif_len=motif_len)
+    Trainer(net, spec, seed=seed).fit(list(seqs), Y)
+    Yv = np.asarray(Y, np.float32).reshape(len(seqs), -1)
+    Z = _validate(net, list(seqs), Yv)
+    vals = np.asarray([calc_auc(Z[:, t], Yv[:, 0]) if net.loss == "nll" else pearson(Z[:, t], Yv[:, 0]) for t in range(ntrial)])
+    return net, int(np.nanargmax(vals)), vals
