@@ -267,12 +267,35 @@ class DeepBindNet(object):
         X, R, out = dev_bufs
         X.copy_(X_host, non_blocking=True)
         R.copy_(R_host, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        if tc and self.hidden == 0 and self.nf == 16 * self.I and self.dropout_rate is None and R.shape[0] >= 8 * 4096:
+            # Scores go back to the host piece by piece on a second stream while the
+            # next piece is being scanned: the 4*I bytes per sequence of the read-back
+            # otherwise add their full PCIe time to the step.
+            if not hasattr(self, "_copy_stream"):
+                self._copy_stream = torch.cuda.Stream(device=self.dev)
+                self._status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+            nseq, npiece = R.shape[0], 8
+            for c in range(npiece):
+                lo, hi = (nseq * c) // npiece, (nseq * (c + 1)) // npiece
+                self.score_tc(X, R[lo:hi], check=False, out=out[lo:hi], status=self._status)
+                done = torch.cuda.Event()
+                done.record(cur)
+                self._copy_stream.wait_event(done)
+                with torch.cuda.stream(self._copy_stream):
+                    out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
+            self._copy_stream.synchronize()
+            cur.synchronize()
+            if int(self._status.item()) != 0:
+                raise _lib.SmatException("scanpool_tc(...) raised an exception\nRuntimeError: tensor-core scan failed (status %d)"
+                                         % int(self._status.item()))
+            return out_host
         if tc:
             self.score_tc(X, R, check=False, out=out)
         else:
             self.score_chunked(X, R, out, chunk)
         out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        cur.synchronize()
         return out_host
 
     def capture_train_step(self, X, R, Y, dropmask=None, warmup=3):

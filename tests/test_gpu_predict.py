@@ -47,3 +47,29 @@ def test_scan_mode(cuda, orc, I, W, stride, rc):
     np.testing.assert_allclose(got["max"].cpu().numpy(), want["max"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(got["sum"].cpu().numpy(), want["sum"], rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(got["avg"].cpu().numpy(), want["avg"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("nseq", [500, 40000])
+def test_predict_host_equals_device_scoring(cuda, nseq):
+    """Host buffers in, host scores out: the small single-launch path and the
+    pipelined path (scan pieces overlapped with the read-back) give what scoring
+    the resident batch gives."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    I, m = 8, 24
+    net = DeepBindNet(synth.model_params(I, m, 5, "all"), I, "all")
+    Xh, Rh = synth.uniform_batch(nseq, 50, m, seed=2)
+    X_host = torch.from_numpy(Xh).pin_memory(); R_host = torch.from_numpy(Rh.view(np.int32)).pin_memory()
+    out_host = torch.empty((nseq, I), dtype=torch.float32).pin_memory()
+    net.prepare_tc("f16x2")
+    net.predict_host(X_host, R_host, out_host, tc=True)
+    want = net.score_tc(X_host.cuda(), R_host.cuda()).cpu()
+    # the mean-pooling sum of a region is grouped by where the 256-row tiles cut it, which depends on
+    # the piece a sequence falls in: same values up to the order of FP32 additions
+    assert float((out_host - want).abs().max()) <= 1e-6 * float(want.abs().max())
+    exact = net.score(X_host.cuda(), R_host.cuda()).cpu()
+    assert float((out_host - exact).abs().max()) <= 3e-6 * float(exact.abs().max()) * 4
+    out2 = torch.empty_like(out_host)
+    net.predict_host(X_host, R_host, out2, tc=False)
+    assert torch.equal(out2, exact)
