@@ -23,7 +23,7 @@ struct head_args {
 	const float* W1; const float* b1; const float* W2; const float* b2;
 	float* loss; float* dpooled; float* dW1; float* db1; float* dW2; float* db2;
 	unsigned B, I, npool, H;
-	int kind;
+	int kind, pairs;
 };
 
 // Sum over the rows i = k, k+8, ... of a column, k = lane % 8, then over the eight
@@ -48,7 +48,8 @@ head_train_kernel(const head_args a)
 	float* w1  = a1 + (size_t)B * HC;      // [np][WS]
 	float* w2  = w1 + (size_t)np * WS;     // [HC]
 	float* out = w2 + HC;                  // [B]       output, then dout
-	float* red = out + B;                  // [blockDim.x]
+	float* zb  = out + B;                  // [B]       output after the logistic (nll) or as is (mse)
+	float* red = zb + B;                   // [blockDim.x]
 
 	const size_t ldp = (size_t)np * a.I;
 	for (unsigned t = tid; t < B * np; t += nt) {
@@ -83,18 +84,27 @@ head_train_kernel(const head_args a)
 	}
 	__syncthreads();
 
-	// loss and dout = (Z - Y) / B   (loss.py:98-112; the logistic's own derivative is not applied, softmax.py:76-77)
+	// loss and dout = (Z - Y) / B   (loss.py:98-112; the logistic's own derivative is not applied, softmax.py:76-77).
+	// With strand pairs (rows 2k, 2k+1 = forward, reverse complement) only the row with the larger
+	// output Z of each pair, the forward one on ties, contributes to loss and gradient
+	// (loss.py:52-65,113-117, maskout.cu:54-67); B still counts every row.
 	const float inv = 1.f / (float)B;
+	for (unsigned i = tid; i < B; i += nt) {
+		const float o = out[i];
+		zb[i] = a.kind == 1 ? 1.f / (1.f + expf(-o)) : o;
+	}
+	__syncthreads();
 	float ls = 0.f;
 	for (unsigned i = tid; i < B; i += nt) {
 		const float y = a.Y[(size_t)i * a.I + b];
-		float z = out[i], l;
-		if (a.kind == 1) {
-			z = 1.f / (1.f + expf(-z));
-			l = logf(fmaxf(1e-15f, z)) * y + logf(fmaxf(1e-15f, 1.f - z)) * (1.f - y);
-		} else { const float d = z - y; l = d * d; }
-		ls += l;
-		out[i] = (z - y) * inv;
+		const float z = zb[i];
+		bool keep = true;
+		if (a.pairs && (i | 1u) < B) keep = (i & 1u) ? !(zb[i - 1] >= z) : (z >= zb[i + 1]);
+		float l;
+		if (a.kind == 1) l = logf(fmaxf(1e-15f, z)) * y + logf(fmaxf(1e-15f, 1.f - z)) * (1.f - y);
+		else { const float d = z - y; l = d * d; }
+		ls += keep ? l : 0.f;
+		out[i] = keep ? (z - y) * inv : 0.f;
 	}
 	red[tid] = ls;
 	__syncthreads();
@@ -156,7 +166,7 @@ head_train_kernel(const head_args a)
 static size_t head_smem_bytes(unsigned B, unsigned np, unsigned H)
 {
 	unsigned HC = H ? H : 1u;
-	return ((size_t)B * np + 2 * (size_t)B * HC + (size_t)np * (HC + 1) + HC + B + 1024) * sizeof(float);
+	return ((size_t)B * np + 2 * (size_t)B * HC + (size_t)np * (HC + 1) + HC + 2 * (size_t)B + 1024) * sizeof(float);
 }
 
 }  // namespace db
@@ -171,7 +181,7 @@ DB_EXPORT uint32_t db_head_max_batch(uint32_t npool, uint32_t hidden)
 	return B;
 }
 
-DB_EXPORT void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_kind, uint32_t B,
+DB_EXPORT void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_kind, int strand_pairs, uint32_t B,
                              const float* pooled, const uint8_t* dropmask, const float* Y,
                              const float* W1, const float* b1, const float* W2, const float* b2,
                              float* loss, float* dpooled, float* dW1, float* db1, float* dW2, float* db2)
@@ -188,7 +198,7 @@ DB_EXPORT void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, i
 	head_args a;
 	a.pooled = pooled; a.mask = dropmask; a.Y = Y; a.W1 = W1; a.b1 = b1; a.W2 = W2; a.b2 = b2;
 	a.loss = loss; a.dpooled = dpooled; a.dW1 = dW1; a.db1 = db1; a.dW2 = dW2; a.db2 = db2;
-	a.B = B; a.I = nmodel; a.npool = npool; a.H = hidden; a.kind = loss_kind;
+	a.B = B; a.I = nmodel; a.npool = npool; a.H = hidden; a.kind = loss_kind; a.pairs = strand_pairs;
 	DB_CUDA(cudaFuncSetAttribute(head_train_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	// few models: one large CTA each hides the latency of the short dependent phases
 	head_train_kernel<<<nmodel, nmodel <= 64 ? 1024 : 256, smem, state().stream>>>(a);

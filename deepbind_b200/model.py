@@ -53,6 +53,7 @@ class DeepBindNet(object):
         self.decay = None                 # per-element L1 decay (set_decay); applied while decay_on
         self.decay_on = False
         self.dropout_rate = None          # per-model dropout rate of the pooled features (set_dropout)
+        self.strand_pairs = False         # training rows are forward / reverse-complement pairs (grads masks the weaker strand)
 
     # ------------------------------------------------------------- parameters
     def _spread(self, vec, name, values, k=None):
@@ -168,7 +169,7 @@ class DeepBindNet(object):
             lossv = torch.empty(I, dtype=torch.float32, device=self.dev)
             dpd = torch.empty_like(pooled)
             has2 = bool(self.hidden)
-            dll.db_head_train(I, npool, self.hidden, 1 if self.loss == "nll" else 0, B, pooled.data_ptr(),
+            dll.db_head_train(I, npool, self.hidden, 1 if self.loss == "nll" else 0, int(self.strand_pairs), B, pooled.data_ptr(),
                               dropmask.data_ptr() if dropmask is not None else None, Y.data_ptr(),
                               self.view("W1").data_ptr(), self.view("b1").data_ptr(),
                               self.view("W2").data_ptr() if has2 else None, self.view("b2").data_ptr() if has2 else None,
@@ -188,12 +189,16 @@ class DeepBindNet(object):
         B = out.shape[0]
         lossv = torch.empty(I, dtype=torch.float32, device=self.dev)
         dout = torch.empty_like(out)
+        z = out
         if self.loss == "nll":
             z = torch.empty_like(out)
             dll.db_logistic(z.data_ptr(), out.data_ptr(), out.numel())
-            dll.db_loss(1, z.data_ptr(), Y.data_ptr(), None, None, B, I, lossv.data_ptr(), dout.data_ptr())
-        else:
-            dll.db_loss(0, out.data_ptr(), Y.data_ptr(), None, None, B, I, lossv.data_ptr(), dout.data_ptr())
+        zmask = None
+        if self.strand_pairs:               # the stronger strand of each row pair carries loss and gradient (loss.py:113-117)
+            zmask = torch.zeros(out.shape, dtype=torch.bool, device=self.dev)
+            dsm.calc_Zmask(_as_f32(z), sarray(zmask, np.bool_))
+        dll.db_loss(1 if self.loss == "nll" else 0, z.data_ptr(), Y.data_ptr(), None,
+                    zmask.data_ptr() if zmask is not None else None, B, I, lossv.data_ptr(), dout.data_ptr())
         if self.hidden:
             W2 = self.view("W2")
             dll.db_colsum(self.view("b2", "dP").data_ptr(), dout.data_ptr(), B, I)

@@ -16,8 +16,10 @@ L1 weight decay (code/libs/deepity/deepity/sgd.py:87-163,287-354):
   a run reproducible against the CPU restatement.
 
 Batches, masks, forward, backward and update all run on the device; when every
-minibatch has the same size the step is replayed from a CUDA graph.  Training
-on both strands (loss masked to the stronger strand) is not built.
+minibatch has the same size the step is replayed from a CUDA graph.  With
+``reverse_complement`` every sequence enters the minibatch on both strands, the
+two rows share target and dropout mask, and only the stronger strand carries
+loss and gradient (kangaroo/data.py:274-306, elemwise.py:140, loss.py:113-117).
 """
 import numpy as np
 import torch
@@ -43,6 +45,7 @@ class Trainer(object):
         net.set_rates(self.rate, self.momentum)
         self.step = 0
         self.history = []                 # (step, mean training loss [I]) at every checkpoint
+        self.reverse_complement = False   # set by fit()
 
     # ------------------------------------------------------------------ data
     def make_batches(self, seqs, Y):
@@ -55,9 +58,11 @@ class Trainer(object):
             Y = np.tile(Y, (1, net.I))
         assert Y.shape[1] == net.I, "targets must have one column, or one per model"
         batches = []
+        rc = bool(self.reverse_complement)
         for lo in range(0, len(seqs), B):
-            X, R = fused.build_batch(seqs[lo:lo + B], net.m - 1, False, device=net.dev)
-            batches.append((X, R, torch.from_numpy(np.ascontiguousarray(Y[lo:lo + B])).to(net.dev)))
+            X, R = fused.build_batch(seqs[lo:lo + B], net.m - 1, rc, device=net.dev)
+            Yb = np.repeat(Y[lo:lo + B], 2, axis=0) if rc else Y[lo:lo + B]       # both strands share the target
+            batches.append((X, R, torch.from_numpy(np.ascontiguousarray(Yb)).to(net.dev)))
         return batches
 
     def _mask(self, nrow, draws):
@@ -67,17 +72,20 @@ class Trainer(object):
             return None
         ones = sm.sarray(torch.ones((nrow, self._mask_cols()), dtype=torch.float32, device=net.dev), np.float32)
         U = None if draws is None else sm.sarray(draws, np.float32)
-        _, M = dsm.dropout_fp_train(ones, sm.asarray(net.dropout_rate), False, U)
+        _, M = dsm.dropout_fp_train(ones, sm.asarray(net.dropout_rate), bool(self.reverse_complement), U)
         return M.tensor
 
     # ------------------------------------------------------------------- loop
-    def fit(self, seqs, Y, uniform_draws=None, on_checkpoint=None, use_graph=True):
+    def fit(self, seqs, Y, uniform_draws=None, on_checkpoint=None, use_graph=True, reverse_complement=False):
         """Trains for the trainer's step budget; returns the loss [I] of the last step.
+        ``reverse_complement``: train on both strands of every sequence.
 
         ``uniform_draws(step, shape)`` (optional) returns the U(0,1) draws of that
         step's dropout mask as a CUDA f32 tensor; ``on_checkpoint(step, trainer)`` is
         called at every checkpoint after the mean training loss was recorded."""
         net, spec = self.net, self.spec
+        self.reverse_complement = bool(reverse_complement)
+        net.strand_pairs = self.reverse_complement
         batches = self.make_batches(seqs, Y)
         nb = len(batches)
         max_steps = int(min(spec.max_steps, spec.max_epochs * nb))
@@ -131,7 +139,11 @@ class Trainer(object):
             lossv = torch.empty(net.I, dtype=torch.float32, device=net.dev)
             if net.loss == "nll":
                 dll.db_logistic(out.data_ptr(), out.data_ptr(), out.numel())
-            dll.db_loss(1 if net.loss == "nll" else 0, out.data_ptr(), Yb.data_ptr(), None, None, out.shape[0], net.I,
-                        lossv.data_ptr(), None)
+            zmask = None
+            if self.reverse_complement:     # only the stronger strand of a pair counts; the mean is over all rows
+                zmask = torch.zeros(out.shape, dtype=torch.bool, device=net.dev)
+                dsm.calc_Zmask(sm.sarray(out, np.float32), sm.sarray(zmask, np.bool_))
+            dll.db_loss(1 if net.loss == "nll" else 0, out.data_ptr(), Yb.data_ptr(), None,
+                        zmask.data_ptr() if zmask is not None else None, out.shape[0], net.I, lossv.data_ptr(), None)
             total += lossv
         return (total / max(1, len(batches))).cpu().numpy()

@@ -150,10 +150,13 @@ void db_l1_decay(float* dP, const float* P, const float* decay, size_t n);
  * minibatch in shared memory.  pooled/dpooled/dropmask [B, npool*nmodel]; Y [B, nmodel];
  * hidden = 0: linear head W1 [(npool*nmodel),1], b1 [nmodel]; hidden = H: W1
  * [(npool*nmodel),H], b1 [H*nmodel], W2 [(H*nmodel),1], b2 [nmodel].  loss_kind 0 = mse,
- * 1 = nll on logistic outputs.  Writes loss [nmodel], dpooled and the four parameter
+ * 1 = nll on logistic outputs.  strand_pairs != 0: rows 2k, 2k+1 are the two strands of
+ * one sequence and only the row with the larger output (the first on ties) contributes
+ * to loss and gradient, as calc_zmask + maskout do in loss.py:52-65,98-117; the mean
+ * still divides by B.  Writes loss [nmodel], dpooled and the four parameter
  * gradients (overwritten).  B must not exceed db_head_max_batch(npool, hidden). */
 uint32_t db_head_max_batch(uint32_t npool, uint32_t hidden);
-void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_kind, uint32_t B,
+void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_kind, int strand_pairs, uint32_t B,
                    const float* pooled, const uint8_t* dropmask, const float* Y,
                    const float* W1, const float* b1, const float* W2, const float* b2,
                    float* loss, float* dpooled, float* dW1, float* db1, float* dW2, float* db2);

@@ -359,7 +359,7 @@ def score_net(params, X, R, pool="max", nmodel=1, strand_max=False):
 
 
 def train_grads(params, X, R, Y, pool="all", nmodel=1, loss="nll", dropmask=None,
-                decay=None, Ymask=None):
+                decay=None, Ymask=None, strand_pairs=False):
     """One forward/backward pass of the training graph; returns (loss[I], grads).
 
     Network: scan -> bias -> rectify -> pool -> dropout(mask given) ->
@@ -368,7 +368,10 @@ def train_grads(params, X, R, Y, pool="all", nmodel=1, loss="nll", dropmask=None
     deepity/std/loss.py:98-112 (dZ = (Z-Y)/nrow for both losses),
     full.py:84-89, elemwise.py:78,172-181, kangaroo/_ext/poolrgn.py:176-180,
     corr1ord.py:120-126.  decay: optional dict name -> per-model L1 weights
-    (full.py:111-119, corr1ord.py:125-126).
+    (full.py:111-119, corr1ord.py:125-126).  strand_pairs: rows are forward /
+    reverse-complement pairs; only the row with the larger output of each pair
+    contributes to loss and gradient (loss.py:52-65,98-117 with maskout.cu:54-67),
+    while the mean still divides by all rows.
     """
     I = nmodel
     dt = params["Wscan"].dtype
@@ -397,10 +400,18 @@ def train_grads(params, X, R, Y, pool="all", nmodel=1, loss="nll", dropmask=None
         scale = 0.5
     if Ymask is not None:
         L = np.where(Ymask, L, 0)
+    Zmask = None
+    if strand_pairs:
+        Zmask = np.zeros(Zo.shape, np.uint8)
+        calc_zmask(Zo, Zmask)
+        Zmask = Zmask.astype(bool)
+        L = np.where(Zmask, L, 0)
     lossval = scale * L.mean(axis=0)
     dout = (Zo - Yb).astype(dt)
     if Ymask is not None:
         dout = np.where(Ymask, dout, 0).astype(dt)
+    if Zmask is not None:
+        dout = np.where(Zmask, dout, 0).astype(dt)
     dout = (dout * dt.type(1.0 / nrow)).astype(dt)
     g = {}
     if "W2" in params:

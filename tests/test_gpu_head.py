@@ -49,7 +49,7 @@ def test_minibatch_beyond_the_tile_uses_the_operator_path(cuda):
     assert 128 <= cap < 4096
     z = torch.zeros(8, device="cuda")
     with pytest.raises(SmatException, match="exceeds the fused head"):
-        dll.db_head_train(1, 32, 32, 1, cap + 64, z.data_ptr(), None, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
+        dll.db_head_train(1, 32, 32, 1, 0, cap + 64, z.data_ptr(), None, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
                           z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr())
     # DeepBindNet falls back to separate operators for such a batch and still trains
     B = cap + 64
@@ -58,3 +58,29 @@ def test_minibatch_beyond_the_tile_uses_the_operator_path(cuda):
     net = DeepBindNet(p, 1, "all")
     L = net.grads(dev(X), dev(R), dev(np.zeros((B, 1), np.float32)))
     assert np.isfinite(L.cpu().numpy()).all()
+
+
+@pytest.mark.parametrize("fused_head", [True, False])
+@pytest.mark.parametrize("I,pool,hidden,loss", [(1, "max", 0, "mse"), (3, "all", 32, "nll")])
+def test_two_strand_training_masks_the_weaker_strand(cuda, orc, I, pool, hidden, loss, fused_head):
+    """Rows are forward / reverse-complement pairs: only the stronger row of each pair carries
+    loss and gradient (calc_zmask + maskout, loss.py:52-65,98-117), the mean divides by all rows."""
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m, nseq = 24, 48
+    p = synth.model_params(I, m, 21, pool, hidden=hidden)
+    X, R = synth.ragged_batch(nseq, 30, 80, m, seed=22, n_frac=0.02, both_strands=True)
+    g = synth.rng(23)
+    y = (g.integers(0, 2, size=(nseq, 1)) if loss == "nll" else g.standard_normal((nseq, 1))).astype(np.float32)
+    Y = np.tile(np.repeat(y, 2, axis=0), (1, I))                # both strands share the target
+    net = DeepBindNet(p, I, pool, loss=loss, fused_head=fused_head)
+    net.strand_pairs = True
+    L = net.grads(dev(X), dev(R), dev(Y)).cpu().numpy()
+    Lw, gw = orc.train_grads(p, X, R, Y, pool, I, loss, strand_pairs=True)
+    np.testing.assert_allclose(L, Lw, rtol=1e-5)
+    got = net.params_numpy("dP")
+    for k, w in gw.items():
+        assert np.max(np.abs(got[k].reshape(w.shape) - w)) <= 1e-5 * max(np.abs(w).max(), 1e-6), k
+    # and it differs from treating the rows as independent samples
+    L2, _ = orc.train_grads(p, X, R, Y, pool, I, loss)
+    assert not np.allclose(Lw, L2)

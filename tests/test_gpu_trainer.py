@@ -25,7 +25,7 @@ def make_data(rng, n, L, classify):
     return seqs, Y
 
 
-def oracle_run(orc, net0, hp, seqs, Y, B, steps, start, drate, mrate, pool, I, loss, draws):
+def oracle_run(orc, net0, hp, seqs, Y, B, steps, start, drate, mrate, pool, I, loss, draws, rc=False):
     """The same training run on the CPU: returns the flat parameter vector."""
     P = orc.flatten(net0).astype(np.float32).copy()
     mom = np.zeros_like(P)
@@ -34,23 +34,24 @@ def oracle_run(orc, net0, hp, seqs, Y, B, steps, start, drate, mrate, pool, I, l
     nb = (len(seqs) + B - 1) // B
     for step in range(steps):
         lo = (step % nb) * B
-        X, R = orc.asbatch(seqs[lo:lo + B], m - 1)
-        Yb = np.tile(Y[lo:lo + B], (1, I))
+        X, R = orc.asbatch(seqs[lo:lo + B], m - 1, rc)
+        Yb = np.tile(np.repeat(Y[lo:lo + B], 2, axis=0) if rc else Y[lo:lo + B], (1, I))
         mask = None
         if draws is not None:
-            rate = np.repeat(hp["dropout"], npool)[None, :]
-            mask = draws[step][:len(R)] >= rate
+            U = draws[step][:len(R)]
+            _, mask = orc.dropout_fp_tr(np.ones_like(U), hp["dropout"].astype(np.float32), U, matchrows=rc)
         decay = hp["decay"] if step >= start else None
 
         def grad(Pv):
-            _, g = orc.train_grads(orc.unflatten(Pv, net0), X, R, Yb, pool, I, loss, mask, decay=decay)
+            _, g = orc.train_grads(orc.unflatten(Pv, net0), X, R, Yb, pool, I, loss, mask, decay=decay, strand_pairs=rc)
             return orc.flatten(g)
         orc.nesterov_step(P, mom, drate, mrate, grad)
     return P
 
 
-@pytest.mark.parametrize("text,I,classify,L", [(HIDDEN, 3, True, 60), (LINEAR, 4, False, 40)])
-def test_training_run_matches_the_oracle(cuda, orc, text, I, classify, L):
+@pytest.mark.parametrize("text,I,classify,L,rc", [(HIDDEN, 3, True, 60, False), (LINEAR, 4, False, 40, False),
+                                                  (HIDDEN, 2, True, 50, True)])
+def test_training_run_matches_the_oracle(cuda, orc, text, I, classify, L, rc):
     import torch
     from deepbind_b200 import cfg
     from deepbind_b200.trainer import Trainer
@@ -67,11 +68,11 @@ def test_training_run_matches_the_oracle(cuda, orc, text, I, classify, L):
     tr = Trainer(net, spec, seed=3)
     net0 = net.params_numpy()
     npool = 16 * (2 if plan.pool == "all" else 1)
-    draws = rng.random((steps, B, npool * I)).astype(np.float32) if plan.drop is not None else None
+    draws = rng.random((steps, B * (2 if rc else 1), npool * I)).astype(np.float32) if plan.drop is not None else None
     want = oracle_run(orc, net0, net.hparams, seqs, Y, B, steps, start, net.drate.cpu().numpy(), net.mrate.cpu().numpy(),
-                      plan.pool, I, plan.loss, draws)
+                      plan.pool, I, plan.loss, draws, rc)
     supply = (lambda step, shape: torch.from_numpy(draws[step][:shape[0]].copy()).cuda()) if draws is not None else None
-    loss = tr.fit(seqs, Y, uniform_draws=supply, use_graph=False)
+    loss = tr.fit(seqs, Y, uniform_draws=supply, use_graph=False, reverse_complement=rc)
     got = net.P.cpu().numpy()
     scale = np.abs(want).max()
     assert np.max(np.abs(got - want)) <= 2e-5 * scale, (np.max(np.abs(got - want)), scale)
