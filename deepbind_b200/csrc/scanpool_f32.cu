@@ -310,8 +310,24 @@ scanpool_bwd_kernel(const bwd_args a)
 	__shared__ unsigned s_lo, s_hi;
 
 	const unsigned f0 = blockIdx.y * FB;
-	const unsigned g0 = blockIdx.x * a.G;
+	// accumulator identity: unit u = (tap group jg, filter fl) covers taps 4jg .. 4jg+3.
+	// The FB threads after the units sum dbias.
+	const unsigned nunit = ((m + 3) / 4) * FB;
+	const bool is_unit = threadIdx.x < nunit, is_bias = threadIdx.x >= nunit && threadIdx.x < nunit + FB;
+	const unsigned j0 = 4 * (threadIdx.x / FB), fl = threadIdx.x % FB;
+	float c[4][4];
+	#pragma unroll
+	for (int t = 0; t < 4; ++t)
+		#pragma unroll
+		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
+	float bsum = 0.f;
+	const unsigned nwords = (a.nf + 15) / 16;
+
+	// The CTA keeps its accumulators over all the region groups it is dealt (every
+	// gridDim.x-th group): one partial result per CTA, however many groups there are.
+	for (unsigned g0 = blockIdx.x * a.G; g0 < a.nregion; g0 += gridDim.x * a.G) {
 	const unsigned ng = min(a.G, a.nregion - g0);
+	__syncthreads();
 	if (threadIdx.x == 0) {
 		unsigned lo = 0xffffffffu, hi = 0;
 		for (unsigned g = 0; g < ng; ++g) {
@@ -337,19 +353,6 @@ scanpool_bwd_kernel(const bwd_args a)
 		davg[t] = va; dmax[t] = vm; amax[t] = am;
 	}
 	__syncthreads();
-
-	// accumulator identity: unit u = (tap group jg, filter fl) covers taps 4jg .. 4jg+3.
-	// The FB threads after the units sum dbias.
-	const unsigned nunit = ((m + 3) / 4) * FB;
-	const bool is_unit = threadIdx.x < nunit, is_bias = threadIdx.x >= nunit && threadIdx.x < nunit + FB;
-	const unsigned j0 = 4 * (threadIdx.x / FB), fl = threadIdx.x % FB;
-	float c[4][4];
-	#pragma unroll
-	for (int t = 0; t < 4; ++t)
-		#pragma unroll
-		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
-	float bsum = 0.f;
-	const unsigned nwords = (a.nf + 15) / 16;
 
 	if (s_hi > s_lo)
 	for (unsigned t0 = s_lo; t0 < s_hi; t0 += TR) {
@@ -381,8 +384,10 @@ scanpool_bwd_kernel(const bwd_args a)
 			dz[t] = v;
 		}
 		__syncthreads();
-		// Rows at or past n have no scan output, hence no filter gradient.
-		const unsigned rows = min((unsigned)TR, a.n > t0 ? a.n - t0 : 0u);
+		// Rows at or past n have no scan output, hence no filter gradient; rows past the
+		// last region of the group carry none either.
+		const unsigned row_end = min(a.n, s_hi);
+		const unsigned rows = min((unsigned)TR, row_end > t0 ? row_end - t0 : 0u);
 		if (is_unit) {
 			// Branch-free: the channel weights are 0, 1/4 or 1, so each product is exact and
 			// the fused multiply-add equals the reference's add of dZ (or dZ/4).
@@ -414,6 +419,7 @@ scanpool_bwd_kernel(const bwd_args a)
 			bsum = s;
 		}
 	}
+	}   // region groups
 	// partial[cta][(4m+1)][nf]; row 4m is dbias
 	float* out = a.partial + (size_t)blockIdx.x * (4 * m + 1) * a.nf;
 	if (is_unit && f0 + fl < a.nf) {
@@ -530,17 +536,27 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	bwd_args a;
 	a.X = X; a.R = regions; a.dpooled = dpooled; a.argmax = argmax; a.actmask = actmask;
 	a.m = m; a.nf = nf; a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.ptype = ptype;
-	a.FB = nf <= 16 ? 16 : (nf <= 32 ? 32 : 64);
+	a.FB = nf <= 16 ? 16 : 32;          // 32 filters per CTA: several CTAs per SM, whose staging and FMA phases overlap
 	while (a.FB > 16 && ((m + 3) / 4 + 1) * a.FB > 512) a.FB /= 2;
 	unsigned nfb = divup(nf, a.FB);
-	a.G = pick_group(nregion, nfb);
 	unsigned threads = (((m + 3) / 4 + 1) * a.FB + 31u) & ~31u;       // one thread per (four taps, filter) and per bias column
 	DB_REQUIRE(threads <= 512, "ValueError: filter length %u is too long for the fused backward kernel", m);
 	if (threads < 128) threads = 128;
-	unsigned ncta = divup(nregion, a.G);
-	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
+	// Regions per group: about one tile of rows.  CTAs per filter block: as many as are resident
+	// at once, each looping over its share of the groups, so that no second, part-filled wave runs.
+	a.G = std::max(1u, std::min((unsigned)GMAX, (unsigned)TR / std::max(1u, npos / nregion)));
 	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + (size_t)(TR + m + 4) * 16 + (size_t)TR * 4 + 16;
 	DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	int per_sm = 1;
+	DB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scanpool_bwd_kernel, (int)threads, smem));
+	unsigned slots = (unsigned)state().sm_count * (unsigned)std::max(per_sm, 1);
+	// With many groups per slot, one CTA per group balances the waves by itself; then the
+	// largest group that still leaves four waves keeps the number of partial results small.
+	for (unsigned G = GMAX; G > a.G; G /= 2)
+		if ((size_t)divup(nregion, G) * nfb >= (size_t)4 * slots) { a.G = G; break; }
+	unsigned ngroup = divup(nregion, a.G);
+	unsigned ncta = (size_t)ngroup * nfb >= (size_t)4 * slots ? ngroup : std::min(ngroup, std::max(1u, slots / nfb));
+	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
 	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
 	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount + nf, (size_t)32), 65535), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta);
