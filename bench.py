@@ -435,7 +435,13 @@ def main():
                     "flops_counted": "executed tensor flops = %d x dense-equivalent 2*K*rows*filters (K=96); the pieces are what "
                                      "fp32-grade results cost on 16-bit tensor cores (f16 and bf16 run at the same rate)" % nsplit,
                     "dense_equiv_tflops": dense_flop / (kernel_ms * 1e-3) / 1e12,
-                    "burst_peak": peaks.get("bf16_tflops"), "traffic": None, "ms_per_launch": kernel_ms,
+                    "burst_peak": peaks.get("bf16_tflops"),
+                    # ncu, one launch of 1,000,000 sequences x 512 models: dram__bytes_read.sum 277 MB +
+                    # dram__bytes_write.sum 2.01 GB (profiles/scanpool_tc_f16x2_genome_scan.md); it grows with the
+                    # sequence count once the score matrix exceeds L2, so it is scaled from that capture
+                    "traffic": (2.287e9 * nseq / 1e6) if (I == 512 and nseq >= 250000) else None,
+                    "traffic_unit": "bytes per launch (algorithmic: %d)" % (nseq * ((L + M - 1) + I * 4)),
+                    "ms_per_launch": kernel_ms,
                     "hbm_gbs_algorithmic": (nseq * ((L + M - 1) + I * 4)) / (kernel_ms * 1e-3) / 1e9}
     else:
         Wd, bd = net.view("Wscan"), net.view("bscan").view(-1)
