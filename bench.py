@@ -26,9 +26,11 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-# stdout carries one JSON line only: keep NCCL's version banner off it (set before anything loads NCCL)
+# stdout carries one JSON line only: NCCL's version banner and warnings go to stderr (set before NCCL
+# loads; NCCL honours the file only from level WARN up, and prints the banner at VERSION and WARN)
 if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
     os.environ["NCCL_DEBUG"] = "WARN"
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
 M, NMOTIF, L = 24, 16, 101
 UNIT = "sequences/s"

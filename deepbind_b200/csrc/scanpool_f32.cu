@@ -103,21 +103,25 @@ scanpool_fwd_kernel(const fwd_args a)
 	float* lut = reinterpret_cast<float*>(smem);                       // m*NQ*32 floats
 	float* act = lut + (size_t)m * NQ * 32;                            // FB*(TR+1) floats
 	uint8_t* xs = reinterpret_cast<uint8_t*>(act + (size_t)FB * (TR + 1));   // TR + m + 8 bytes (4-aligned)
-	__shared__ unsigned rg0[GMAX], rg1[GMAX];
+	__shared__ unsigned rg0[GMAX], rg1[GMAX], rcnt[GMAX];
 	__shared__ unsigned s_lo, s_hi, s_sum;
 
 	const unsigned f0 = blockIdx.y * FB;
 	const unsigned g0 = blockIdx.x * a.G;
 	const unsigned ng = min(a.G, a.nregion - g0);
+	// one thread per region fetches its bounds; the loads are in flight while the table is built
+	unsigned my_r0 = 0, my_r1 = 0;
+	if (threadIdx.x < ng) { my_r0 = a.R[2 * (g0 + threadIdx.x)]; my_r1 = a.R[2 * (g0 + threadIdx.x) + 1]; }
 	build_lut(lut, a.W, m, a.nf, f0, FB);
+	if (threadIdx.x < ng) {
+		rcnt[threadIdx.x] = my_r1 - my_r0;                 // integer row count (poolrgn.cuh:112,152)
+		rg0[threadIdx.x] = my_r0;
+		rg1[threadIdx.x] = my_r1 <= my_r0 ? my_r0 + 1 : my_r1;   // an empty region still reads its first row (poolrgn.cuh:60)
+	}
+	__syncthreads();
 	if (threadIdx.x == 0) {
 		unsigned lo = 0xffffffffu, hi = 0, sum = 0;
-		for (unsigned g = 0; g < ng; ++g) {
-			unsigned r0 = a.R[2 * (g0 + g)], r1 = a.R[2 * (g0 + g) + 1];
-			if (r1 <= r0) r1 = r0 + 1;          // an empty region still reads its first row (poolrgn.cuh:60)
-			rg0[g] = r0; rg1[g] = r1;
-			lo = min(lo, r0); hi = max(hi, r1); sum += r1 - r0;
-		}
+		for (unsigned g = 0; g < ng; ++g) { lo = min(lo, rg0[g]); hi = max(hi, rg1[g]); sum += rg1[g] - rg0[g]; }
 		s_lo = lo; s_hi = hi; s_sum = sum;
 	}
 	__syncthreads();
@@ -184,7 +188,7 @@ scanpool_fwd_kernel(const fwd_args a)
 	}
 	if (pool_thread) {
 		const unsigned g = g0 + pg, f = f0 + pf;
-		const unsigned cnt = a.R[2 * g + 1] - a.R[2 * g];     // integer row count (poolrgn.cuh:112,152)
+		const unsigned cnt = rcnt[pg];
 		const size_t o = (size_t)g * a.nf + f;
 		switch (a.ptype) {
 		case DB_PT_MAX: a.pooled[o] = xmax; if (a.argmax) a.argmax[o] = xidx * a.nf + f; break;
@@ -328,14 +332,11 @@ scanpool_bwd_kernel(const bwd_args a)
 	for (unsigned g0 = blockIdx.x * a.G; g0 < a.nregion; g0 += gridDim.x * a.G) {
 	const unsigned ng = min(a.G, a.nregion - g0);
 	__syncthreads();
-	if (threadIdx.x == 0) {
-		unsigned lo = 0xffffffffu, hi = 0;
-		for (unsigned g = 0; g < ng; ++g) {
-			unsigned r0 = a.R[2 * (g0 + g)], r1 = a.R[2 * (g0 + g) + 1];
-			rg0[g] = r0; rg1[g] = r1;
-			if (r1 > r0) { lo = min(lo, r0); hi = max(hi, r1); }
-		}
-		s_lo = lo; s_hi = hi;
+	// one thread per region fetches its bounds (one round trip, not ng of them); the last
+	// warp takes the job so that it overlaps the others' loads of dpooled below
+	if (threadIdx.x >= blockDim.x - GMAX) {
+		const unsigned g = threadIdx.x - (blockDim.x - GMAX);
+		if (g < ng) { rg0[g] = a.R[2 * (g0 + g)]; rg1[g] = a.R[2 * (g0 + g) + 1]; }
 	}
 	for (unsigned t = threadIdx.x; t < ng * FB; t += blockDim.x) {
 		unsigned g = t / FB, f = f0 + t % FB;
@@ -351,6 +352,13 @@ scanpool_bwd_kernel(const bwd_args a)
 			}
 		}
 		davg[t] = va; dmax[t] = vm; amax[t] = am;
+	}
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		unsigned lo = 0xffffffffu, hi = 0;
+		for (unsigned g = 0; g < ng; ++g)
+			if (rg1[g] > rg0[g]) { lo = min(lo, rg0[g]); hi = max(hi, rg1[g]); }
+		s_lo = lo; s_hi = hi;
 	}
 	__syncthreads();
 

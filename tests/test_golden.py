@@ -83,3 +83,33 @@ def test_gpu_training_matches_fixture(cuda, name):
     P = net.P.cpu().numpy()
     assert np.max(np.abs(P - z["P_final"])) <= 1e-5 * np.abs(z["P_final"]).max()
     assert np.max(np.abs(net.mP.cpu().numpy() - z["mP_final"])) <= 1e-5 * max(np.abs(z["mP_final"]).max(), 1e-6)
+
+
+def _predict_fixture():
+    z, params = load("scan_predict")
+    off = z["offsets"]
+    text = z["text"].tobytes().decode("latin-1")
+    seqs = [text[off[i]:off[i + 1]] for i in range(len(off) - 1)]
+    return z, params, seqs
+
+
+def test_oracle_reproduces_predict_fixture(orc):
+    z, params, seqs = _predict_fixture()
+    out = orc.predict(params, seqs, int(z["m"]), str(z["pool"]), int(z["nmodel"]), scan=int(z["scan"]), stride=int(z["stride"]),
+                      reverse_complement=bool(z["reverse_complement"]))
+    for k in ("direct", "max", "avg", "sum"):
+        np.testing.assert_allclose(out[k], z[k], rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(out["pmaps"][0], z["pmap0"], rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_gpu_predict_matches_fixture(cuda):
+    from deepbind_b200.model import DeepBindNet
+    from deepbind_b200.predict import predict
+    z, params, seqs = _predict_fixture()
+    net = DeepBindNet(params, int(z["nmodel"]), str(z["pool"]))
+    got = predict(net, seqs, scan=int(z["scan"]), stride=int(z["stride"]), reverse_complement=bool(z["reverse_complement"]),
+                  want_pmaps=True)
+    for k in ("direct", "max", "avg", "sum"):
+        np.testing.assert_allclose(got[k].cpu().numpy(), z[k], rtol=1e-5, atol=1e-5 if k == "sum" else 1e-6)
+    np.testing.assert_allclose(got["pmaps"][0].cpu().numpy(), z["pmap0"], rtol=1e-5, atol=1e-6)
