@@ -40,6 +40,8 @@ void ensure_device();
 void* scratch(size_t bytes);   // stream-ordered use only; grows with cudaMalloc
 // FP32 motif scan writing Z [n, nf] (scanpool_f32.cu); n = rows written, X holds n + m - 1 bytes
 void launch_corr1ord_f32(const float* W, unsigned m, unsigned nf, const uint8_t* X, unsigned n, float* Z);
+// FP32 filter gradient of the scan from dZ [n, nf], accumulated into dW (scanpool_f32.cu)
+void launch_corr1ord_bprop_W_f32(float* dW, unsigned m, unsigned nf, const uint8_t* X, unsigned n, const float* dZ);
 
 inline void cuda_check(cudaError_t e, const char* what, const char* file, int line)
 {

@@ -324,7 +324,7 @@ DB_EXPORT void api_corr1ord_bprop_W(smat* dW, const smat* X, const smat* dZ, con
 	unsigned m = dW->shape.y / nchannel, nf = dW->shape.x;
 	if (size_of(X) < m) return;
 	unsigned n = (unsigned)size_of(X) - m + 1;
-	if (dZ->dtype == DB_F32) launch_corr1ord_bprop_W((float*)dW->data, m, nf, (const uint8_t*)X->data, n, (const float*)dZ->data);
+	if (dZ->dtype == DB_F32) launch_corr1ord_bprop_W_f32((float*)dW->data, m, nf, (const uint8_t*)X->data, n, (const float*)dZ->data);
 	else                     launch_corr1ord_bprop_W((double*)dW->data, m, nf, (const uint8_t*)X->data, n, (const double*)dZ->data);
 	DB_API_CATCH
 }

@@ -447,7 +447,7 @@ scanpool_bwd_kernel(const bwd_args a)
 // eight sums.  The order depends on `nparts` only, so repeated runs agree bit for bit.
 __global__ void __launch_bounds__(256)
 scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const float* __restrict__ partial,
-                    size_t wcount, unsigned nf, unsigned nparts)
+                    size_t wcount, unsigned nf, unsigned nparts, int accumulate)
 {
 	__shared__ float part[8][32];
 	const size_t total = wcount + nf;
@@ -469,10 +469,111 @@ scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const flo
 		if (w == 0 && i < total) {
 			const float s = ((part[0][lane] + part[1][lane]) + (part[2][lane] + part[3][lane])) +
 			                ((part[4][lane] + part[5][lane]) + (part[6][lane] + part[7][lane]));
-			if (i < wcount) dW[i] = s; else if (dbias) dbias[i - wcount] = s;
+			if (i < wcount) dW[i] = accumulate ? dW[i] + s : s; else if (dbias) dbias[i - wcount] = s;
 		}
 		__syncthreads();
 	}
+}
+
+// ----------------------------------- the filter gradient alone (api_corr1ord_bprop_W)
+// dW[(4j+k), f] += sum_i dZ[i, f] * [X[i+j] == k]  (+1/4 on all four channels for N;
+// corr1ord_bprop.cuh:91-138) from a dZ that lives in HBM: the accumulation loop of
+// the fused backward kernel, fed by coalesced tiles of dZ.  A CTA keeps its 16
+// accumulators per thread over every TR-row tile it is dealt and writes one partial
+// result; the second stage adds the partials, CTA ascending, into dW.
+struct bpw_args {
+	const uint8_t* X; const float* dZ; float* partial;
+	unsigned m, nf, n, npos, FB;
+};
+
+__global__ void __launch_bounds__(512)
+corr1ord_bprop_W_f32_kernel(const bpw_args a)
+{
+	extern __shared__ __align__(16) unsigned char smem[];
+	const unsigned m = a.m, FB = a.FB;
+	float* dz = reinterpret_cast<float*>(smem);                         // [TR][FB]
+	float4* oh = reinterpret_cast<float4*>(dz + (size_t)TR * FB);       // [TR + m + 4]
+	const unsigned f0 = blockIdx.y * FB;
+	const unsigned nunit = ((m + 3) / 4) * FB;
+	const bool is_unit = threadIdx.x < nunit;
+	const unsigned j0 = 4 * (threadIdx.x / FB), fl = threadIdx.x % FB;
+	float c[4][4];
+	#pragma unroll
+	for (int t = 0; t < 4; ++t)
+		#pragma unroll
+		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
+	for (unsigned t0 = blockIdx.x * TR; t0 < a.n; t0 += gridDim.x * TR) {
+		__syncthreads();
+		for (unsigned t = threadIdx.x; t < TR + m + 4; t += blockDim.x) {
+			unsigned i = t0 + t, x = i < a.npos ? a.X[i] : 254u;
+			const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
+			oh[t] = make_float4(x == 0u ? 1.f : q, x == 1u ? 1.f : q, x == 2u ? 1.f : q, x == 3u ? 1.f : q);
+		}
+		const unsigned rows = min((unsigned)TR, a.n - t0);
+		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
+			const unsigned r = t / FB, e = t % FB;
+			dz[t] = (r < rows && f0 + e < a.nf) ? a.dZ[(size_t)(t0 + r) * a.nf + f0 + e] : 0.f;
+		}
+		__syncthreads();
+		if (is_unit) {
+			const float* dzc = dz + fl;
+			const float4* ohj = oh + j0;
+			float4 w0 = ohj[0], w1 = ohj[1], w2 = ohj[2], w3 = ohj[3];
+			unsigned r = 0;
+			for (; r + 4 <= rows; r += 4) {
+				float v = dzc[(r + 0) * FB];
+				bwd_fma4(c[0], v, w0); bwd_fma4(c[1], v, w1); bwd_fma4(c[2], v, w2); bwd_fma4(c[3], v, w3);
+				w0 = ohj[r + 4];
+				v = dzc[(r + 1) * FB];
+				bwd_fma4(c[0], v, w1); bwd_fma4(c[1], v, w2); bwd_fma4(c[2], v, w3); bwd_fma4(c[3], v, w0);
+				w1 = ohj[r + 5];
+				v = dzc[(r + 2) * FB];
+				bwd_fma4(c[0], v, w2); bwd_fma4(c[1], v, w3); bwd_fma4(c[2], v, w0); bwd_fma4(c[3], v, w1);
+				w2 = ohj[r + 6];
+				v = dzc[(r + 3) * FB];
+				bwd_fma4(c[0], v, w3); bwd_fma4(c[1], v, w0); bwd_fma4(c[2], v, w1); bwd_fma4(c[3], v, w2);
+				w3 = ohj[r + 7];
+			}
+			for (; r < rows; ++r) {
+				const float v = dzc[r * FB];
+				bwd_fma4(c[0], v, ohj[r]); bwd_fma4(c[1], v, ohj[r + 1]); bwd_fma4(c[2], v, ohj[r + 2]); bwd_fma4(c[3], v, ohj[r + 3]);
+			}
+		}
+	}
+	float* out = a.partial + (size_t)blockIdx.x * 4 * m * a.nf;
+	if (is_unit && f0 + fl < a.nf) {
+		#pragma unroll
+		for (int t = 0; t < 4; ++t)
+			if (j0 + t < m) {
+				#pragma unroll
+				for (int k = 0; k < 4; ++k) out[(size_t)(4 * (j0 + t) + k) * a.nf + f0 + fl] = c[t][k];
+			}
+	}
+}
+
+void launch_corr1ord_bprop_W_f32(float* dW, unsigned m, unsigned nf, const uint8_t* X, unsigned n, const float* dZ)
+{
+	if (n == 0 || nf == 0 || m == 0) return;
+	bpw_args a;
+	a.X = X; a.dZ = dZ; a.m = m; a.nf = nf; a.n = n; a.npos = n + m - 1;
+	a.FB = nf <= 16 ? 16 : 32;
+	while (a.FB > 16 && ((m + 3) / 4) * a.FB > 512) a.FB /= 2;
+	unsigned threads = (((m + 3) / 4) * a.FB + 31u) & ~31u;
+	DB_REQUIRE(threads <= 512, "ValueError: filter length %u is too long for this kernel", m);
+	if (threads < 128) threads = 128;
+	unsigned nfb = divup(nf, a.FB);
+	size_t smem = (size_t)TR * a.FB * 4 + (size_t)(TR + m + 4) * 16;
+	DB_CUDA(cudaFuncSetAttribute(corr1ord_bprop_W_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	int per_sm = 1;
+	DB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, corr1ord_bprop_W_f32_kernel, (int)threads, smem));
+	unsigned slots = (unsigned)state().sm_count * (unsigned)std::max(per_sm, 1);
+	unsigned ncta = std::min(divup(n, (unsigned)TR), std::max(1u, slots / nfb));     // one resident wave
+	size_t wcount = (size_t)4 * m * nf;
+	a.partial = (float*)scratch((size_t)ncta * wcount * sizeof(float));
+	corr1ord_bprop_W_f32_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
+	DB_LAUNCH_CHECK();
+	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount, (size_t)32), 65535), 256, 0, state().stream>>>(dW, nullptr, a.partial, wcount, 0, ncta, 1);
+	DB_LAUNCH_CHECK();
 }
 
 static unsigned pick_fb(unsigned nf, unsigned m, size_t per_filter_bytes, size_t budget)
@@ -567,7 +668,7 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
 	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
-	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount + nf, (size_t)32), 65535), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta);
+	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount + nf, (size_t)32), 65535), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta, 0);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }

@@ -173,6 +173,17 @@ def test_speed_against_the_reference_kernels(ref, capsys):
     t["ref poolrgn(all)"] = timeit(lambda: ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), PT["all"]))
     t["new api_poolrgn(all)"] = timeit(lambda: ks.poolrgn(sarr, sR, "all", want_argmax=True))
     t["new fused scan+bias+relu+pool"] = timeit(lambda: fused.scanpool(tW, tb, sX.tensor.view(-1), tR, "all", want_argmax=True))
+    # backward operators: filter gradient from dZ, pooling gradient scattered into the activation
+    dZ = torch.randn((X.size, nf), dtype=torch.float32, device="cuda")
+    dW = torch.zeros((4 * m, nf), dtype=torch.float32, device="cuda")
+    sdZ, sdW = sm.sarray(dZ, np.float32), sm.sarray(dW, np.float32)
+    t["ref corr1ord_bprop_W"] = timeit(lambda: ref.ref_corr1ord_bprop_W(F32, P(dW), m, nf, P(tX), n, P(dZ)))
+    t["new api_corr1ord_bprop_W"] = timeit(lambda: ks.corr1ord_bprop_W(sdW, sX, sdZ, 4))
+    dP = torch.randn((nseq, 2 * nf), dtype=torch.float32, device="cuda")
+    sdP, sAt = sm.sarray(dP, np.float32), sm.sarray(At, np.uint32)
+    ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), PT["all"])          # argmax of the activation in Z
+    t["ref poolrgn_bprop(all)"] = timeit(lambda: ref.ref_poolrgn_bprop(F32, P(dZ), nf, P(tR), nseq, 2, P(dP), P(At), PT["all"]))
+    t["new api_poolrgn_bprop(all)"] = timeit(lambda: ks.poolrgn_bprop(sdZ, sR, sdP, sAt, "all"))
     zbytes = X.size * nf * 4
     with capsys.disabled():
         print("\n%-34s %9s %10s" % ("kernel (16384 x 101 nt, 16 x 24)", "ms", "GB/s of Z"))
