@@ -483,41 +483,101 @@ scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const flo
 // result; the second stage adds the partials, CTA ascending, into dW.
 struct bpw_args {
 	const uint8_t* X; const float* dZ; float* partial;
-	unsigned m, nf, n, npos, FB;
+	unsigned m, nf, n, npos, FB, logfb, vec;
 };
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, unsigned src_bytes)
+{
+	// src_bytes 0: nothing is read and the 16 bytes are zero-filled
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+	             :: "r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// Tile t0 of dZ into dzb[TR][FB]: 16-byte asynchronous copies when rows of dZ are
+// 16-byte aligned (a.vec), else plain loads.
+__device__ __forceinline__ void bpw_stage_dz(const bpw_args& a, unsigned t0, unsigned f0, float* dzb)
+{
+	const unsigned rows = min((unsigned)TR, a.n - t0);
+	if (a.vec) {
+		const unsigned lq = a.logfb - 2, q = 1u << lq;
+		for (unsigned t = threadIdx.x; t < (unsigned)TR << lq; t += blockDim.x) {
+			const unsigned r = t >> lq, e = (t & (q - 1)) * 4;
+			const bool ok = r < rows && f0 + e < a.nf;
+			cp_async16(dzb + (r << a.logfb) + e, ok ? a.dZ + (size_t)(t0 + r) * a.nf + f0 + e : a.dZ, ok ? 16u : 0u);
+		}
+	} else {
+		for (unsigned t = threadIdx.x; t < (unsigned)TR << a.logfb; t += blockDim.x) {
+			const unsigned r = t >> a.logfb, e = t & (a.FB - 1);
+			dzb[t] = (r < rows && f0 + e < a.nf) ? a.dZ[(size_t)(t0 + r) * a.nf + f0 + e] : 0.f;
+		}
+	}
+	asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+static constexpr int BPW_XB = 3;          // bases a thread carries for the next tile: (TR + m + 4) <= 3 * 128
+
+__device__ __forceinline__ void bpw_load_x(const bpw_args& a, unsigned t0, unsigned (&xb)[BPW_XB])
+{
+	#pragma unroll
+	for (int k = 0; k < BPW_XB; ++k) {
+		const unsigned i = t0 + threadIdx.x + k * blockDim.x;
+		xb[k] = (threadIdx.x + k * blockDim.x < TR + a.m + 4 && i < a.npos) ? a.X[i] : 254u;
+	}
+}
+
+__device__ __forceinline__ void bpw_store_oh(const bpw_args& a, const unsigned (&xb)[BPW_XB], float4* ohb)
+{
+	#pragma unroll
+	for (int k = 0; k < BPW_XB; ++k) {
+		const unsigned t = threadIdx.x + k * blockDim.x, x = xb[k];
+		if (t < TR + a.m + 4) {
+			const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
+			ohb[t] = make_float4(x == 0u ? 1.f : q, x == 1u ? 1.f : q, x == 2u ? 1.f : q, x == 3u ? 1.f : q);
+		}
+	}
+}
 
 __global__ void __launch_bounds__(512)
 corr1ord_bprop_W_f32_kernel(const bpw_args a)
 {
 	extern __shared__ __align__(16) unsigned char smem[];
-	const unsigned m = a.m, FB = a.FB;
-	float* dz = reinterpret_cast<float*>(smem);                         // [TR][FB]
-	float4* oh = reinterpret_cast<float4*>(dz + (size_t)TR * FB);       // [TR + m + 4]
+	const unsigned m = a.m, FB = a.FB, noh = TR + m + 4;
+	float* dz = reinterpret_cast<float*>(smem);                             // [2][TR][FB]
+	float4* oh = reinterpret_cast<float4*>(dz + 2 * (size_t)TR * FB);       // [2][TR + m + 4]
 	const unsigned f0 = blockIdx.y * FB;
 	const unsigned nunit = ((m + 3) / 4) * FB;
 	const bool is_unit = threadIdx.x < nunit;
-	const unsigned j0 = 4 * (threadIdx.x / FB), fl = threadIdx.x % FB;
+	const unsigned j0 = 4 * (threadIdx.x >> a.logfb), fl = threadIdx.x & (FB - 1);
 	float c[4][4];
 	#pragma unroll
 	for (int t = 0; t < 4; ++t)
 		#pragma unroll
 		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
-	for (unsigned t0 = blockIdx.x * TR; t0 < a.n; t0 += gridDim.x * TR) {
+	const unsigned stride = gridDim.x * TR;
+	unsigned xb[BPW_XB];
+	unsigned t0 = blockIdx.x * TR, buf = 0;
+	// Two buffers: while a tile is accumulated, the copies of the CTA's next tile are in
+	// flight and its bases wait in registers (turned into channel weights once the
+	// accumulation is done, when their loads have long returned).
+	if (t0 < a.n) {
+		bpw_stage_dz(a, t0, f0, dz);
+		bpw_load_x(a, t0, xb);
+		bpw_store_oh(a, xb, oh);
+	}
+	for (; t0 < a.n; t0 += stride, buf ^= 1) {
+		const unsigned next = t0 + stride;           // stride < 2^31 and n < 2^32 - stride: checked by the launcher
+		const bool more = next < a.n;
+		if (more) {
+			bpw_stage_dz(a, next, f0, dz + (buf ^ 1) * (size_t)TR * FB);
+			bpw_load_x(a, next, xb);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");
+		} else
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
 		__syncthreads();
-		for (unsigned t = threadIdx.x; t < TR + m + 4; t += blockDim.x) {
-			unsigned i = t0 + t, x = i < a.npos ? a.X[i] : 254u;
-			const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
-			oh[t] = make_float4(x == 0u ? 1.f : q, x == 1u ? 1.f : q, x == 2u ? 1.f : q, x == 3u ? 1.f : q);
-		}
 		const unsigned rows = min((unsigned)TR, a.n - t0);
-		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
-			const unsigned r = t / FB, e = t % FB;
-			dz[t] = (r < rows && f0 + e < a.nf) ? a.dZ[(size_t)(t0 + r) * a.nf + f0 + e] : 0.f;
-		}
-		__syncthreads();
 		if (is_unit) {
-			const float* dzc = dz + fl;
-			const float4* ohj = oh + j0;
+			const float* dzc = dz + buf * (size_t)TR * FB + fl;
+			const float4* ohj = oh + buf * noh + j0;
 			float4 w0 = ohj[0], w1 = ohj[1], w2 = ohj[2], w3 = ohj[3];
 			unsigned r = 0;
 			for (; r + 4 <= rows; r += 4) {
@@ -539,6 +599,8 @@ corr1ord_bprop_W_f32_kernel(const bpw_args a)
 				bwd_fma4(c[0], v, ohj[r]); bwd_fma4(c[1], v, ohj[r + 1]); bwd_fma4(c[2], v, ohj[r + 2]); bwd_fma4(c[3], v, ohj[r + 3]);
 			}
 		}
+		if (more) bpw_store_oh(a, xb, oh + (buf ^ 1) * noh);
+		__syncthreads();
 	}
 	float* out = a.partial + (size_t)blockIdx.x * 4 * m * a.nf;
 	if (is_unit && f0 + fl < a.nf) {
@@ -558,16 +620,23 @@ void launch_corr1ord_bprop_W_f32(float* dW, unsigned m, unsigned nf, const uint8
 	a.X = X; a.dZ = dZ; a.m = m; a.nf = nf; a.n = n; a.npos = n + m - 1;
 	a.FB = nf <= 16 ? 16 : 32;
 	while (a.FB > 16 && ((m + 3) / 4) * a.FB > 512) a.FB /= 2;
+	a.logfb = a.FB == 16 ? 4 : 5;
+	a.vec = (nf % 4 == 0 && ((uintptr_t)dZ & 15) == 0) ? 1u : 0u;
 	unsigned threads = (((m + 3) / 4) * a.FB + 31u) & ~31u;
 	DB_REQUIRE(threads <= 512, "ValueError: filter length %u is too long for this kernel", m);
 	if (threads < 128) threads = 128;
+	DB_REQUIRE((unsigned)TR + m + 4 <= BPW_XB * threads, "ValueError: filter length %u is too long for this kernel", m);
 	unsigned nfb = divup(nf, a.FB);
-	size_t smem = (size_t)TR * a.FB * 4 + (size_t)(TR + m + 4) * 16;
+	size_t smem = 2 * ((size_t)TR * a.FB * 4 + (size_t)(TR + m + 4) * 16);
 	DB_CUDA(cudaFuncSetAttribute(corr1ord_bprop_W_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	int per_sm = 1;
 	DB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, corr1ord_bprop_W_f32_kernel, (int)threads, smem));
-	unsigned slots = (unsigned)state().sm_count * (unsigned)std::max(per_sm, 1);
-	unsigned ncta = std::min(divup(n, (unsigned)TR), std::max(1u, slots / nfb));     // one resident wave
+	// one resident wave; no more than 16 warps an SM, which keep the FMA pipes busy once the
+	// copies overlap the arithmetic, so that the second stage has few partials to add
+	per_sm = std::max(1, std::min(per_sm, (int)(512 / threads)));
+	unsigned slots = (unsigned)state().sm_count * (unsigned)per_sm;
+	unsigned ncta = std::min(divup(n, (unsigned)TR), std::max(1u, slots / nfb));
+	DB_REQUIRE((uint64_t)n + (uint64_t)ncta * TR < (1ull << 32), "ValueError: too many rows (%u) for this kernel", n);
 	size_t wcount = (size_t)4 * m * nf;
 	a.partial = (float*)scratch((size_t)ncta * wcount * sizeof(float));
 	corr1ord_bprop_W_f32_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
