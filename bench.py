@@ -170,6 +170,12 @@ def _events_ms(fn, reps):
     return e0.elapsed_time(e1) / reps
 
 
+def _read_peaks():
+    """Peaks measured on this pool's GPUs (written beside this file by the harness); {} if absent."""
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    return json.load(open(pk)) if os.path.exists(pk) else {}
+
+
 def side_workloads(dev, with_cpu):
     """Short device-timed runs of the other benchmark configurations (inputs resident
     in HBM, CUDA events, 3+ warm-up passes), each beside the CPU restatement timed on
@@ -189,6 +195,30 @@ def side_workloads(dev, with_cpu):
         t = time.perf_counter(); fn(); dt = time.perf_counter() - t
         return units / dt
 
+    # FP32 add issue rate: SMs x 128 lanes x max SM clock, cross-checked by a register-only
+    # chain of adds on every lane.  The lookup-add kernels fetch one table operand per add
+    # from shared memory, whose return path (32 operands/clk/SM) is the tighter ceiling.
+    from deepbind_b200 import _lib
+    lib = _lib.load()
+    prop = torch.cuda.get_device_properties(dev)
+    sm_mhz = float(_read_peaks().get("sm_max_mhz") or 1965.0)
+    issue_peak = prop.multi_processor_count * 128 * sm_mhz * 1e6
+    for _ in range(3):
+        lib.db_fadd_probe(None, 512)
+    nadd = [0]
+
+    def probe():
+        nadd[0] = int(lib.db_fadd_probe(None, 4096))
+    probe_ms = _events_ms(probe, 5)
+    out["fp32_add_issue"] = {"unit": "Tadd/s", "nominal": issue_peak / 1e12, "measured_fadd_chain": nadd[0] / (probe_ms * 1e-3) / 1e12,
+                             "smem_operand_ceiling": issue_peak / 4 / 1e12}
+
+    def rates(rows, nf, m, ms, passes=1):
+        """Lookup-adds of `passes` scans of `rows` buffer rows, against the two ceilings."""
+        adds = float(rows) * nf * m * passes
+        return {"adds": adds, "Tadd_per_s": adds / (ms * 1e-3) / 1e12, "frac_fp32_add_issue": adds / (ms * 1e-3) / issue_peak,
+                "frac_smem_operand_ceiling": adds / (ms * 1e-3) / (issue_peak / 4)}
+
     # config 1: PBM-style forward scoring, 4096 x 40 nt, one model, exact FP32 kernel
     p = synth.model_params(1, M, 21, "max")
     Xh, Rh = synth.uniform_batch(4096, 40, M, seed=22)
@@ -197,7 +227,9 @@ def side_workloads(dev, with_cpu):
         net.score(X, R)
     ms = _events_ms(lambda: net.score(X, R), 20)
     out["pbm_forward"] = {"unit": "sequences/s", "value": 4096 / ms * 1e3, "ms": ms, "kernel": "f32 lookup-add, bit-exact",
-                          "cpu": cpu_time(lambda: orc.score_net(p, Xh, Rh, "max", 1), 4096)}
+                          "cpu": cpu_time(lambda: orc.score_net(p, Xh, Rh, "max", 1), 4096),
+                          "bound": "launch latency (99 M adds; one scan launch + head)",
+                          **rates(int((Rh[:, 1] - Rh[:, 0]).sum()), NMOTIF, M, ms)}
 
     # config 5: ragged both-strand RNA scoring, 200000 x U{20..200} nt, 5 % N, 16 x 16 filters, strand max
     p = synth.model_params(1, 16, 51, "max")
@@ -208,7 +240,9 @@ def side_workloads(dev, with_cpu):
     ms = _events_ms(lambda: net.score(X, R, strand_max=True), 10)
     ns = 20000
     out["ragged_rna"] = {"unit": "sequences/s", "value": 200000 / ms * 1e3, "ms": ms, "kernel": "f32 lookup-add, bit-exact",
-                         "cpu": cpu_time(lambda: orc.score_net(p, Xh[:Rh[2 * ns - 1, 1] + 15], Rh[:2 * ns], "max", 1, strand_max=True), ns)}
+                         "cpu": cpu_time(lambda: orc.score_net(p, Xh[:Rh[2 * ns - 1, 1] + 15], Rh[:2 * ns], "max", 1, strand_max=True), ns),
+                         "bound": "shared-memory operand return path", "hbm_gbs_algorithmic": (Xh.size + 4 * 200000) / (ms * 1e-3) / 1e9,
+                         **rates(int((Rh[:, 1] - Rh[:, 0]).sum()), NMOTIF, 16, ms)}
     del X, R
 
     def train(name, I, B, L, pool, hidden, loss, nbatch, reps, cpu_steps):
@@ -254,7 +288,8 @@ def side_workloads(dev, with_cpu):
             cpu = cpu_steps * B * I / (time.perf_counter() - t)
         out[name] = {"unit": "train samples/s (model x sample)", "value": I * B / ms * 1e3, "ms_per_step": ms,
                      "models": I, "minibatch": B, "kernel": "f32 fused scan+pool forward/backward, CUDA-graph replay",
-                     "cpu": cpu}
+                     "cpu": cpu, "adds_counted": "forward scan + recompute + filter gradient = 3 scans of the minibatch",
+                     **rates(B * (L + M - 1), NMOTIF * I, M, ms, passes=3)}
 
     # config 2: ChIP-seq-style training, one model, minibatch 128, allpool -> 32 hidden (dropout 0.5) -> sigmoid
     train("chip_train", 1, 128, 101, "all", 32, "nll", 64, 200, 5)
@@ -412,10 +447,7 @@ def main():
         raise SystemExit("tensor-core scan reported status %d" % int(status.item()))
 
     # dominant kernel alone: CUDA events on the launch stream around the scan launches of one step
-    peaks = {}
-    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(pk):
-        peaks = json.load(open(pk))
+    peaks = _read_peaks()
     prop = torch.cuda.get_device_properties(dev)
     barrier()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -231,3 +231,32 @@ DB_EXPORT void db_loss(int kind, const float* Z, const float* Y, const uint8_t* 
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }
+
+// Measurement aid (no counterpart in the reference): a register-only chain of FP32
+// adds on every lane of the GPU, eight independent accumulators per thread, 2048
+// threads per SM.  Timed by the caller with events on the library's stream, it gives
+// the non-FMA FP32 issue rate that the lookup-add kernels are set against.
+__global__ void __launch_bounds__(256) fadd_probe_kernel(float* sink, unsigned iters, float d)
+{
+	float a[8];
+	#pragma unroll
+	for (int k = 0; k < 8; ++k) a[k] = (float)(threadIdx.x + k);
+	for (unsigned i = 0; i < iters; ++i) {
+		#pragma unroll
+		for (int u = 0; u < 16; ++u)
+			#pragma unroll
+			for (int k = 0; k < 8; ++k) a[k] = __fadd_rn(a[k], d);
+	}
+	float s = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+	if (s == -123.456f && sink) sink[0] = s;       // never true for d > 0: keeps the chain alive
+}
+
+DB_EXPORT uint64_t db_fadd_probe(float* sink, uint32_t iters)
+{
+	DB_API_TRY
+	const unsigned ncta = (unsigned)state().sm_count * 8;
+	fadd_probe_kernel<<<ncta, 256, 0, state().stream>>>(sink, iters, 1.0f);
+	DB_LAUNCH_CHECK();
+	return (uint64_t)ncta * 256 * 128 * iters;
+	DB_API_CATCH_RETURN(0)
+}

@@ -143,6 +143,13 @@ void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, con
  * `decay` is the per-model decay spread over the flat parameter vector, zero on biases. */
 void db_l1_decay(float* dP, const float* P, const float* decay, size_t n);
 
+/* Measurement aid, no counterpart in the reference: launches a register-only chain of
+ * FP32 adds on every lane (2048 threads per SM, 128 * iters adds per thread) on the
+ * library's stream and returns the number of adds launched (0 on error).  Timed with
+ * events by the caller it gives the non-FMA FP32 issue rate the lookup-add kernels
+ * are measured against.  `sink` (nullable, one float) is never written. */
+uint64_t db_fadd_probe(float* sink, uint32_t iters);
+
 /* The dense head of one training step in one launch (no counterpart as one call;
  * replaces dropout -> full -> bias -> rectify -> full -> bias -> logistic -> loss and
  * their backward passes: elemwise.py:128-150,171,74-78, full.py:78-89, softmax.py:50-61,
