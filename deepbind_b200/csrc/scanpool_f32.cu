@@ -31,11 +31,19 @@ __device__ __forceinline__ unsigned code16_of(unsigned x)
 	return x < 4u ? x * 16u : (x == 254u ? 80u : 64u);
 }
 
+__device__ __forceinline__ void cp_async4(void* dst, const void* src, unsigned src_bytes)
+{
+	// copies src_bytes (0..4) and zero-fills the rest of the 4 bytes
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
+	             :: "r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+
 struct fwd_args {
 	const float* W; const float* bias; const uint8_t* X; const uint32_t* R;
 	float* pooled; uint32_t* argmax; uint16_t* actmask;
 	unsigned m, nf, npos, n, nregion, G, FB;
 	int relu, ptype;
+	unsigned xaligned;               // X starts on a 4-byte boundary: tiles of bases are fetched by cp.async
 };
 
 // Builds lut[j][q][c][4] for the CTA's filter block.
@@ -102,9 +110,11 @@ scanpool_fwd_kernel(const fwd_args a)
 	const unsigned FB = a.FB, NQ = FB / 4;
 	float* lut = reinterpret_cast<float*>(smem);                       // m*NQ*32 floats
 	float* act = lut + (size_t)m * NQ * 32;                            // FB*(TR+1) floats
-	uint8_t* xs = reinterpret_cast<uint8_t*>(act + (size_t)FB * (TR + 1));   // TR + m + 8 bytes (4-aligned)
+	unsigned* raw = reinterpret_cast<unsigned*>(act + (size_t)FB * (TR + 1));   // (TR + m + 12) / 4 units: the next tile's bases
+	uint8_t* xs = reinterpret_cast<uint8_t*>(raw + (TR + m + 12) / 4);          // TR + m + 8 bytes (4-aligned)
 	__shared__ unsigned rg0[GMAX], rg1[GMAX], rcnt[GMAX];
 	__shared__ unsigned s_lo, s_hi, s_sum;
+	__shared__ __align__(16) float sbias[64];                          // FB <= 64
 
 	const unsigned f0 = blockIdx.y * FB;
 	const unsigned g0 = blockIdx.x * a.G;
@@ -134,26 +144,54 @@ scanpool_fwd_kernel(const fwd_args a)
 	const unsigned rl = threadIdx.x % TR, fg = threadIdx.x / TR;
 	const unsigned char* lutp = reinterpret_cast<const unsigned char*>(lut) + fg * 512;
 	const unsigned stride = NQ * 128;
-	float bv[16];
-	#pragma unroll
-	for (int v = 0; v < 16; ++v) {
-		unsigned f = f0 + fg * 16 + v;
-		bv[v] = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
-	}
+	// the block's biases wait in shared memory: sixteen registers less across the scan
+	for (unsigned t = threadIdx.x; t < FB; t += blockDim.x) sbias[t] = (a.bias && f0 + t < a.nf) ? a.bias[f0 + t] : 0.f;
 	// pool-phase identity and state
 	const unsigned pg = threadIdx.x / FB, pf = threadIdx.x % FB;
 	const bool pool_thread = pg < ng && f0 + pf < a.nf;
 	float xmax = 0.f, xsum = 0.f; unsigned xidx = 0; bool started = false;
 
-	for (unsigned s = 0; s < nspan; ++s) {
-		const unsigned lo = one_span ? s_lo : rg0[s], hi = one_span ? s_hi : rg1[s];
-		for (unsigned t0 = lo; t0 < hi; t0 += TR) {
-			__syncthreads();
-			for (unsigned t = threadIdx.x; t < TR + m + 3; t += blockDim.x) {
-				unsigned i = t0 + t;
-				xs[t] = (uint8_t)(i < a.npos ? code16_of(a.X[i]) : 80u);
+	// Bases of a tile: 4-byte units by cp.async into `raw` (from the 4-byte boundary at or
+	// below t0) when X is 4-byte aligned, issued a tile ahead; turned into table offsets
+	// xs[] once the previous tile's scan is done.
+	auto fetch_x = [&](unsigned t0) {
+		if (!a.xaligned) return;
+		const unsigned b0 = t0 & ~3u, nunit = ((t0 & 3u) + TR + m + 3 + 3) / 4;
+		for (unsigned w = threadIdx.x; w < nunit; w += blockDim.x) {
+			const unsigned i = b0 + 4 * w;
+			const unsigned left = i < a.npos ? min(4u, a.npos - i) : 0u;
+			cp_async4(raw + w, a.X + (left ? i : 0u), left);
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	auto store_x = [&](unsigned t0) {
+		if (a.xaligned) {
+			// a thread converts the units it copied itself: its own wait is enough, no barrier
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
+			const unsigned off = t0 & 3u, nunit = (off + TR + m + 3 + 3) / 4;
+			for (unsigned w = threadIdx.x; w < nunit; w += blockDim.x) {
+				const unsigned v = raw[w];
+				#pragma unroll
+				for (unsigned j = 0; j < 4; ++j) {
+					const unsigned t = 4 * w + j - off;               // wraps for the bytes below t0
+					if (t < TR + m + 3) xs[t] = (uint8_t)code16_of(t0 + t < a.npos ? (v >> (8 * j)) & 0xffu : 254u);
+				}
 			}
-			__syncthreads();
+		} else
+			for (unsigned t = threadIdx.x; t < TR + m + 3; t += blockDim.x) {
+				const unsigned i = t0 + t;
+				xs[t] = (uint8_t)code16_of(i < a.npos ? a.X[i] : 254u);
+			}
+	};
+	unsigned s = 0, t0 = one_span ? s_lo : rg0[0];
+	fetch_x(t0);
+	for (;;) {
+		const unsigned hi = one_span ? s_hi : rg1[s];
+		store_x(t0);
+		__syncthreads();
+		if (t0 + TR < hi) fetch_x(t0 + TR);               // the next tile, recomputed below: nothing extra stays live over the scan
+		else if (s + 1 < nspan) fetch_x(rg0[s + 1]);
+		{
 			const unsigned row = t0 + rl;
 			if (row < hi) {
 				float z[16];
@@ -166,7 +204,7 @@ scanpool_fwd_kernel(const fwd_args a)
 				#pragma unroll
 				for (int v = 0; v < 16; ++v) {
 					float x = z[v];
-					if (a.bias) x = x + bv[v];
+					if (a.bias) x = x + sbias[fg * 16 + v];
 					if (a.relu) x = x > 0.f ? x : 0.f;
 					if (x > 0.f) bits |= 1u << v;
 					act[(fg * 16 + v) * (TR + 1) + rl] = x;
@@ -184,6 +222,11 @@ scanpool_fwd_kernel(const fwd_args a)
 					else { if (v > xmax) { xmax = v; xidx = r; } xsum += v; }
 				}
 			}
+		}
+		t0 += TR;
+		if (t0 >= hi) {
+			if (++s >= nspan) break;
+			t0 = rg0[s];
 		}
 	}
 	if (pool_thread) {
@@ -291,6 +334,7 @@ struct bwd_args {
 	float* partial;
 	unsigned m, nf, npos, n, nregion, G, FB;
 	int ptype;
+	unsigned xaligned, maligned;     // X / actmask start on a 4-byte boundary: their tiles are fetched by cp.async
 };
 
 __device__ __forceinline__ void bwd_fma4(float (&c)[4], float v, const float4& w)
@@ -298,136 +342,235 @@ __device__ __forceinline__ void bwd_fma4(float (&c)[4], float v, const float4& w
 	c[0] = fmaf(v, w.x, c[0]); c[1] = fmaf(v, w.y, c[1]); c[2] = fmaf(v, w.z, c[2]); c[3] = fmaf(v, w.w, c[3]);
 }
 
-__global__ void __launch_bounds__(512)
+static constexpr int KMAX = 8;           // region groups one CTA of the backward kernel can be dealt
+
+// Shared-memory views of the backward kernel.
+struct bwd_smem {
+	float* dz; float* davg; float* dmax; unsigned* amax; float4* oh; int* rowg;
+	float* rdp; unsigned* ram; unsigned* rx; unsigned* rm;      // raw copies of the next tile's inputs
+};
+
+// Asynchronous copies of what group g0's pooling gradient needs: dpooled and argmax of
+// its ng x FB (region, filter) pairs.
+__device__ __forceinline__ void bwd_fetch_group(const bwd_args& a, const bwd_smem& sm, unsigned g0, unsigned ng,
+                                                unsigned f0, unsigned logfb)
+{
+	const unsigned FB = 1u << logfb;
+	for (unsigned t = threadIdx.x; t < (ng << logfb); t += blockDim.x) {
+		const unsigned g = t >> logfb, f = f0 + (t & (FB - 1));
+		if (f >= a.nf) continue;
+		const size_t o = (size_t)(g0 + g) * a.nf + f;
+		if (a.ptype == DB_PT_ALL) { cp_async4(sm.rdp + 2 * t, a.dpooled + 2 * o, 4); cp_async4(sm.rdp + 2 * t + 1, a.dpooled + 2 * o + 1, 4); }
+		else cp_async4(sm.rdp + 2 * t, a.dpooled + o, 4);
+		if (a.ptype == DB_PT_MAX || a.ptype == DB_PT_ALL) cp_async4(sm.ram + t, a.argmax + o, 4);
+	}
+}
+
+// Asynchronous copies of a tile's bases (4-byte units from t0 on; X is 4-byte aligned
+// on this path and t0 is rounded down) and of its activity words (the one or two
+// 4-byte units that hold the CTA's FB bits of each row).
+__device__ __forceinline__ void bwd_fetch_tile(const bwd_args& a, const bwd_smem& sm, unsigned t0, unsigned srows,
+                                               unsigned f0, unsigned nwords, unsigned units)
+{
+	if (a.xaligned) {
+		const unsigned b0 = t0 & ~3u, nunit = ((t0 & 3u) + TR + a.m + 4 + 3) / 4;
+		for (unsigned w = threadIdx.x; w < nunit; w += blockDim.x) {
+			const unsigned i = b0 + 4 * w;
+			const unsigned left = i < a.npos ? min(4u, a.npos - i) : 0u;
+			cp_async4(sm.rx + w, a.X + (left ? i : 0u), left);
+		}
+	}
+	if (a.maligned) {
+		const size_t total = (size_t)a.npos * nwords;
+		for (unsigned t = threadIdx.x; t < srows * units; t += blockDim.x) {
+			const unsigned r = units == 2 ? t >> 1 : t, u = units == 2 ? t & 1u : 0u;
+			const size_t wi = ((size_t)(t0 + r) * nwords + (f0 >> 4)) & ~(size_t)1;       // first 16-bit word of the unit pair
+			const size_t w = wi + 2 * u;
+			const unsigned left = w < total ? (unsigned)min((size_t)2, total - w) * 2u : 0u;
+			cp_async4(sm.rm + 2 * r + u, a.actmask + (left ? w : 0), left);
+		}
+	}
+}
+
+__global__ void __maxnreg__(56)
 scanpool_bwd_kernel(const bwd_args a)
 {
 	extern __shared__ __align__(16) unsigned char smem[];
 	const unsigned m = a.m, FB = a.FB;
-	float* dz = reinterpret_cast<float*>(smem);                         // [TR][FB]
-	float* davg = dz + (size_t)TR * FB;                                 // [GMAX][FB] mean share per row
-	float* dmax = davg + GMAX * FB;                                     // [GMAX][FB]
-	unsigned* amax = reinterpret_cast<unsigned*>(dmax + GMAX * FB);     // [GMAX][FB] argmax row
+	bwd_smem sm;
+	sm.dz = reinterpret_cast<float*>(smem);                                // [TR][FB]
+	sm.davg = sm.dz + (size_t)TR * FB;                                     // [GMAX][FB] mean share per row
+	sm.dmax = sm.davg + GMAX * FB;                                         // [GMAX][FB]
+	sm.amax = reinterpret_cast<unsigned*>(sm.dmax + GMAX * FB);            // [GMAX][FB] argmax row
 	// per input row the weight each channel's gradient receives: one-hot, 1/4 each for N, 0 for a dropped base
-	float4* oh = reinterpret_cast<float4*>(amax + GMAX * FB);           // [TR + m + 4]
-	int* rowg = reinterpret_cast<int*>(oh + TR + m + 4);                // [TR] region of a row within this CTA, or -1
-	__shared__ unsigned rg0[GMAX], rg1[GMAX];
-	__shared__ unsigned s_lo, s_hi;
+	sm.oh = reinterpret_cast<float4*>(sm.amax + GMAX * FB);                // [TR + m + 4]
+	sm.rowg = reinterpret_cast<int*>(sm.oh + TR + m + 4);                  // [TR] region of a row within the group, or -1
+	sm.rdp = reinterpret_cast<float*>(sm.rowg + TR);                       // [GMAX][FB][2]
+	sm.ram = reinterpret_cast<unsigned*>(sm.rdp + 2 * GMAX * FB);          // [GMAX][FB]
+	sm.rm = sm.ram + GMAX * FB;                                            // [TR][2]
+	sm.rx = sm.rm + 2 * TR;                                                // [(TR + m + 4 + 3) / 4 + 1]
+	float* dz = sm.dz; float4* oh = sm.oh;
+	__shared__ unsigned gb0[KMAX][GMAX], gb1[KMAX][GMAX], glo[KMAX], ghi[KMAX];
 
 	const unsigned f0 = blockIdx.y * FB;
 	// accumulator identity: unit u = (tap group jg, filter fl) covers taps 4jg .. 4jg+3.
 	// The FB threads after the units sum dbias.
 	const unsigned nunit = ((m + 3) / 4) * FB;
 	const bool is_unit = threadIdx.x < nunit, is_bias = threadIdx.x >= nunit && threadIdx.x < nunit + FB;
-	const unsigned j0 = 4 * (threadIdx.x / FB), fl = threadIdx.x % FB;
+	const unsigned logfb = FB == 16 ? 4 : 5;                            // FB is 16 or 32
+	const unsigned j0 = 4 * (threadIdx.x >> logfb), fl = threadIdx.x & (FB - 1);
 	float c[4][4];
 	#pragma unroll
 	for (int t = 0; t < 4; ++t)
 		#pragma unroll
 		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
 	float bsum = 0.f;
-	const unsigned nwords = (a.nf + 15) / 16;
+	const unsigned nwords = (a.nf + 15) / 16, units = FB == 32 ? 2u : 1u;
+	// staging identity: filter column fl, rows sr0, sr0 + srstep, ...  (the block size is a
+	// multiple of FB, so the activity word and bit a thread tests are fixed)
+	const unsigned sr0 = threadIdx.x >> logfb, srstep = blockDim.x >> logfb;
+	const bool sfok = f0 + fl < a.nf;
+	const unsigned swi = (f0 + fl) >> 4, ssh = (f0 + fl) & 15;
 
-	// The CTA keeps its accumulators over all the region groups it is dealt (every
-	// gridDim.x-th group): one partial result per CTA, however many groups there are.
-	for (unsigned g0 = blockIdx.x * a.G; g0 < a.nregion; g0 += gridDim.x * a.G) {
-	const unsigned ng = min(a.G, a.nregion - g0);
-	__syncthreads();
-	// one thread per region fetches its bounds (one round trip, not ng of them); the last
-	// warp takes the job so that it overlaps the others' loads of dpooled below
-	if (threadIdx.x >= blockDim.x - GMAX) {
-		const unsigned g = threadIdx.x - (blockDim.x - GMAX);
-		if (g < ng) { rg0[g] = a.R[2 * (g0 + g)]; rg1[g] = a.R[2 * (g0 + g) + 1]; }
-	}
-	for (unsigned t = threadIdx.x; t < ng * FB; t += blockDim.x) {
-		unsigned g = t / FB, f = f0 + t % FB;
-		float va = 0.f, vm = 0.f; unsigned am = 0xffffffffu;
-		if (f < a.nf) {
-			size_t o = (size_t)(g0 + g) * a.nf + f;
-			unsigned cnt = a.R[2 * (g0 + g) + 1] - a.R[2 * (g0 + g)];
-			switch (a.ptype) {
-			case DB_PT_MAX: vm = a.dpooled[o]; am = a.argmax[o] / a.nf; break;
-			case DB_PT_AVG: va = a.dpooled[o] / (float)cnt; break;
-			case DB_PT_SUM: va = a.dpooled[o]; break;
-			default:        vm = a.dpooled[2*o]; va = a.dpooled[2*o+1] / (float)cnt; am = a.argmax[o] / a.nf; break;
-			}
-		}
-		davg[t] = va; dmax[t] = vm; amax[t] = am;
+	// The CTA is dealt every gridDim.x-th region group (at most KMAX of them) and keeps its
+	// accumulators over all of them: one partial result per CTA.  Their bounds come first,
+	// in one round trip, so that every later load can be issued a tile ahead.
+	const unsigned gstride = gridDim.x * a.G;
+	unsigned K = 0;
+	for (unsigned g0 = blockIdx.x * a.G; g0 < a.nregion && K < KMAX; g0 += gstride) ++K;
+	for (unsigned t = threadIdx.x; t < K * GMAX; t += blockDim.x) {
+		const unsigned k = t / GMAX, g = t % GMAX, rgn = blockIdx.x * a.G + k * gstride + g;
+		const bool ok = g < a.G && rgn < a.nregion;
+		gb0[k][g] = ok ? a.R[2 * rgn] : 0u;
+		gb1[k][g] = ok ? a.R[2 * rgn + 1] : 0u;
 	}
 	__syncthreads();
-	if (threadIdx.x == 0) {
+	if (threadIdx.x < K) {
 		unsigned lo = 0xffffffffu, hi = 0;
-		for (unsigned g = 0; g < ng; ++g)
-			if (rg1[g] > rg0[g]) { lo = min(lo, rg0[g]); hi = max(hi, rg1[g]); }
-		s_lo = lo; s_hi = hi;
+		for (unsigned g = 0; g < GMAX; ++g)
+			if (gb1[threadIdx.x][g] > gb0[threadIdx.x][g]) { lo = min(lo, gb0[threadIdx.x][g]); hi = max(hi, gb1[threadIdx.x][g]); }
+		glo[threadIdx.x] = lo; ghi[threadIdx.x] = hi;       // empty group: hi 0 <= lo
 	}
 	__syncthreads();
 
-	if (s_hi > s_lo)
-	for (unsigned t0 = s_lo; t0 < s_hi; t0 += TR) {
-		__syncthreads();
+	// Turns the raw copies of tile (k, t0) into the tile's operands: channel weights oh,
+	// the rows' regions, the group's pooling gradient (first tile of a group), then dZ.
+	auto convert = [&](unsigned k, unsigned t0, bool first) {
+		const unsigned g0 = blockIdx.x * a.G + k * gstride, ng = min(a.G, a.nregion - g0);
+		const unsigned srows = min((unsigned)TR, ghi[k] - t0);
 		for (unsigned t = threadIdx.x; t < TR + m + 4; t += blockDim.x) {
-			unsigned i = t0 + t, x = i < a.npos ? a.X[i] : 254u;
+			const unsigned i = t0 + t;
+			unsigned x = 254u;
+			if (i < a.npos) x = a.xaligned ? reinterpret_cast<const uint8_t*>(sm.rx)[(t0 & 3u) + t] : a.X[i];
 			const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
 			oh[t] = make_float4(x == 0u ? 1.f : q, x == 1u ? 1.f : q, x == 2u ? 1.f : q, x == 3u ? 1.f : q);
 		}
-		for (unsigned r = threadIdx.x; r < TR; r += blockDim.x) {
+		for (unsigned r = threadIdx.x; r < srows; r += blockDim.x) {
 			const unsigned row = t0 + r;
 			int g = -1;
-			if (row < s_hi)
-				for (unsigned k = 0; k < ng; ++k) if (row >= rg0[k] && row < rg1[k]) g = (int)k;
-			rowg[r] = g;
+			for (unsigned q = 0; q < ng; ++q) if (row >= gb0[k][q] && row < gb1[k][q]) g = (int)q;
+			sm.rowg[r] = g;
 		}
-		__syncthreads();
-		for (unsigned t = threadIdx.x; t < TR * FB; t += blockDim.x) {
-			const unsigned r = t / FB, e = t % FB, row = t0 + r;
-			const int g = rowg[r];
-			float v = 0.f;
-			if (g >= 0 && f0 + e < a.nf) {
-				const unsigned bits = a.actmask[(size_t)row * nwords + (f0 + e) / 16];
-				if ((bits >> ((f0 + e) & 15)) & 1u) {
-					v = davg[g * FB + e];
-					if (amax[g * FB + e] == row) v = v + dmax[g * FB + e];
+		if (first)
+			for (unsigned t = threadIdx.x; t < (ng << logfb); t += blockDim.x) {
+				const unsigned g = t >> logfb, f = f0 + (t & (FB - 1));
+				float va = 0.f, vm = 0.f; unsigned am = 0xffffffffu;
+				if (f < a.nf) {
+					const float cnt = (float)(gb1[k][g] - gb0[k][g]);
+					switch (a.ptype) {
+					case DB_PT_MAX: vm = sm.rdp[2 * t]; am = sm.ram[t] / a.nf; break;
+					case DB_PT_AVG: va = sm.rdp[2 * t] / cnt; break;
+					case DB_PT_SUM: va = sm.rdp[2 * t]; break;
+					default:        vm = sm.rdp[2 * t]; va = sm.rdp[2 * t + 1] / cnt; am = sm.ram[t] / a.nf; break;
+					}
 				}
+				sm.davg[t] = va; sm.dmax[t] = vm; sm.amax[t] = am;
 			}
-			dz[t] = v;
+		__syncthreads();
+		#pragma unroll 2
+		for (unsigned r = sr0; r < srows; r += srstep) {
+			const unsigned row = t0 + r;
+			const int g = sm.rowg[r];
+			unsigned bits = 0;
+			if (g >= 0 && sfok) {
+				const size_t wi = (size_t)row * nwords + swi;
+				bits = a.maligned ? reinterpret_cast<const uint16_t*>(sm.rm)[4 * r + (unsigned)(wi - (((size_t)row * nwords + (f0 >> 4)) & ~(size_t)1))]
+				                  : (unsigned)a.actmask[wi];
+			}
+			float v = 0.f;
+			if ((bits >> ssh) & 1u) {
+				v = sm.davg[g * FB + fl];
+				if (sm.amax[g * FB + fl] == row) v = v + sm.dmax[g * FB + fl];
+			}
+			dz[r * FB + fl] = v;
 		}
 		__syncthreads();
-		// Rows at or past n have no scan output, hence no filter gradient; rows past the
-		// last region of the group carry none either.
-		const unsigned row_end = min(a.n, s_hi);
-		const unsigned rows = min((unsigned)TR, row_end > t0 ? row_end - t0 : 0u);
-		if (is_unit) {
-			// Branch-free: the channel weights are 0, 1/4 or 1, so each product is exact and
-			// the fused multiply-add equals the reference's add of dZ (or dZ/4).
-			const float* dzc = dz + fl;
-			const float4* ohj = oh + j0;
-			float4 w0 = ohj[0], w1 = ohj[1], w2 = ohj[2], w3 = ohj[3];
-			unsigned r = 0;
-			for (; r + 4 <= rows; r += 4) {       // four rows per pass: the window rotates through its registers
-				float v = dzc[(r + 0) * FB];
-				bwd_fma4(c[0], v, w0); bwd_fma4(c[1], v, w1); bwd_fma4(c[2], v, w2); bwd_fma4(c[3], v, w3);
-				w0 = ohj[r + 4];
-				v = dzc[(r + 1) * FB];
-				bwd_fma4(c[0], v, w1); bwd_fma4(c[1], v, w2); bwd_fma4(c[2], v, w3); bwd_fma4(c[3], v, w0);
-				w1 = ohj[r + 5];
-				v = dzc[(r + 2) * FB];
-				bwd_fma4(c[0], v, w2); bwd_fma4(c[1], v, w3); bwd_fma4(c[2], v, w0); bwd_fma4(c[3], v, w1);
-				w2 = ohj[r + 6];
-				v = dzc[(r + 3) * FB];
-				bwd_fma4(c[0], v, w3); bwd_fma4(c[1], v, w0); bwd_fma4(c[2], v, w1); bwd_fma4(c[3], v, w2);
-				w3 = ohj[r + 7];
+	};
+	auto fetch = [&](unsigned k, unsigned t0, bool first) {
+		const unsigned g0 = blockIdx.x * a.G + k * gstride;
+		if (first) bwd_fetch_group(a, sm, g0, min(a.G, a.nregion - g0), f0, logfb);
+		bwd_fetch_tile(a, sm, t0, min((unsigned)TR, ghi[k] - t0), f0, nwords, units);
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+
+	unsigned k = 0;
+	while (k < K && ghi[k] <= glo[k]) ++k;
+	if (k < K) {
+		unsigned t0 = glo[k];
+		fetch(k, t0, true);
+		asm volatile("cp.async.wait_group 0;" ::: "memory");
+		__syncthreads();
+		convert(k, t0, true);
+		for (;;) {
+			// the tile after this one: its copies fly while this one is accumulated
+			unsigned nk = k, nt0 = t0 + TR;
+			if (nt0 >= ghi[k]) {
+				do ++nk; while (nk < K && ghi[nk] <= glo[nk]);
+				nt0 = nk < K ? glo[nk] : 0u;
 			}
-			for (; r < rows; ++r) {
-				const float v = dzc[r * FB];
-				bwd_fma4(c[0], v, ohj[r]); bwd_fma4(c[1], v, ohj[r + 1]); bwd_fma4(c[2], v, ohj[r + 2]); bwd_fma4(c[3], v, ohj[r + 3]);
+			if (nk < K) fetch(nk, nt0, nk != k);
+			// Rows at or past n have no scan output, hence no filter gradient; rows past the
+			// last region of the group carry none either (and are not staged).
+			const unsigned srows = min((unsigned)TR, ghi[k] - t0);
+			const unsigned row_end = min(a.n, ghi[k]);
+			const unsigned rows = min((unsigned)TR, row_end > t0 ? row_end - t0 : 0u);
+			if (is_unit) {
+				// Branch-free: the channel weights are 0, 1/4 or 1, so each product is exact and
+				// the fused multiply-add equals the reference's add of dZ (or dZ/4).
+				const float* dzc = dz + fl;
+				const float4* ohj = oh + j0;
+				float4 w0 = ohj[0], w1 = ohj[1], w2 = ohj[2], w3 = ohj[3];
+				unsigned r = 0;
+				for (; r + 4 <= rows; r += 4) {       // four rows per pass: the window rotates through its registers
+					float v = dzc[(r + 0) * FB];
+					bwd_fma4(c[0], v, w0); bwd_fma4(c[1], v, w1); bwd_fma4(c[2], v, w2); bwd_fma4(c[3], v, w3);
+					w0 = ohj[r + 4];
+					v = dzc[(r + 1) * FB];
+					bwd_fma4(c[0], v, w1); bwd_fma4(c[1], v, w2); bwd_fma4(c[2], v, w3); bwd_fma4(c[3], v, w0);
+					w1 = ohj[r + 5];
+					v = dzc[(r + 2) * FB];
+					bwd_fma4(c[0], v, w2); bwd_fma4(c[1], v, w3); bwd_fma4(c[2], v, w0); bwd_fma4(c[3], v, w1);
+					w2 = ohj[r + 6];
+					v = dzc[(r + 3) * FB];
+					bwd_fma4(c[0], v, w3); bwd_fma4(c[1], v, w0); bwd_fma4(c[2], v, w1); bwd_fma4(c[3], v, w2);
+					w3 = ohj[r + 7];
+				}
+				for (; r < rows; ++r) {
+					const float v = dzc[r * FB];
+					bwd_fma4(c[0], v, ohj[r]); bwd_fma4(c[1], v, ohj[r + 1]); bwd_fma4(c[2], v, ohj[r + 2]); bwd_fma4(c[3], v, ohj[r + 3]);
+				}
+			} else if (is_bias) {
+				float s = bsum;
+				for (unsigned r = 0; r < srows; ++r) s += dz[r * FB + fl];
+				bsum = s;
 			}
-		} else if (is_bias) {
-			float s = bsum;
-			for (unsigned r = 0; r < TR; ++r) s += dz[r * FB + fl];
-			bsum = s;
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
+			__syncthreads();
+			if (nk >= K) break;
+			convert(nk, nt0, nk != k);
+			k = nk; t0 = nt0;
 		}
 	}
-	}   // region groups
 	// partial[cta][(4m+1)][nf]; row 4m is dbias
 	float* out = a.partial + (size_t)blockIdx.x * (4 * m + 1) * a.nf;
 	if (is_unit && f0 + fl < a.nf) {
@@ -435,7 +578,7 @@ scanpool_bwd_kernel(const bwd_args a)
 		for (int t = 0; t < 4; ++t)
 			if (j0 + t < m) {
 				#pragma unroll
-				for (int k = 0; k < 4; ++k) out[(size_t)(4 * (j0 + t) + k) * a.nf + f0 + fl] = c[t][k];
+				for (int k2 = 0; k2 < 4; ++k2) out[(size_t)(4 * (j0 + t) + k2) * a.nf + f0 + fl] = c[t][k2];
 			}
 	}
 	if (is_bias && f0 + fl < a.nf) out[(size_t)4 * m * a.nf + f0 + fl] = bsum;
@@ -473,6 +616,38 @@ scanpool_bwd_reduce(float* __restrict__ dW, float* __restrict__ dbias, const flo
 		}
 		__syncthreads();
 	}
+}
+
+// Few partials: a thread per output reads them all at once (independent, coalesced
+// loads), four chains over parts p mod 4.  Again the order depends on `nparts` only.
+__global__ void __launch_bounds__(256)
+scanpool_bwd_reduce_few(float* __restrict__ dW, float* __restrict__ dbias, const float* __restrict__ partial,
+                        size_t wcount, unsigned nf, unsigned nparts, int accumulate)
+{
+	const size_t total = wcount + nf;
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= total) return;
+	const float* P = partial + i;
+	float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+	unsigned p = 0;
+	#pragma unroll 4
+	for (; p + 4 <= nparts; p += 4) {
+		s0 += P[(size_t)p * total]; s1 += P[(size_t)(p + 1) * total];
+		s2 += P[(size_t)(p + 2) * total]; s3 += P[(size_t)(p + 3) * total];
+	}
+	for (; p < nparts; ++p) s0 += P[(size_t)p * total];
+	const float s = (s0 + s1) + (s2 + s3);
+	if (i < wcount) dW[i] = accumulate ? dW[i] + s : s; else if (dbias) dbias[i - wcount] = s;
+}
+
+static void launch_bwd_reduce(float* dW, float* dbias, const float* partial, size_t wcount, unsigned nf, unsigned nparts, int accumulate)
+{
+	const size_t total = wcount + nf;
+	if (nparts <= 64 && total >= 8192)
+		scanpool_bwd_reduce_few<<<(unsigned)divup(total, (size_t)256), 256, 0, state().stream>>>(dW, dbias, partial, wcount, nf, nparts, accumulate);
+	else
+		scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(total, (size_t)32), 65535), 256, 0, state().stream>>>(dW, dbias, partial, wcount, nf, nparts, accumulate);
+	DB_LAUNCH_CHECK();
 }
 
 // ----------------------------------- the filter gradient alone (api_corr1ord_bprop_W)
@@ -641,8 +816,7 @@ void launch_corr1ord_bprop_W_f32(float* dW, unsigned m, unsigned nf, const uint8
 	a.partial = (float*)scratch((size_t)ncta * wcount * sizeof(float));
 	corr1ord_bprop_W_f32_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
-	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount, (size_t)32), 65535), 256, 0, state().stream>>>(dW, nullptr, a.partial, wcount, 0, ncta, 1);
-	DB_LAUNCH_CHECK();
+	launch_bwd_reduce(dW, nullptr, a.partial, wcount, 0, ncta, 1);
 }
 
 static unsigned pick_fb(unsigned nf, unsigned m, size_t per_filter_bytes, size_t budget)
@@ -652,11 +826,21 @@ static unsigned pick_fb(unsigned nf, unsigned m, size_t per_filter_bytes, size_t
 	return FB;
 }
 
-static unsigned pick_group(unsigned nregion, unsigned nfb)
+// Resident CTAs per SM of a forward kernel instance, remembered per (kernel, m, FB).
+template <typename K>
+static unsigned fwd_ctas_per_sm(K kern, unsigned m, unsigned FB, size_t smem)
 {
-	unsigned G = GMAX;
-	while (G > 1 && (size_t)divup(nregion, G) * nfb < (size_t)2 * state().sm_count) G /= 2;
-	return G;
+	struct entry { const void* k; unsigned m, FB, per_sm; };
+	static entry cache[16];
+	static unsigned used = 0;
+	for (unsigned i = 0; i < used; ++i)
+		if (cache[i].k == (const void*)kern && cache[i].m == m && cache[i].FB == FB) return cache[i].per_sm;
+	int per_sm = 1;
+	DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	DB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)(TR * FB / 16), smem));
+	per_sm = std::max(per_sm, 1);
+	if (used < 16) cache[used++] = entry{(const void*)kern, m, FB, (unsigned)per_sm};
+	return (unsigned)per_sm;
 }
 
 }  // namespace db
@@ -677,19 +861,34 @@ DB_EXPORT void db_scanpool_fwd(const float* W, uint32_t m, uint32_t nf, const fl
 	a.W = W; a.bias = bias; a.X = X; a.R = regions; a.pooled = pooled; a.argmax = argmax; a.actmask = actmask;
 	a.m = m; a.nf = nf; a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion;
 	a.relu = relu; a.ptype = ptype;
-	a.FB = pick_fb(nf, m, 32, 120 * 1024);
-	DB_REQUIRE((size_t)m * a.FB * 32 <= 160 * 1024, "ValueError: filter length %u is too long for the fused kernel", m);
-	unsigned nfb = divup(nf, a.FB);
-	a.G = pick_group(nregion, nfb);
-	size_t smem = (size_t)m * a.FB * 32 + (size_t)a.FB * (TR + 1) * 4 + TR + m + 16;
-	dim3 grid(divup(nregion, a.G), nfb), block(TR * a.FB / 16);
-	auto launch = [&](auto kern) {
-		DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	const unsigned fbmax = pick_fb(nf, m, 32, 120 * 1024);
+	DB_REQUIRE((size_t)m * fbmax * 32 <= 160 * 1024, "ValueError: filter length %u is too long for the fused kernel", m);
+	a.xaligned = ((uintptr_t)X & 3) == 0;
+	auto smem_of = [&](unsigned FB) { return (size_t)m * FB * 32 + (size_t)FB * (TR + 1) * 4 + 2 * (size_t)(TR + m + 16); };
+	auto run = [&](auto kern) {
+		// Filters per CTA and regions per CTA: the pair with the least work on the busiest SM,
+		// a CTA costing its rows plus a fixed share (table build, first loads).  Small batches
+		// then run as one well-filled resident wave instead of one and a bit.
+		const double rpr = std::max(1u, npos / nregion);
+		double best = 0; a.FB = 0; a.G = 1;
+		for (unsigned FB = fbmax; FB >= 16; FB /= 2) {
+			const unsigned per_sm = fwd_ctas_per_sm(kern, m, FB, smem_of(FB));
+			const size_t nfb = divup(nf, FB);
+			for (unsigned G = GMAX; G >= 1; --G) {
+				const size_t ncta = (size_t)divup(nregion, G) * nfb;
+				const size_t load = divup(ncta, (size_t)state().sm_count);
+				const double cost = (double)load * FB * (G * rpr + 100.0) * (load > per_sm ? 1.15 : 1.0);
+				if (a.FB == 0 || cost < best) { best = cost; a.FB = FB; a.G = G; }
+			}
+		}
+		const size_t smem = smem_of(a.FB);
+		dim3 grid(divup(nregion, a.G), divup(nf, a.FB)), block(TR * a.FB / 16);
+		DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_of(fbmax)));
 		kern<<<grid, block, smem, state().stream>>>(a);
 	};
-	if (m == 24) launch(scanpool_fwd_kernel<24>);
-	else if (m == 16) launch(scanpool_fwd_kernel<16>);
-	else launch(scanpool_fwd_kernel<0>);
+	if (m == 24) run(scanpool_fwd_kernel<24>);
+	else if (m == 16) run(scanpool_fwd_kernel<16>);
+	else run(scanpool_fwd_kernel<0>);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }
@@ -723,7 +922,9 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	// Regions per group: about one tile of rows.  CTAs per filter block: as many as are resident
 	// at once, each looping over its share of the groups, so that no second, part-filled wave runs.
 	a.G = std::max(1u, std::min((unsigned)GMAX, (unsigned)TR / std::max(1u, npos / nregion)));
-	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + (size_t)(TR + m + 4) * 16 + (size_t)TR * 4 + 16;
+	a.xaligned = ((uintptr_t)X & 3) == 0; a.maligned = ((uintptr_t)actmask & 3) == 0;
+	size_t smem = (size_t)TR * a.FB * 4 + (size_t)GMAX * a.FB * 12 + (size_t)(TR + m + 4) * 16 + (size_t)TR * 4 +
+	              (size_t)GMAX * a.FB * 12 + (size_t)TR * 8 + (size_t)(TR + m + 16) + 16;
 	DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	int per_sm = 1;
 	DB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scanpool_bwd_kernel, (int)threads, smem));
@@ -734,10 +935,10 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 		if ((size_t)divup(nregion, G) * nfb >= (size_t)4 * slots) { a.G = G; break; }
 	unsigned ngroup = divup(nregion, a.G);
 	unsigned ncta = (size_t)ngroup * nfb >= (size_t)4 * slots ? ngroup : std::min(ngroup, std::max(1u, slots / nfb));
+	ncta = std::max(ncta, divup(ngroup, (unsigned)KMAX));            // a CTA holds the bounds of at most KMAX groups
 	a.partial = (float*)scratch((size_t)ncta * (wcount + nf) * sizeof(float));
 	scanpool_bwd_kernel<<<dim3(ncta, nfb), threads, smem, state().stream>>>(a);
 	DB_LAUNCH_CHECK();
-	scanpool_bwd_reduce<<<(unsigned)std::min<size_t>(divup(wcount + nf, (size_t)32), 65535), 256, 0, state().stream>>>(dW, dbias, a.partial, wcount, nf, ncta, 0);
-	DB_LAUNCH_CHECK();
+	launch_bwd_reduce(dW, dbias, a.partial, wcount, nf, ncta, 0);
 	DB_API_CATCH
 }
