@@ -288,7 +288,8 @@ def side_workloads(dev, with_cpu):
             cpu = cpu_steps * B * I / (time.perf_counter() - t)
         out[name] = {"unit": "train samples/s (model x sample)", "value": I * B / ms * 1e3, "ms_per_step": ms,
                      "models": I, "minibatch": B, "kernel": "f32 fused scan+pool forward/backward, CUDA-graph replay",
-                     "cpu": cpu, "adds_counted": "forward scan + recompute + filter gradient = 3 scans of the minibatch",
+                     "cpu": cpu, "adds_counted": "dense equivalent: forward scan + recompute + filter gradient = 3 scans of the minibatch "
+                                                "(with max pooling alone the backward kernel visits only the argmax rows)",
                      **rates(B * (L + M - 1), NMOTIF * I, M, ms, passes=3)}
 
     # config 2: ChIP-seq-style training, one model, minibatch 128, allpool -> 32 hidden (dropout 0.5) -> sigmoid

@@ -584,6 +584,99 @@ scanpool_bwd_kernel(const bwd_args a)
 	if (is_bias && f0 + fl < a.nf) out[(size_t)4 * m * a.nf + f0 + fl] = bsum;
 }
 
+// ---- max pooling alone: dZ has one nonzero row per (region, filter), the argmax row, so
+// the dense accumulation above would add 0 for every other row.  Here a CTA stages, for a
+// chunk of regions and FB filters, that row and its delta (0 when the unit was inactive
+// or the region empty), and a thread per (four taps, filter) adds delta x channel weights
+// of the four bases its taps see at that row; regions ascending, so the sums are the
+// dense kernel's with the exact zeros left out.  One chunk: results go straight to dW
+// and dbias; several: per-chunk partials, added by the second stage.
+static constexpr int RC = 32;            // regions staged per round, at most
+
+struct bwdmax_args {
+	const uint8_t* X; const uint32_t* R; const float* dpooled; const uint32_t* argmax; const uint16_t* actmask;
+	float* partial; float* dW; float* dbias;
+	unsigned m, nf, npos, n, nregion, FB, rper, rc;  // rper: regions per chunk; rc: regions per round
+};
+
+__global__ void __launch_bounds__(512)
+scanpool_bwd_max_kernel(const bwdmax_args a)
+{
+	extern __shared__ __align__(16) unsigned char smem[];       // [rc][FB][mp] bases under the taps at the argmax rows
+	__shared__ float dval[RC * 32], dwv[RC * 32];               // delta for dbias; for dW (0 when the row has no scan output)
+	const unsigned m = a.m, mp = (m + 3u) & ~3u, FB = a.FB, logfb = FB == 16 ? 4 : 5;
+	const unsigned f0 = blockIdx.y * FB;
+	const unsigned nunit = ((m + 3) / 4) * FB;
+	const bool is_unit = threadIdx.x < nunit, is_bias = threadIdx.x >= nunit && threadIdx.x < nunit + FB;
+	const unsigned j0 = 4 * (threadIdx.x >> logfb), fl = threadIdx.x & (FB - 1);
+	const unsigned nwords = (a.nf + 15) / 16;
+	float c[4][4];
+	#pragma unroll
+	for (int t = 0; t < 4; ++t)
+		#pragma unroll
+		for (int k = 0; k < 4; ++k) c[t][k] = 0.f;
+	float bsum = 0.f;
+	const unsigned gbeg = blockIdx.x * a.rper, gend = min(a.nregion, gbeg + a.rper);
+	for (unsigned g0 = gbeg; g0 < gend; g0 += a.rc) {
+		const unsigned ng = min(a.rc, gend - g0);
+		__syncthreads();
+		for (unsigned t = threadIdx.x; t < (ng << logfb); t += blockDim.x) {
+			const unsigned g = g0 + (t >> logfb), f = f0 + (t & (FB - 1));
+			float d = 0.f; unsigned row = 0;
+			if (f < a.nf) {
+				const size_t o = (size_t)g * a.nf + f;
+				const uint2 rg = make_uint2(a.R[2 * g], a.R[2 * g + 1]);
+				const float dp = a.dpooled[o];                       // independent of the row: in flight with argmax
+				row = a.argmax[o] / a.nf;
+				const unsigned bits = a.actmask[(size_t)row * nwords + (f >> 4)];
+				if (rg.y > rg.x && ((bits >> (f & 15)) & 1u)) d = dp;
+			}
+			const bool scanned = row < a.n;                      // rows at or past n have no scan output
+			dval[t] = d; dwv[t] = scanned ? d : 0.f;
+			if (scanned && d != 0.f) {
+				unsigned char* w = smem + (size_t)t * mp;
+				for (unsigned j = 0; j < m; ++j) w[j] = a.X[row + j];
+			}
+		}
+		__syncthreads();
+		if (is_unit) {
+			for (unsigned g = 0; g < ng; ++g) {
+				const unsigned t = (g << logfb) + fl;
+				const float d = dwv[t];
+				if (d == 0.f) continue;
+				const unsigned xw = *reinterpret_cast<const unsigned*>(smem + (size_t)t * mp + j0);
+				#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					if (j0 + k < m) {
+						const unsigned x = (xw >> (8 * k)) & 0xffu;
+						const float q = (x >= 4u && x != 254u) ? 0.25f : 0.f;
+						c[k][0] = fmaf(d, x == 0u ? 1.f : q, c[k][0]); c[k][1] = fmaf(d, x == 1u ? 1.f : q, c[k][1]);
+						c[k][2] = fmaf(d, x == 2u ? 1.f : q, c[k][2]); c[k][3] = fmaf(d, x == 3u ? 1.f : q, c[k][3]);
+					}
+			}
+		} else if (is_bias) {
+			float s = bsum;
+			for (unsigned g = 0; g < ng; ++g) s += dval[(g << logfb) + fl];
+			bsum = s;
+		}
+	}
+	// one chunk: the results themselves; else partial[chunk][(4m+1)][nf], row 4m = dbias
+	const bool direct = gridDim.x == 1;
+	float* out = direct ? a.dW : a.partial + (size_t)blockIdx.x * (4 * m + 1) * a.nf;
+	if (is_unit && f0 + fl < a.nf) {
+		#pragma unroll
+		for (int t = 0; t < 4; ++t)
+			if (j0 + t < m) {
+				#pragma unroll
+				for (int k = 0; k < 4; ++k) out[(size_t)(4 * (j0 + t) + k) * a.nf + f0 + fl] = c[t][k];
+			}
+	}
+	if (is_bias && f0 + fl < a.nf) {
+		if (!direct) out[(size_t)4 * m * a.nf + f0 + fl] = bsum;
+		else if (a.dbias) a.dbias[f0 + fl] = bsum;
+	}
+}
+
 // Second stage: sums the per-CTA partial gradients in a fixed order.  A CTA of eight
 // warps owns 32 consecutive outputs (one coalesced row segment per part); warp w
 // adds the parts w, w+8, ... with four independent chains, and warp 0 combines the
@@ -910,6 +1003,31 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 	}
 	DB_REQUIRE(X && regions && dpooled && actmask, "ValueError: db_scanpool_bwd got a NULL pointer");
 	DB_REQUIRE(argmax || (ptype != DB_PT_MAX && ptype != DB_PT_ALL), "ValueError: pooledmaps_argmax must be specified for max pooling.");
+	if (ptype == DB_PT_MAX) {
+		bwdmax_args x;
+		x.X = X; x.R = regions; x.dpooled = dpooled; x.argmax = argmax; x.actmask = actmask; x.dW = dW; x.dbias = dbias;
+		x.m = m; x.nf = nf; x.npos = npos; x.n = npos >= m ? npos - m + 1 : 0; x.nregion = nregion;
+		x.FB = nf <= 16 ? 16 : 32;
+		while (x.FB > 16 && ((m + 3) / 4 + 1) * x.FB > 512) x.FB /= 2;
+		const unsigned nfb = divup(nf, x.FB);
+		unsigned threads = (((m + 3) / 4 + 1) * x.FB + 31u) & ~31u;
+		DB_REQUIRE(threads <= 512, "ValueError: filter length %u is too long for the fused backward kernel", m);
+		// Chunks of at least eight regions (about one staged (region, filter) pair per thread, so that
+		// the dependent loads argmax -> activity word, bases of all pairs are in flight together),
+		// no more than fill the GPU four CTAs deep.
+		unsigned nchunk = std::max(1u, std::min(nregion / 8, divup(4u * (unsigned)state().sm_count, nfb)));
+		x.rper = divup(nregion, nchunk);
+		nchunk = divup(nregion, x.rper);
+		x.partial = nchunk > 1 ? (float*)scratch((size_t)nchunk * (wcount + nf) * sizeof(float)) : nullptr;
+		const unsigned mp = (m + 3u) & ~3u;
+		x.rc = std::max(1u, std::min((unsigned)RC, (unsigned)(64 * 1024 / ((size_t)x.FB * mp))));
+		const size_t smem = (size_t)x.rc * x.FB * mp;
+		DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_max_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, (size_t)48 * 1024)));
+		scanpool_bwd_max_kernel<<<dim3(nchunk, nfb), threads, smem, state().stream>>>(x);
+		DB_LAUNCH_CHECK();
+		if (nchunk > 1) launch_bwd_reduce(dW, dbias, x.partial, wcount, nf, nchunk, 0);
+		return;
+	}
 	bwd_args a;
 	a.X = X; a.R = regions; a.dpooled = dpooled; a.argmax = argmax; a.actmask = actmask;
 	a.m = m; a.nf = nf; a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.ptype = ptype;
