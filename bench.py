@@ -490,7 +490,7 @@ def main():
                 k1.record(); k1.synchronize()
                 ktime += k0.elapsed_time(k1)
         kernel_ms = ktime / (min(reps, 2) * nchunk)
-        adds = adds_per_seq(I) * min(args.chunk, nseq)
+        adds = adds_per_seq(I) * nseq / nchunk                    # per launch, on average (the last chunk may be short)
         sm_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz") or 1965.0
         lut_peak = prop.multi_processor_count * 32 * sm_max * 1e6
         roofline = {"bound": "smem-lookup", "kernel": "scanpool_fwd_kernel<24> (FP32 lookup-add)",
