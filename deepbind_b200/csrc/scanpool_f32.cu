@@ -587,7 +587,7 @@ scanpool_bwd_kernel(const bwd_args a)
 // ---- max pooling alone: dZ has one nonzero row per (region, filter), the argmax row, so
 // the dense accumulation above would add 0 for every other row.  Here a CTA stages, for a
 // chunk of regions and FB filters, that row and its delta (0 when the unit was inactive
-// or the region empty), and a thread per (four taps, filter) adds delta x channel weights
+// there), and a thread per (four taps, filter) adds delta x channel weights
 // of the four bases its taps see at that row; regions ascending, so the sums are the
 // dense kernel's with the exact zeros left out.  One chunk: results go straight to dW
 // and dbias; several: per-chunk partials, added by the second stage.
@@ -625,11 +625,10 @@ scanpool_bwd_max_kernel(const bwdmax_args a)
 			float d = 0.f; unsigned row = 0;
 			if (f < a.nf) {
 				const size_t o = (size_t)g * a.nf + f;
-				const uint2 rg = make_uint2(a.R[2 * g], a.R[2 * g + 1]);
 				const float dp = a.dpooled[o];                       // independent of the row: in flight with argmax
 				row = a.argmax[o] / a.nf;
 				const unsigned bits = a.actmask[(size_t)row * nwords + (f >> 4)];
-				if (rg.y > rg.x && ((bits >> (f & 15)) & 1u)) d = dp;
+				if ((bits >> (f & 15)) & 1u) d = dp;                 // an empty region's delta lands on its recorded row too (poolrgn_bprop.cuh:57)
 			}
 			const bool scanned = row < a.n;                      // rows at or past n have no scan output
 			dval[t] = d; dwv[t] = scanned ? d : 0.f;

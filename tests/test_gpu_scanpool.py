@@ -151,3 +151,53 @@ def test_fused_equals_unfused_device_chain(cuda):
     P, A = ks.poolrgn(Z, sR, "all", want_argmax=True)
     gP, gA, _ = fused.scanpool(sW.tensor, tb, sX.tensor.view(-1), sR.tensor, "all", want_argmax=True)
     assert torch.equal(gP, P.tensor) and torch.equal(gA, A.tensor)
+
+
+def _backward_case(orc, m, nf, X, R, W, b, ptype):
+    """Oracle chain (poolrgn_bprop -> rectifier -> filter gradient, float64 sums) beside the fused backward."""
+    from deepbind_b200 import fused
+    Z = orc.corr1ord(W, X)
+    act = np.maximum(Z + b, 0)
+    P, A = orc.poolrgn(act, R, ptype, True)
+    rng = np.random.default_rng(5)
+    dP = rng.standard_normal(P.shape).astype(f32)
+    dA = orc.poolrgn_bprop(np.zeros(act.shape, np.float64), R, dP.astype(np.float64), A, ptype)
+    dZ = dA * np.sign(act)
+    want_db = dZ.sum(axis=0)
+    want_dW = orc.corr1ord_bprop_W(np.zeros((4 * m, nf)), X, dZ)
+    tW, tb, tX, tR, tdP = to_dev(W, b, X, R, dP)
+    gP, gA, gM = fused.scanpool(tW, tb, tX, tR, ptype, want_argmax=True, want_actmask=True)
+    assert np.array_equal(gP.cpu().numpy(), orc.scanpool(W, b, True, X, R, ptype, True)[0], equal_nan=True)
+    dW, db = fused.scanpool_bprop(m, nf, tX, tR, ptype, tdP, gA, gM)
+    scale = np.abs(dZ).sum(axis=0).max() + 1e-30
+    assert np.max(np.abs(dW.cpu().numpy() - want_dW)) <= 1e-5 * scale
+    assert np.max(np.abs(db.cpu().numpy() - want_db)) <= 1e-5 * scale
+
+
+@pytest.mark.parametrize("ptype", ["max", "avg", "all"])
+def test_backward_few_long_regions(cuda, orc, ptype):
+    """Nine regions of 500-900 rows: several tiles per region group in the dense kernel, and
+    the max-pooling kernel writing its results without a second stage."""
+    from deepbind_b200 import synth
+    m, nf = 11, 64
+    X, R = synth.ragged_batch(9, 500, 900, m, seed=77)
+    rng = np.random.default_rng(78)
+    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(f32)
+    b = rng.uniform(-0.1, 0.0, nf).astype(f32)
+    _backward_case(orc, m, nf, X, R, W, b, ptype)
+
+
+def test_backward_max_regions_in_any_layout(cuda, orc):
+    """Max pooling with gaps between regions, regions out of order, an empty region (its delta lands
+    on the row the forward pass recorded for it, as in the reference) and rows past the last scan
+    output (bias gradient only)."""
+    rng = np.random.default_rng(9)
+    m, nf, npos = 6, 40, 3000
+    X = rng.integers(0, 4, size=npos, dtype=np.uint8)
+    X[rng.random(npos) < 0.03] = 255
+    W = (rng.standard_normal((4 * m, nf)) * 0.2).astype(f32)
+    b = rng.uniform(-0.2, 0.1, nf).astype(f32)
+    R = np.array([[2900, 3000], [10, 50], [2000, 2001], [700, 1500], [60, 60], [0, 3], [100, 101], [1500, 1501],
+                  [1600, 1700], [1700, 1800], [1800, 1900], [200, 300], [300, 400], [400, 500], [500, 600], [600, 650],
+                  [2100, 2200], [2200, 2300]], np.uint32)
+    _backward_case(orc, m, nf, X, R, W, b, "max")
