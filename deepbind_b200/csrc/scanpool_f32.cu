@@ -43,7 +43,6 @@ struct fwd_args {
 	float* pooled; uint32_t* argmax; uint16_t* actmask;
 	unsigned m, nf, npos, n, nregion, G, FB;
 	int relu, ptype;
-	unsigned xaligned;               // X starts on a 4-byte boundary: tiles of bases are fetched by cp.async
 };
 
 // Builds lut[j][q][c][4] for the CTA's filter block.
@@ -110,8 +109,7 @@ scanpool_fwd_kernel(const fwd_args a)
 	const unsigned FB = a.FB, NQ = FB / 4;
 	float* lut = reinterpret_cast<float*>(smem);                       // m*NQ*32 floats
 	float* act = lut + (size_t)m * NQ * 32;                            // FB*(TR+1) floats
-	unsigned* raw = reinterpret_cast<unsigned*>(act + (size_t)FB * (TR + 1));   // (TR + m + 12) / 4 units: the next tile's bases
-	uint8_t* xs = reinterpret_cast<uint8_t*>(raw + (TR + m + 12) / 4);          // TR + m + 8 bytes (4-aligned)
+	uint8_t* xs = reinterpret_cast<uint8_t*>(act + (size_t)FB * (TR + 1));   // TR + m + 8 bytes (4-aligned)
 	__shared__ unsigned rg0[GMAX], rg1[GMAX], rcnt[GMAX];
 	__shared__ unsigned s_lo, s_hi, s_sum;
 	__shared__ __align__(16) float sbias[64];                          // FB <= 64
@@ -151,46 +149,19 @@ scanpool_fwd_kernel(const fwd_args a)
 	const bool pool_thread = pg < ng && f0 + pf < a.nf;
 	float xmax = 0.f, xsum = 0.f; unsigned xidx = 0; bool started = false;
 
-	// Bases of a tile: 4-byte units by cp.async into `raw` (from the 4-byte boundary at or
-	// below t0) when X is 4-byte aligned, issued a tile ahead; turned into table offsets
-	// xs[] once the previous tile's scan is done.
-	auto fetch_x = [&](unsigned t0) {
-		if (!a.xaligned) return;
-		const unsigned b0 = t0 & ~3u, nunit = ((t0 & 3u) + TR + m + 3 + 3) / 4;
-		for (unsigned w = threadIdx.x; w < nunit; w += blockDim.x) {
-			const unsigned i = b0 + 4 * w;
-			const unsigned left = i < a.npos ? min(4u, a.npos - i) : 0u;
-			cp_async4(raw + w, a.X + (left ? i : 0u), left);
-		}
-		asm volatile("cp.async.commit_group;" ::: "memory");
-	};
+	// Two barriers per tile: the bases of tile i+1 are staged right after the pool phase of
+	// tile i (whose scan, the last reader of xs[], ended at the barrier before that phase).
 	auto store_x = [&](unsigned t0) {
-		if (a.xaligned) {
-			// a thread converts the units it copied itself: its own wait is enough, no barrier
-			asm volatile("cp.async.wait_group 0;" ::: "memory");
-			const unsigned off = t0 & 3u, nunit = (off + TR + m + 3 + 3) / 4;
-			for (unsigned w = threadIdx.x; w < nunit; w += blockDim.x) {
-				const unsigned v = raw[w];
-				#pragma unroll
-				for (unsigned j = 0; j < 4; ++j) {
-					const unsigned t = 4 * w + j - off;               // wraps for the bytes below t0
-					if (t < TR + m + 3) xs[t] = (uint8_t)code16_of(t0 + t < a.npos ? (v >> (8 * j)) & 0xffu : 254u);
-				}
-			}
-		} else
-			for (unsigned t = threadIdx.x; t < TR + m + 3; t += blockDim.x) {
-				const unsigned i = t0 + t;
-				xs[t] = (uint8_t)code16_of(i < a.npos ? a.X[i] : 254u);
-			}
+		for (unsigned t = threadIdx.x; t < TR + m + 3; t += blockDim.x) {
+			const unsigned i = t0 + t;
+			xs[t] = (uint8_t)code16_of(i < a.npos ? a.X[i] : 254u);
+		}
 	};
 	unsigned s = 0, t0 = one_span ? s_lo : rg0[0];
-	fetch_x(t0);
 	for (;;) {
 		const unsigned hi = one_span ? s_hi : rg1[s];
 		store_x(t0);
 		__syncthreads();
-		if (t0 + TR < hi) fetch_x(t0 + TR);               // the next tile, recomputed below: nothing extra stays live over the scan
-		else if (s + 1 < nspan) fetch_x(rg0[s + 1]);
 		{
 			const unsigned row = t0 + rl;
 			if (row < hi) {
@@ -201,10 +172,16 @@ scanpool_fwd_kernel(const fwd_args a)
 					for (int v = 0; v < 16; ++v) z[v] = 0.f;
 				}
 				unsigned bits = 0;
+				float bv[16];
+				#pragma unroll
+				for (int v = 0; v < 16; v += 4) {
+					const float4 q = *reinterpret_cast<const float4*>(sbias + fg * 16 + v);
+					bv[v] = q.x; bv[v + 1] = q.y; bv[v + 2] = q.z; bv[v + 3] = q.w;
+				}
 				#pragma unroll
 				for (int v = 0; v < 16; ++v) {
 					float x = z[v];
-					if (a.bias) x = x + sbias[fg * 16 + v];
+					if (a.bias) x = x + bv[v];
 					if (a.relu) x = x > 0.f ? x : 0.f;
 					if (x > 0.f) bits |= 1u << v;
 					act[(fg * 16 + v) * (TR + 1) + rl] = x;
@@ -955,8 +932,7 @@ DB_EXPORT void db_scanpool_fwd(const float* W, uint32_t m, uint32_t nf, const fl
 	a.relu = relu; a.ptype = ptype;
 	const unsigned fbmax = pick_fb(nf, m, 32, 120 * 1024);
 	DB_REQUIRE((size_t)m * fbmax * 32 <= 160 * 1024, "ValueError: filter length %u is too long for the fused kernel", m);
-	a.xaligned = ((uintptr_t)X & 3) == 0;
-	auto smem_of = [&](unsigned FB) { return (size_t)m * FB * 32 + (size_t)FB * (TR + 1) * 4 + 2 * (size_t)(TR + m + 16); };
+	auto smem_of = [&](unsigned FB) { return (size_t)m * FB * 32 + (size_t)FB * (TR + 1) * 4 + TR + m + 16; };
 	auto run = [&](auto kern) {
 		// Filters per CTA and regions per CTA: the pair with the least work on the busiest SM,
 		// a CTA costing its rows plus a fixed share (table build, first loads).  Small batches

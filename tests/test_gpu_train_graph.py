@@ -33,3 +33,24 @@ def test_graph_replay_equals_eager_steps(cuda, I, pool, hidden, loss):
     torch.cuda.synchronize()
     assert torch.equal(net.P, eager.P) and torch.equal(net.mP, eager.mP)
     assert np.all(np.isfinite(loss_t.cpu().numpy()))
+
+
+@pytest.mark.parametrize("strand_max", [False, True])
+def test_captured_scoring_equals_direct_scoring(cuda, strand_max):
+    """score() replayed from a CUDA graph, also after its input buffers were refilled in place."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m, n = 24, 96
+    p = synth.model_params(3, m, 5, "max")
+    net = DeepBindNet(p, 3, "max")
+    Xa, Ra = synth.uniform_batch(n, 40, m, seed=6)
+    Xb, _ = synth.uniform_batch(n, 40, m, seed=7)
+    X = torch.from_numpy(Xa).cuda(); R = torch.from_numpy(Ra.view(np.int32)).cuda()
+    graph, out = net.capture_score(X, R, strand_max)
+    graph.replay()
+    assert torch.equal(out, net.score(X, R, strand_max))
+    X.copy_(torch.from_numpy(Xb).cuda())
+    graph.replay()
+    assert torch.equal(out, net.score(X, R, strand_max))
+    assert out.shape == ((n // 2 if strand_max else n), 3)
