@@ -85,9 +85,17 @@ def cpu_run(args, nsample, steps, warmup):
         orc.score_net(params, X, R, "all", args.nmodel)
         times.append(time.perf_counter() - t)
     dt = sum(times)
+    # the same restatement on one thread, on a sixteenth of the sample
+    n1 = max(64, nsample // 16)
+    orc.set_num_threads(1)
+    t = time.perf_counter()
+    orc.score_net(params, X[:R[n1 - 1, 1] + M - 1], R[:n1], "all", args.nmodel)
+    single = n1 / (time.perf_counter() - t)
+    orc.set_num_threads(cores)
     return {"value": nsample * steps / dt, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": "%d of the workload's sequences x %d models per step, %d step(s), OpenMP over sequences"
-                      % (nsample, args.nmodel, steps)}, dt / steps
+                      % (nsample, args.nmodel, steps),
+            "single_thread": {"value": single, "unit": UNIT, "sample": "%d sequences" % n1}}, dt / steps
 
 
 def reference_arm(args):
