@@ -20,6 +20,7 @@
 // not by FP32 issue; the ALU work around it is free.  In the pool phase a thread
 // owns one (region, filter) column and walks the tile's rows in order.
 #include "db_common.cuh"
+#include <cooperative_groups.h>
 
 namespace db {
 
@@ -574,6 +575,9 @@ struct bwdmax_args {
 	const uint8_t* X; const uint32_t* R; const float* dpooled; const uint32_t* argmax; const uint16_t* actmask;
 	float* partial; float* dW; float* dbias;
 	unsigned m, nf, npos, n, nregion, FB, rper, rc;  // rper: regions per chunk; rc: regions per round
+	unsigned mode;                                   // 0: one chunk, results written directly; 1: per-chunk partials for
+	                                                 // the second stage; 2: the chunks of a filter block form a cluster
+	                                                 // and add their partials through distributed shared memory
 };
 
 __global__ void __launch_bounds__(512)
@@ -636,8 +640,38 @@ scanpool_bwd_max_kernel(const bwdmax_args a)
 			bsum = s;
 		}
 	}
+	if (a.mode == 2) {
+		namespace cg = cooperative_groups;
+		cg::cluster_group cluster = cg::this_cluster();
+		__syncthreads();                                     // the staged bases are no longer read
+		float* part = reinterpret_cast<float*>(smem);        // [(4m+1)][FB], row 4m = dbias
+		if (is_unit) {
+			#pragma unroll
+			for (int t = 0; t < 4; ++t)
+				if (j0 + t < m) {
+					#pragma unroll
+					for (int k = 0; k < 4; ++k) part[((4 * (j0 + t) + k) << logfb) + fl] = c[t][k];
+				}
+		}
+		if (is_bias) part[((4 * m) << logfb) + fl] = bsum;
+		cluster.sync();
+		// CTA `rank` finishes a slice of the block's outputs, chunks (= ranks) ascending
+		const unsigned C = cluster.num_blocks(), rank = cluster.block_rank();
+		const unsigned total = (4 * m + 1) << logfb, S = (total + C - 1) / C;
+		for (unsigned j = rank * S + threadIdx.x; j < min(total, (rank + 1) * S); j += blockDim.x) {
+			float s = 0.f;
+			for (unsigned q = 0; q < C; ++q) s += cluster.map_shared_rank(part, q)[j];
+			const unsigned row = j >> logfb, f = f0 + (j & (FB - 1));
+			if (f < a.nf) {
+				if (row < 4 * m) a.dW[(size_t)row * a.nf + f] = s;
+				else if (a.dbias) a.dbias[f] = s;
+			}
+		}
+		cluster.sync();                                      // nobody leaves while its partials are being read
+		return;
+	}
 	// one chunk: the results themselves; else partial[chunk][(4m+1)][nf], row 4m = dbias
-	const bool direct = gridDim.x == 1;
+	const bool direct = a.mode == 0;
 	float* out = direct ? a.dW : a.partial + (size_t)blockIdx.x * (4 * m + 1) * a.nf;
 	if (is_unit && f0 + fl < a.nf) {
 		#pragma unroll
@@ -993,14 +1027,24 @@ DB_EXPORT void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32
 		unsigned nchunk = std::max(1u, std::min(nregion / 8, divup(4u * (unsigned)state().sm_count, nfb)));
 		x.rper = divup(nregion, nchunk);
 		nchunk = divup(nregion, x.rper);
-		x.partial = nchunk > 1 ? (float*)scratch((size_t)nchunk * (wcount + nf) * sizeof(float)) : nullptr;
+		x.mode = nchunk == 1 ? 0u : (nchunk <= 8 ? 2u : 1u);
+		x.partial = x.mode == 1 ? (float*)scratch((size_t)nchunk * (wcount + nf) * sizeof(float)) : nullptr;
 		const unsigned mp = (m + 3u) & ~3u;
 		x.rc = std::max(1u, std::min((unsigned)RC, (unsigned)(64 * 1024 / ((size_t)x.FB * mp))));
-		const size_t smem = (size_t)x.rc * x.FB * mp;
+		const size_t smem = std::max((size_t)x.rc * x.FB * mp, (size_t)(4 * m + 1) * x.FB * sizeof(float));
 		DB_CUDA(cudaFuncSetAttribute(scanpool_bwd_max_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, (size_t)48 * 1024)));
-		scanpool_bwd_max_kernel<<<dim3(nchunk, nfb), threads, smem, state().stream>>>(x);
+		if (x.mode == 2) {
+			cudaLaunchConfig_t cfg = {};
+			cfg.gridDim = dim3(nchunk, nfb); cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smem; cfg.stream = state().stream;
+			cudaLaunchAttribute attr[1];
+			attr[0].id = cudaLaunchAttributeClusterDimension;
+			attr[0].val.clusterDim.x = nchunk; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+			cfg.attrs = attr; cfg.numAttrs = 1;
+			DB_CUDA(cudaLaunchKernelEx(&cfg, scanpool_bwd_max_kernel, x));
+		} else
+			scanpool_bwd_max_kernel<<<dim3(nchunk, nfb), threads, smem, state().stream>>>(x);
 		DB_LAUNCH_CHECK();
-		if (nchunk > 1) launch_bwd_reduce(dW, dbias, x.partial, wcount, nf, nchunk, 0);
+		if (x.mode == 1) launch_bwd_reduce(dW, dbias, x.partial, wcount, nf, nchunk, 0);
 		return;
 	}
 	bwd_args a;
