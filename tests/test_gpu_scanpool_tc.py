@@ -136,3 +136,36 @@ def test_many_sequences_many_ctas(cuda, orc):
     want, _ = orc.scanpool(p["Wscan"].astype(np.float64), p["bscan"].astype(np.float64), True, X, R, "all")
     got, _ = fused.scanpool_tc(fused.TCWeights(dev(p["Wscan"]), dev(p["bscan"]), 3), dev(X), dev(R), "all")
     assert np.max(np.abs(got.cpu().numpy() - want)) <= 1e-5 * np.abs(want).max()
+
+
+def test_full_size_genome_scan(cuda, orc):
+    """The benchmark's own size: 1,000,000 sequences x 101 nt scored by 512 models in one launch
+    (score matrix 2 GB).  The second half of the batch repeats the first, so the two halves of the
+    score matrix must agree (to the mean pooling's grouping: a sequence's rows fall differently on
+    the kernel's column pieces); sampled rows are checked against the CPU oracle; per-model column
+    sums of the two halves give a checksum over every score."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m, I, L, half = 24, 512, 101, 500000
+    p = synth.model_params(I, m, 7, "all")
+    Xh, Rh = synth.uniform_batch(half, L, m, seed=11)
+    rows = half * (L + m - 1)
+    X2 = np.concatenate([Xh[:rows], Xh[:rows], np.full(m - 1, 255, np.uint8)])
+    R2 = np.concatenate([Rh, Rh + np.uint32(rows)]).astype(np.uint32)
+    net = DeepBindNet(p, I, "all")
+    net.prepare_tc("f16x2")
+    X, R = dev(X2), dev(R2)
+    S = net.score_tc(X, R)
+    assert S.shape == (2 * half, I) and bool(torch.isfinite(S).all())
+    scale = float(S.abs().max())
+    assert float((S[:half] - S[half:]).abs().max()) <= 2e-6 * scale
+    ca, cb = S[:half].double().sum(0), S[half:].double().sum(0)
+    assert float((ca - cb).abs().max()) <= 1e-7 * float(S[:half].double().abs().sum(0).max())
+    pick = np.random.default_rng(3).choice(half, 24, replace=False)
+    Xs = np.concatenate([Xh[Rh[i, 0]:Rh[i, 1]] for i in pick] + [np.full(m - 1, 255, np.uint8)])
+    Rs = (np.arange(24, dtype=np.uint32)[:, None] * np.uint32(L + m - 1) + np.array([0, L + m - 1], np.uint32)).astype(np.uint32)
+    want = orc.score_net({k: v.astype(np.float64) for k, v in p.items()}, Xs, Rs, "all", I)
+    got = S[torch.from_numpy(pick).cuda()].cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 3e-6 * max(scale, np.abs(want).max())
+    assert np.max(np.abs(S[torch.from_numpy(pick + half).cuda()].cpu().numpy() - want)) <= 3e-6 * max(scale, np.abs(want).max())
