@@ -201,3 +201,31 @@ def test_backward_max_regions_in_any_layout(cuda, orc):
                   [1600, 1700], [1700, 1800], [1800, 1900], [200, 300], [300, 400], [400, 500], [500, 600], [600, 650],
                   [2100, 2200], [2200, 2300]], np.uint32)
     _backward_case(orc, m, nf, X, R, W, b, "max")
+
+
+def test_full_size_ragged_both_strands(cuda, orc):
+    """The ragged both-strand workload at its benchmark size (200,000 sequences of 20-200 nt with
+    5 % N, 400,000 strands, 16 x 16 filters, strand max).  Swapping the two strands of every pair
+    in the region list must not change a single score; sampled pairs are checked against the CPU
+    oracle."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m, nseq = 16, 200000
+    p = synth.model_params(1, m, 51, "max")
+    X, R = synth.ragged_batch(nseq, 20, 200, m, seed=52, n_frac=0.05, both_strands=True)
+    net = DeepBindNet(p, 1, "max")
+    tX, tR = to_dev(X, R)
+    S = net.score(tX, tR, strand_max=True)
+    assert S.shape == (nseq, 1)
+    Rs = R.reshape(nseq, 2, 2)[:, ::-1].reshape(2 * nseq, 2).copy()
+    S2 = net.score(tX, to_dev(Rs)[0], strand_max=True)
+    assert torch.equal(S, S2)
+    pick = np.random.default_rng(4).choice(nseq, 64, replace=False)
+    rows = np.stack([2 * pick, 2 * pick + 1], 1).ravel()
+    Xs = np.concatenate([X[R[i, 0]:R[i, 1]] for i in rows] + [np.full(m - 1, 255, np.uint8)])
+    ends = np.cumsum([R[i, 1] - R[i, 0] for i in rows]).astype(np.uint32)
+    Rp = np.stack([np.concatenate([[0], ends[:-1]]).astype(np.uint32), ends], 1)
+    want = orc.score_net(p, Xs, Rp, "max", 1, strand_max=True)
+    got = S[torch.from_numpy(pick).cuda()].cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 1e-6 * np.abs(want).max()
