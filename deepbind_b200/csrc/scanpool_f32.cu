@@ -19,6 +19,15 @@
 // scan is bound by the shared-memory return path (one 4-byte operand per add),
 // not by FP32 issue; the ALU work around it is free.  In the pool phase a thread
 // owns one (region, filter) column and walks the tile's rows in order.
+//
+// Backward, three kernels behind db_scanpool_bwd / api_corr1ord_bprop_W:
+//   scanpool_bwd_kernel           mean and max+mean pooling: dZ rebuilt per tile from the
+//                                 pooled deltas, argmax and activity bits, then dense one-hot
+//                                 FMAs; the next tile's inputs arrive by cp.async meanwhile
+//   scanpool_bwd_max_kernel       max pooling: only the argmax row of each (region, filter)
+//   corr1ord_bprop_W_f32_kernel   the unfused operator: dZ streamed from HBM by cp.async
+// All of them sum in a fixed order (rows, then CTAs or cluster ranks ascending): no float
+// atomics, repeated runs agree bit for bit.
 #include "db_common.cuh"
 #include <cooperative_groups.h>
 
