@@ -352,18 +352,35 @@ DB_EXPORT void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, i
 	a.pooled = pooled; a.mask = dropmask; a.Y = Y; a.W1 = W1; a.b1 = b1; a.W2 = W2; a.b2 = b2;
 	a.loss = loss; a.dpooled = dpooled; a.dW1 = dW1; a.db1 = db1; a.dW2 = dW2; a.db2 = db2;
 	a.B = B; a.I = nmodel; a.npool = npool; a.H = hidden; a.kind = loss_kind; a.pairs = strand_pairs;
-	// Few models: a cluster of CTAs per model, each with a slice of the rows.
-	const unsigned C = nmodel <= 16 ? 8u : (nmodel <= 32 ? 4u : 1u);
-	if (C > 1 && B >= 4 * C) {
-		const unsigned Bc = (divup(B, C) + 1u) & ~1u;
-		const size_t csmem = head_cluster_smem_bytes(Bc, npool, hidden);
-		DB_CUDA(cudaFuncSetAttribute(head_train_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
-		cudaLaunchConfig_t cfg = {};
-		cfg.gridDim = dim3(nmodel * C); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = csmem; cfg.stream = state().stream;
-		cudaLaunchAttribute attr[1];
+	// Few models: a cluster of CTAs per model, each with a slice of the rows.  Sixteen CTAs (a
+	// cluster size the device has to grant) when the minibatch is long enough and the device
+	// can place such a cluster; else the portable eight or four.
+	unsigned C = nmodel <= 16 ? 8u : (nmodel <= 32 ? 4u : 1u);
+	auto cluster_cfg = [&](unsigned c, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, unsigned& Bc) {
+		Bc = (divup(B, c) + 1u) & ~1u;
+		cfg = cudaLaunchConfig_t{};
+		cfg.gridDim = dim3(nmodel * c); cfg.blockDim = dim3(256);
+		cfg.dynamicSmemBytes = head_cluster_smem_bytes(Bc, npool, hidden); cfg.stream = state().stream;
 		attr[0].id = cudaLaunchAttributeClusterDimension;
-		attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+		attr[0].val.clusterDim.x = c; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
 		cfg.attrs = attr; cfg.numAttrs = 1;
+	};
+	if (C > 1 && B >= 4 * C) {
+		cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1]; unsigned Bc = 0;
+		static int wide = -1;                                 // can a cluster of 16 be placed? asked once
+		if (nmodel <= 8 && B >= 128 && wide != 0) {
+			cluster_cfg(16, cfg, attr, Bc);
+			if (wide < 0) {
+				int n = 0;
+				wide = cudaFuncSetAttribute(head_train_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+				       cudaFuncSetAttribute(head_train_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(cfg.dynamicSmemBytes, (size_t)48 * 1024)) == cudaSuccess &&
+				       cudaOccupancyMaxActiveClusters(&n, head_train_cluster_kernel, &cfg) == cudaSuccess && n >= 1;
+				(void)cudaGetLastError();
+			}
+			if (wide > 0) C = 16;
+		}
+		cluster_cfg(C, cfg, attr, Bc);
+		DB_CUDA(cudaFuncSetAttribute(head_train_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(cfg.dynamicSmemBytes, (size_t)48 * 1024)));
 		DB_CUDA(cudaLaunchKernelEx(&cfg, head_train_cluster_kernel, a, Bc));
 		DB_LAUNCH_CHECK();
 		return;
