@@ -189,7 +189,7 @@ def side_workloads(dev, with_cpu):
     in HBM, CUDA events, 3+ warm-up passes), each beside the CPU restatement timed on
     a bounded sample.  They ride along in the JSON line under `other_configs`."""
     import torch
-    from deepbind_b200 import synth
+    from deepbind_b200 import fused, synth
     from deepbind_b200.model import DeepBindNet
     from oracle import oracle as orc
     out = {}
@@ -259,14 +259,14 @@ def side_workloads(dev, with_cpu):
     del X, R
 
     def train(name, I, B, L, pool, hidden, loss, nbatch, reps, cpu_steps):
-        """Minibatch steps (forward, backward, Nesterov update) replayed from a CUDA
-        graph; every step first copies the next minibatch of the resident dataset
-        into the graph's input buffers."""
+        """Minibatch steps (fetch of the next minibatch of the resident dataset, forward,
+        backward, Nesterov update) replayed from a CUDA graph."""
         p = synth.model_params(I, M, 31, pool, hidden=hidden)
         g = synth.rng(32)
         Xh, Rh = synth.uniform_batch(B * nbatch, L, M, seed=33)
         rows = B * (L + M - 1)
-        Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(M - 1, 255, np.uint8)])
+        tail = M - 1 + (-(rows + M - 1)) % 16         # closing pad, grown so that a minibatch is whole 16-byte units
+        Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(tail, 255, np.uint8)])
                                           for i in range(nbatch)])).to(dev)
         R1 = torch.from_numpy(Rh[:B].view(np.int32)).to(dev)
         Yh = g.integers(0, 2, size=(nbatch, B, 1)).astype(np.float32) if loss == "nll" else \
@@ -279,14 +279,10 @@ def side_workloads(dev, with_cpu):
         net.set_rates(lr, 0.9)
         Xs, Ys = Xall[0].clone(), Yall[0].clone()
         Ms = Mall[0].clone() if Mall is not None else None
-        graph, _ = net.capture_train_step(Xs, R1, Ys, Ms)
-        state = {"i": 0}
+        feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)] + ([(Mall, Ms)] if Ms is not None else []))
+        graph, _ = net.capture_train_step(Xs, R1, Ys, Ms, feed=feed)
 
         def step():
-            i = state["i"] = (state["i"] + 1) % nbatch
-            Xs.copy_(Xall[i]); Ys.copy_(Yall[i])
-            if Ms is not None:
-                Ms.copy_(Mall[i])
             graph.replay()
         for _ in range(5):
             step()
@@ -320,7 +316,7 @@ def calibration_sharded(dev, rank, world):
     Time = CUDA events on every rank, maximum over ranks."""
     import torch
     import torch.distributed as dist
-    from deepbind_b200 import shard, synth
+    from deepbind_b200 import fused, shard, synth
     from deepbind_b200.model import DeepBindNet
     NMODEL, B, Lc, nbatch, reps = 90, 64, 40, 64, 100
     ids = shard.shard_models(NMODEL, rank, world)
@@ -329,7 +325,8 @@ def calibration_sharded(dev, rank, world):
     p = synth.model_params(I, M, 31 + rank, "max")
     Xh, Rh = synth.uniform_batch(B * nbatch, Lc, M, seed=33)
     rows = B * (Lc + M - 1)
-    Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(M - 1, 255, np.uint8)])
+    tail = M - 1 + (-(rows + M - 1)) % 16             # closing pad, grown so that a minibatch is whole 16-byte units
+    Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(tail, 255, np.uint8)])
                                       for i in range(nbatch)])).to(dev)
     R1 = torch.from_numpy(Rh[:B].view(np.int32)).to(dev)
     Yall = torch.from_numpy(np.tile(g.standard_normal((nbatch, B, 1)).astype(np.float32), (1, 1, I))).to(dev)
@@ -337,16 +334,15 @@ def calibration_sharded(dev, rank, world):
     net = DeepBindNet(p, I, "max", loss="mse")
     net.set_rates(lr_all[ids], 0.9)
     Xs, Ys = Xall[0].clone(), Yall[0].clone()
-    graph, loss = net.capture_train_step(Xs, R1, Ys, None)
+    feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)])
+    graph, loss = net.capture_train_step(Xs, R1, Ys, None, feed=feed)
     nmax = (NMODEL + world - 1) // world
     mine = torch.zeros(nmax, dtype=torch.float32, device=dev)
     everyone = torch.empty(world * nmax, dtype=torch.float32, device=dev)
 
     def run(n):
-        for s in range(n):
-            i = s % nbatch
-            Xs.copy_(Xall[i]); Ys.copy_(Yall[i])
-            graph.replay()
+        for _ in range(n):
+            graph.replay()                            # fetch of the next minibatch + training step
         mine[:I] = loss.view(-1)[:I]
         dist.all_gather_into_tensor(everyone, mine)
     run(5)

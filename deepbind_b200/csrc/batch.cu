@@ -133,3 +133,71 @@ DB_EXPORT void db_build_batch(const uint8_t* text, const uint32_t* offsets, uint
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }
+
+// ----------------------------------------------------------- minibatch fetch
+// The training loop of the reference uploads every minibatch from the host
+// (deepity/data.py, kangaroo/data.py:274-354).  With the dataset resident in HBM as
+// `nbatch` equally sized minibatches, one launch copies minibatch order[step % nbatch]
+// of up to three arrays (sequences, targets, dropout masks) into the buffers a
+// captured training step reads, and advances the step counter on the device -- so a
+// CUDA graph can replay "fetch, step" with no host work between steps.
+// state[0] = step counter, state[1] = arrivals of the current launch.  Every CTA reads
+// the counter before it arrives; the last one to arrive advances it: no CTA waits.
+struct fetch_args {
+	const uint8_t* src[3]; uint8_t* dst[3]; size_t bytes[3];
+	uint32_t* state; const uint32_t* order; uint32_t nbatch;
+};
+
+__global__ void __launch_bounds__(256) minibatch_fetch_kernel(const fetch_args a)
+{
+	__shared__ unsigned s_batch;
+	if (threadIdx.x == 0) {
+		const unsigned step = *reinterpret_cast<volatile uint32_t*>(a.state) % a.nbatch;
+		s_batch = a.order ? a.order[step] : step;
+	}
+	__syncthreads();
+	const unsigned b = s_batch;
+	const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+	#pragma unroll
+	for (int k = 0; k < 3; ++k) {
+		const size_t n = a.bytes[k];
+		if (!n) continue;
+		const uint8_t* s = a.src[k] + (size_t)b * n;
+		uint8_t* d = a.dst[k];
+		if ((((uintptr_t)s | (uintptr_t)d | n) & 15) == 0) {
+			for (size_t i = tid; i < n / 16; i += nth) reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(s)[i];
+		} else {
+			for (size_t i = tid; i < n; i += nth) d[i] = s[i];
+		}
+	}
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		__threadfence();
+		if (atomicAdd(a.state + 1, 1u) == gridDim.x - 1) {       // last CTA of this launch
+			a.state[1] = 0;
+			a.state[0] = a.state[0] + 1;
+			__threadfence();
+		}
+	}
+}
+
+DB_EXPORT void db_minibatch_fetch(uint32_t* counters, const uint32_t* order, uint32_t nbatch,
+                                  const void* src0, void* dst0, size_t bytes0,
+                                  const void* src1, void* dst1, size_t bytes1,
+                                  const void* src2, void* dst2, size_t bytes2)
+{
+	DB_API_TRY
+	DB_REQUIRE(counters && nbatch, "ValueError: db_minibatch_fetch needs its two counters and at least one minibatch");
+	fetch_args a;
+	a.src[0] = (const uint8_t*)src0; a.dst[0] = (uint8_t*)dst0; a.bytes[0] = src0 && dst0 ? bytes0 : 0;
+	a.src[1] = (const uint8_t*)src1; a.dst[1] = (uint8_t*)dst1; a.bytes[1] = src1 && dst1 ? bytes1 : 0;
+	a.src[2] = (const uint8_t*)src2; a.dst[2] = (uint8_t*)dst2; a.bytes[2] = src2 && dst2 ? bytes2 : 0;
+	a.state = counters; a.order = order; a.nbatch = nbatch;
+	const size_t most = std::max(a.bytes[0], std::max(a.bytes[1], a.bytes[2]));
+	// eight bytes a thread: an array whose minibatches are not multiples of 16 bytes is copied
+	// byte by byte, and those loads should all be in flight at once
+	const unsigned ncta = (unsigned)std::min<size_t>(std::max<size_t>(1, divup(most, (size_t)(256 * 8))), 2u * (unsigned)state().sm_count);
+	minibatch_fetch_kernel<<<ncta, 256, 0, state().stream>>>(a);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}

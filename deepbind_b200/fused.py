@@ -135,6 +135,37 @@ def build_windows(seqs, windowsize, stride, padding, reverse_complement=False, d
     return X, R, woff_h
 
 
+class MinibatchFeed(object):
+    """Device-resident dataset cut into ``nbatch`` equal minibatches, fetched by one
+    launch per step (db_minibatch_fetch): ``pairs`` is a list of up to three
+    (dataset tensor [nbatch, ...], step buffer [...]) pairs -- sequences, targets,
+    dropout masks.  ``fetch()`` copies the next minibatch into the step buffers and
+    advances the device-side step counter; captured into a CUDA graph in front of a
+    training step, the whole loop replays without host work.  ``order`` (optional int32
+    device tensor [nbatch]) gives the minibatch visited at each step of an epoch."""
+
+    def __init__(self, pairs, order=None):
+        assert 1 <= len(pairs) <= 3
+        self.pairs = [(a.contiguous(), b) for a, b in pairs]
+        self.nbatch = int(self.pairs[0][0].shape[0])
+        for a, b in self.pairs:
+            assert a.shape[0] == self.nbatch and a[0].numel() * a.element_size() == b.numel() * b.element_size()
+            assert b.is_contiguous()
+        self.order = order
+        self.counters = torch.zeros(2, dtype=torch.int32, device=self.pairs[0][0].device)
+
+    def fetch(self):
+        bind_stream()
+        args = []
+        for k in range(3):
+            if k < len(self.pairs):
+                a, b = self.pairs[k]
+                args += [_ptr(a), _ptr(b), b.numel() * b.element_size()]
+            else:
+                args += [None, None, 0]
+        _dll().db_minibatch_fetch(_ptr(self.counters), _ptr(self.order) if self.order is not None else None, self.nbatch, *args)
+
+
 TC_PRECISION = {"bf16": 1, "bf16x2": 2, "bf16x3": 3, "f16x2": 4, "f16": 5}
 TC_PIECES = {1: 1, 2: 2, 3: 3, 4: 2, 5: 1}     # 16-bit operand pieces per weight = tensor-core passes
 

@@ -303,7 +303,7 @@ class DeepBindNet(object):
         cur.synchronize()
         return out_host
 
-    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3):
+    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3, feed=None):
         """Captures one Nesterov step on the static buffers X, R, Y, dropmask into a
         CUDA graph and returns (graph, loss): refill the buffers in place (same
         shapes) and call ``graph.replay()`` for every further step.  A minibatch
@@ -311,17 +311,28 @@ class DeepBindNet(object):
         per-launch host cost that otherwise dominates (the reference pays it on
         every step, 40-60 ctypes calls each).  The warm-up steps run first on a
         side stream so that the library's scratch buffer has its final size: no
-        allocation may happen while a stream is being captured."""
+        allocation may happen while a stream is being captured.  With ``feed`` (a
+        fused.MinibatchFeed whose step buffers are X, Y, dropmask) the graph first
+        fetches the next minibatch of the device-resident dataset, so replaying it
+        walks the dataset with no host work between steps; the feed's step counter is
+        back at zero when this returns."""
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
         with torch.cuda.stream(side):
             for _ in range(warmup):
+                if feed is not None:
+                    feed.fetch()
                 self.train_step(X, R, Y, dropmask)
         cur.wait_stream(side)
         torch.cuda.synchronize()
+        if feed is not None:
+            feed.counters.zero_()
+            torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
+            if feed is not None:
+                feed.fetch()
             loss = self.train_step(X, R, Y, dropmask)
         return graph, loss
 

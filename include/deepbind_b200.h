@@ -143,6 +143,19 @@ void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, con
  * `decay` is the per-model decay spread over the flat parameter vector, zero on biases. */
 void db_l1_decay(float* dP, const float* P, const float* decay, size_t n);
 
+/* Minibatch fetch on the device (the reference uploads every minibatch from the host:
+ * deepity/data.py, kangaroo/data.py:274-354).  The dataset lies in HBM as `nbatch`
+ * equally sized minibatches per array; one launch copies minibatch
+ * order[counters[0] % nbatch] (or counters[0] % nbatch itself when order is NULL) of up
+ * to three arrays (src_k + index * bytes_k -> dst_k; NULL pointers or 0 bytes skip an
+ * array) and then advances counters[0].  counters is a device array of two uint32, both
+ * zero before the first call.  Captured into a CUDA graph in front of a training step
+ * it lets the graph be replayed with no host work between steps. */
+void db_minibatch_fetch(uint32_t* counters, const uint32_t* order, uint32_t nbatch,
+                        const void* src0, void* dst0, size_t bytes0,
+                        const void* src1, void* dst1, size_t bytes1,
+                        const void* src2, void* dst2, size_t bytes2);
+
 /* Measurement aid, no counterpart in the reference: launches a register-only chain of
  * FP32 adds on every lane (2048 threads per SM, 128 * iters adds per thread) on the
  * library's stream and returns the number of adds launched (0 on error).  Timed with

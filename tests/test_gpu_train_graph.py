@@ -54,3 +54,61 @@ def test_captured_scoring_equals_direct_scoring(cuda, strand_max):
     graph.replay()
     assert torch.equal(out, net.score(X, R, strand_max))
     assert out.shape == ((n // 2 if strand_max else n), 3)
+
+
+def test_minibatch_feed_walks_the_dataset(cuda):
+    """db_minibatch_fetch: minibatch order[step % nbatch] of three arrays per launch, the step
+    counter kept on the device; odd sizes take the byte path."""
+    import torch
+    from deepbind_b200 import fused
+    g = torch.Generator(device="cuda").manual_seed(1)
+    nbatch = 5
+    A = torch.randint(0, 255, (nbatch, 1003), dtype=torch.uint8, device="cuda", generator=g)
+    B = torch.randn((nbatch, 64, 3), device="cuda", generator=g)
+    C = torch.rand((nbatch, 64, 32), device="cuda", generator=g) >= 0.5
+    a, b, c = torch.empty_like(A[0]), torch.empty_like(B[0]), torch.empty_like(C[0])
+    feed = fused.MinibatchFeed([(A, a), (B, b), (C, c)])
+    for step in range(12):
+        feed.fetch()
+        i = step % nbatch
+        assert torch.equal(a, A[i]) and torch.equal(b, B[i]) and torch.equal(c, C[i])
+    assert feed.counters.tolist() == [12, 0]
+    order = torch.tensor([3, 0, 4, 1, 2], dtype=torch.int32, device="cuda")
+    feed = fused.MinibatchFeed([(B, b)], order=order)
+    for step in range(7):
+        feed.fetch()
+        assert torch.equal(b, B[int(order[step % nbatch])])
+    big = torch.randn((3, 1 << 20), device="cuda", generator=g)        # several CTAs per launch
+    dst = torch.empty_like(big[0])
+    feed = fused.MinibatchFeed([(big, dst)])
+    for step in range(4):
+        feed.fetch()
+        assert torch.equal(dst, big[step % 3])
+
+
+def test_graph_with_feed_equals_eager_steps_over_the_dataset(cuda):
+    """fetch + step replayed from one graph = eager steps on the same minibatches in order."""
+    import torch
+    from deepbind_b200 import fused, synth
+    from deepbind_b200.model import DeepBindNet
+    m, B, I, nbatch = 24, 32, 4, 3
+    p = synth.model_params(I, m, 3, "max")
+    Xh, Rh = synth.uniform_batch(B * nbatch, 40, m, seed=1)
+    rows = B * (40 + m - 1)
+    Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(m - 1, 255, np.uint8)])
+                                      for i in range(nbatch)])).cuda()
+    R = torch.from_numpy(Rh[:B].view(np.int32)).cuda()
+    Yall = torch.from_numpy(synth.rng(2).standard_normal((nbatch, B, I)).astype(np.float32)).cuda()
+    eager = DeepBindNet(p, I, "max", loss="mse"); eager.set_rates(0.02, 0.9)
+    for s in range(7):
+        eager.train_step(Xall[s % nbatch], R, Yall[s % nbatch])
+    net = DeepBindNet(p, I, "max", loss="mse"); net.set_rates(0.02, 0.9)
+    P0, m0 = net.P.clone(), net.mP.clone()
+    Xs, Ys = Xall[0].clone(), Yall[0].clone()
+    feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)])
+    graph, _ = net.capture_train_step(Xs, R, Ys, feed=feed)
+    net.P.copy_(P0); net.mP.copy_(m0)
+    for _ in range(7):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(net.P, eager.P) and torch.equal(net.mP, eager.mP)
