@@ -92,25 +92,29 @@ class Trainer(object):
         checkpoints = {int(max_steps * float(k) / spec.checkpoints) for k in range(1, int(spec.checkpoints) + 1)}
         same = all(b[0].numel() == batches[0][0].numel() and b[1].shape == batches[0][1].shape for b in batches)
         graphs = {}
-        static = None
+        static = feed = None
         if use_graph and same and uniform_draws is None:
             X0, R0, Y0 = batches[0]
             static = (X0.clone(), R0.clone(), Y0.clone(), self._mask(R0.shape[0], None))
+            # the captured step fetches minibatch (step % nb) of the stacked dataset by itself
+            feed = fused.MinibatchFeed([(torch.stack([b[0] for b in batches]), static[0]),
+                                        (torch.stack([b[1] for b in batches]), static[1]),
+                                        (torch.stack([b[2] for b in batches]), static[2])])
         loss = None
         for step in range(max_steps):
             X, R, Yb = batches[step % nb]
             net.decay_on = step >= spec.weight_decay_start
             if static is not None:
                 sX, sR, sY, sM = static
-                sX.copy_(X); sY.copy_(Yb)
                 if sM is not None:
                     sM.copy_(self._mask(R.shape[0], None))
                 key = bool(net.decay_on)
                 if key not in graphs:
                     # the capture's warm-up steps are real steps: put the state back afterwards
                     P0, mP0 = net.P.clone(), net.mP.clone()
-                    graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3)
+                    graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3, feed=feed)
                     net.P.copy_(P0); net.mP.copy_(mP0)
+                    feed.counters[0] = step
                 graphs[key][0].replay()
                 loss = graphs[key][1]
             else:
