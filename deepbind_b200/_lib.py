@@ -99,6 +99,7 @@ _PROTOTYPES = {
     "db_loss": (None, [c_int, P, P, P, P, c_uint32, c_uint32, P, P]),
     "db_l1_decay": (None, [P, P, P, c_size_t]),
     "db_fadd_probe": (c_uint64, [P, c_uint32]),
+    "db_dropout_mask": (None, [P, c_uint32, c_uint32, P, c_uint32, c_int, P]),
     "db_minibatch_fetch": (None, [P, P, c_uint32, P, P, c_size_t, P, P, c_size_t, P, P, c_size_t]),
     "db_head_max_batch": (c_uint32, [c_uint32, c_uint32]),
     "db_head_train": (None, [c_uint32, c_uint32, c_uint32, c_int, c_int, c_uint32, P, P, P, P, P, P, P, P, P, P, P, P, P]),

@@ -333,6 +333,54 @@ DB_EXPORT void api_calc_zmask(const smat* Z, smat* M)
 	DB_API_CATCH
 }
 
+// Keep-mask of one training step drawn on the device, for steps replayed from a CUDA
+// graph: the draw index is a counter in device memory (counters[0]; counters[1] counts
+// the CTAs of the running launch), read by every CTA before it arrives and advanced by
+// the last one, so every replay draws a fresh mask with no host work.  Same Bernoulli
+// rule as dropout_fp_tr_kernel (dropout.cu:41-62): keep where u >= rate[model]; with
+// matchrows the two strands of a pair share their mask row.
+__global__ void __launch_bounds__(256)
+dropout_mask_kernel(uint8_t* M, size_t nrow, size_t ncol, const float* rate, unsigned k, int matchrows,
+                    uint64_t seed, uint32_t* counters)
+{
+	__shared__ unsigned s_step;
+	if (threadIdx.x == 0) s_step = *reinterpret_cast<volatile uint32_t*>(counters);
+	__syncthreads();
+	const uint64_t call = ((uint64_t)1 << 40) + s_step;          // apart from the host-counted draws of api_dropout_fp_tr
+	if (matchrows) {
+		GRID_STRIDE(i, nrow * ncol / 2) {
+			const size_t row = (i / ncol) * 2, col = i % ncol;
+			const bool mask = uniform_01(seed, call, i) >= rate[col / k];
+			M[row * ncol + col] = mask; M[(row + 1) * ncol + col] = mask;
+		}
+	} else {
+		GRID_STRIDE(i, nrow * ncol) M[i] = uniform_01(seed, call, i) >= rate[(i % ncol) / k];
+	}
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		__threadfence();
+		if (atomicAdd(counters + 1, 1u) == gridDim.x - 1) {
+			counters[1] = 0;
+			counters[0] = counters[0] + 1;
+			__threadfence();
+		}
+	}
+}
+
+DB_EXPORT void db_dropout_mask(uint8_t* M, uint32_t nrow, uint32_t ncol, const float* rate, uint32_t nmodel,
+                               int matchrows, uint32_t* counters)
+{
+	DB_API_TRY
+	DB_REQUIRE(M && rate && counters, "ValueError: db_dropout_mask got a NULL pointer");
+	DB_REQUIRE(nmodel > 0 && ncol % nmodel == 0, "ValueError: the mask's %u columns do not divide among %u models", ncol, nmodel);
+	DB_REQUIRE(!matchrows || nrow % 2 == 0, "ValueError: matched rows need an even number of rows (got %u)", nrow);
+	if (!nrow || !ncol) return;
+	const size_t n = (size_t)nrow * ncol / (matchrows ? 2 : 1);
+	dropout_mask_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(M, nrow, ncol, rate, ncol / nmodel, matchrows, state().seed, counters);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
 static void dropout_fp_tr(const smat* X, const smat* rate, const smat* U, smat* Z, smat* M, int matchrows)
 {
 	require_float(X, "X"); require_float(rate, "rate"); require_float(Z, "Z"); require_dtype(M, DB_B8, "M", "b8");

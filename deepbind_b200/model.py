@@ -303,7 +303,7 @@ class DeepBindNet(object):
         cur.synchronize()
         return out_host
 
-    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3, feed=None):
+    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3, feed=None, prologue=None):
         """Captures one Nesterov step on the static buffers X, R, Y, dropmask into a
         CUDA graph and returns (graph, loss): refill the buffers in place (same
         shapes) and call ``graph.replay()`` for every further step.  A minibatch
@@ -315,7 +315,9 @@ class DeepBindNet(object):
         fused.MinibatchFeed whose step buffers are X, Y, dropmask) the graph first
         fetches the next minibatch of the device-resident dataset, so replaying it
         walks the dataset with no host work between steps; the feed's step counter is
-        back at zero when this returns."""
+        back at zero when this returns.  ``prologue`` (a callable launching further
+        kernels, e.g. the draw of the step's dropout mask into ``dropmask``) runs inside
+        the graph between the fetch and the step."""
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
@@ -323,6 +325,8 @@ class DeepBindNet(object):
             for _ in range(warmup):
                 if feed is not None:
                     feed.fetch()
+                if prologue is not None:
+                    prologue()
                 self.train_step(X, R, Y, dropmask)
         cur.wait_stream(side)
         torch.cuda.synchronize()
@@ -333,6 +337,8 @@ class DeepBindNet(object):
         with torch.cuda.graph(graph):
             if feed is not None:
                 feed.fetch()
+            if prologue is not None:
+                prologue()
             loss = self.train_step(X, R, Y, dropmask)
         return graph, loss
 

@@ -100,19 +100,28 @@ class Trainer(object):
             feed = fused.MinibatchFeed([(torch.stack([b[0] for b in batches]), static[0]),
                                         (torch.stack([b[1] for b in batches]), static[1]),
                                         (torch.stack([b[2] for b in batches]), static[2])])
+            if static[3] is not None:
+                # the step's dropout mask is drawn by a kernel of the graph (draw counter on the device)
+                rate_dev = torch.from_numpy(np.ascontiguousarray(net.dropout_rate, np.float32)).to(net.dev)
+                mask_counters = torch.zeros(2, dtype=torch.int32, device=net.dev)
+                sM0 = static[3]
+
+                def draw_mask():
+                    sm.bind_stream()
+                    _lib.load().db_dropout_mask(sM0.data_ptr(), sM0.shape[0], sM0.shape[1], rate_dev.data_ptr(), net.I,
+                                                int(self.reverse_complement), mask_counters.data_ptr())
         loss = None
         for step in range(max_steps):
             X, R, Yb = batches[step % nb]
             net.decay_on = step >= spec.weight_decay_start
             if static is not None:
                 sX, sR, sY, sM = static
-                if sM is not None:
-                    sM.copy_(self._mask(R.shape[0], None))
                 key = bool(net.decay_on)
                 if key not in graphs:
                     # the capture's warm-up steps are real steps: put the state back afterwards
                     P0, mP0 = net.P.clone(), net.mP.clone()
-                    graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3, feed=feed)
+                    graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3, feed=feed,
+                                                         prologue=draw_mask if sM is not None else None)
                     net.P.copy_(P0); net.mP.copy_(mP0)
                     feed.counters[0] = step
                 graphs[key][0].replay()

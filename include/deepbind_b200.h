@@ -143,6 +143,14 @@ void db_loss(int kind, const float* Z, const float* Y, const uint8_t* Ymask, con
  * `decay` is the per-model decay spread over the flat parameter vector, zero on biases. */
 void db_l1_decay(float* dP, const float* P, const float* decay, size_t n);
 
+/* Dropout keep-mask of one training step drawn on the device (dropout.cu:41-62: keep where
+ * u >= rate[model]; matchrows: the two strands of a row pair share a mask row), for steps
+ * replayed from a CUDA graph: the draw index is counters[0] (device uint32[2], zero before
+ * the first call), advanced by the launch itself, so every replay draws a fresh mask.
+ * M bool [nrow, ncol], ncol = features per model * nmodel; rate f32 [nmodel]. */
+void db_dropout_mask(uint8_t* M, uint32_t nrow, uint32_t ncol, const float* rate, uint32_t nmodel,
+                     int matchrows, uint32_t* counters);
+
 /* Minibatch fetch on the device (the reference uploads every minibatch from the host:
  * deepity/data.py, kangaroo/data.py:274-354).  The dataset lies in HBM as `nbatch`
  * equally sized minibatches per array; one launch copies minibatch

@@ -112,3 +112,46 @@ def test_graph_with_feed_equals_eager_steps_over_the_dataset(cuda):
         graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(net.P, eager.P) and torch.equal(net.mP, eager.mP)
+
+
+@pytest.mark.parametrize("matchrows", [0, 1])
+def test_device_drawn_dropout_masks(cuda, matchrows):
+    """db_dropout_mask: keep-rate 1 - rate[model] per model block, a fresh draw on every launch (also
+    when the launch is replayed from a CUDA graph), strand pairs sharing their row when asked."""
+    import torch
+    from deepbind_b200 import _lib
+    from deepbind_b200.smat import bind_stream
+    dll = _lib.load()
+    nrow, k, I = 512, 32, 3
+    rate = torch.tensor([0.5, 0.2, 0.0], dtype=torch.float32, device="cuda")
+    M = torch.zeros((nrow, k * I), dtype=torch.bool, device="cuda")
+    counters = torch.zeros(2, dtype=torch.int32, device="cuda")
+
+    def draw():
+        bind_stream()
+        dll.db_dropout_mask(M.data_ptr(), nrow, k * I, rate.data_ptr(), I, matchrows, counters.data_ptr())
+    draw()
+    first = M.clone()
+    keep = first.float().view(nrow, I, k).mean(dim=(0, 2)).cpu().numpy()
+    assert abs(keep[0] - 0.5) < 0.03 and abs(keep[1] - 0.8) < 0.03 and keep[2] == 1.0
+    if matchrows:
+        assert torch.equal(first[0::2], first[1::2])
+    else:
+        assert not torch.equal(first[0::2], first[1::2])
+    draw()
+    assert not torch.equal(M, first) and counters.tolist() == [2, 0]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        draw()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        draw()
+    seen = []
+    for _ in range(3):
+        g.replay(); torch.cuda.synchronize()
+        seen.append(M.clone())
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])
+    assert counters.tolist() == [6, 0]
