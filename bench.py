@@ -284,7 +284,7 @@ def side_workloads(dev, with_cpu):
 
         def step():
             graph.replay()
-        for _ in range(5):
+        for _ in range(200):                          # replays are tens of microseconds: warm up past the clock ramp
             step()
         ms = _events_ms(step, reps)
         cpu = None
@@ -302,9 +302,9 @@ def side_workloads(dev, with_cpu):
                      **rates(B * (L + M - 1), NMOTIF * I, M, ms, passes=3)}
 
     # config 2: ChIP-seq-style training, one model, minibatch 128, allpool -> 32 hidden (dropout 0.5) -> sigmoid
-    train("chip_train", 1, 128, 101, "all", 32, "nll", 64, 200, 5)
+    train("chip_train", 1, 128, 101, "all", 32, "nll", 64, 2000, 5)
     # config 3: calibration sweep, 90 independent models trained at once on 40-nt probes, minibatch 64
-    train("calibration", 90, 64, 40, "max", 0, "mse", 64, 100, 1)
+    train("calibration", 90, 64, 40, "max", 0, "mse", 64, 1000, 1)
     return out
 
 
@@ -318,7 +318,7 @@ def calibration_sharded(dev, rank, world):
     import torch.distributed as dist
     from deepbind_b200 import fused, shard, synth
     from deepbind_b200.model import DeepBindNet
-    NMODEL, B, Lc, nbatch, reps = 90, 64, 40, 64, 100
+    NMODEL, B, Lc, nbatch, reps = 90, 64, 40, 64, 1000
     ids = shard.shard_models(NMODEL, rank, world)
     I = len(ids)
     g = synth.rng(32)
@@ -345,7 +345,7 @@ def calibration_sharded(dev, rank, world):
             graph.replay()                            # fetch of the next minibatch + training step
         mine[:I] = loss.view(-1)[:I]
         dist.all_gather_into_tensor(everyone, mine)
-    run(5)
+    run(200)
     dist.barrier(); torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(); run(reps); e1.record()
