@@ -90,16 +90,20 @@ class Trainer(object):
         nb = len(batches)
         max_steps = int(min(spec.max_steps, spec.max_epochs * nb))
         checkpoints = {int(max_steps * float(k) / spec.checkpoints) for k in range(1, int(spec.checkpoints) + 1)}
-        same = all(b[0].numel() == batches[0][0].numel() and b[1].shape == batches[0][1].shape for b in batches)
+        # Minibatches shaped like the first one (all of them, or all but a shorter last one) run
+        # as a captured step; a last minibatch of another shape runs call by call.
+        nfull = 0
+        while nfull < nb and batches[nfull][0].numel() == batches[0][0].numel() and batches[nfull][1].shape == batches[0][1].shape:
+            nfull += 1
         graphs = {}
         static = feed = None
-        if use_graph and same and uniform_draws is None:
+        if use_graph and nfull >= max(1, nb - 1) and uniform_draws is None:
             X0, R0, Y0 = batches[0]
             static = (X0.clone(), R0.clone(), Y0.clone(), self._mask(R0.shape[0], None))
-            # the captured step fetches minibatch (step % nb) of the stacked dataset by itself
-            feed = fused.MinibatchFeed([(torch.stack([b[0] for b in batches]), static[0]),
-                                        (torch.stack([b[1] for b in batches]), static[1]),
-                                        (torch.stack([b[2] for b in batches]), static[2])])
+            # the captured step fetches the next of the stacked full minibatches by itself
+            feed = fused.MinibatchFeed([(torch.stack([b[0] for b in batches[:nfull]]), static[0]),
+                                        (torch.stack([b[1] for b in batches[:nfull]]), static[1]),
+                                        (torch.stack([b[2] for b in batches[:nfull]]), static[2])])
             if static[3] is not None:
                 # the step's dropout mask is drawn by a kernel of the graph (draw counter on the device)
                 rate_dev = torch.from_numpy(np.ascontiguousarray(net.dropout_rate, np.float32)).to(net.dev)
@@ -114,7 +118,7 @@ class Trainer(object):
         for step in range(max_steps):
             X, R, Yb = batches[step % nb]
             net.decay_on = step >= spec.weight_decay_start
-            if static is not None:
+            if static is not None and step % nb < nfull:
                 sX, sR, sY, sM = static
                 key = bool(net.decay_on)
                 if key not in graphs:
@@ -123,7 +127,7 @@ class Trainer(object):
                     graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3, feed=feed,
                                                          prologue=draw_mask if sM is not None else None)
                     net.P.copy_(P0); net.mP.copy_(mP0)
-                    feed.counters[0] = step
+                    feed.counters[0] = (step // nb) * nfull + min(step % nb, nfull)     # captured steps run so far
                 graphs[key][0].replay()
                 loss = graphs[key][1]
             else:

@@ -80,11 +80,13 @@ def test_training_run_matches_the_oracle(cuda, orc, text, I, classify, L, rc):
     assert [s for s, _ in tr.history] == [5, 10] and all(h.shape == (I,) for _, h in tr.history)
 
 
-def test_graph_replay_equals_eager_steps(cuda):
+@pytest.mark.parametrize("nseq", [128, 148])
+def test_graph_replay_equals_eager_steps(cuda, nseq):
+    """148 sequences: the fifth minibatch is short and runs call by call between the captured steps."""
     from deepbind_b200 import cfg
     from deepbind_b200.trainer import Trainer
     rng = np.random.default_rng(8)
-    seqs, Y = make_data(rng, 128, 40, False)
+    seqs, Y = make_data(rng, nseq, 40, False)
     spec = cfg.sgd(rate=0.02, momentum=0.9, batchsize=32, max_epochs=100, max_steps=12, checkpoints=1, weight_decay_start=5)
     out = []
     for use_graph in (False, True):
