@@ -145,6 +145,50 @@ class DeepBindNet(object):
             out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
         return out
 
+    def input_gradients(self, X, R, strand_max=False):
+        """Gradient maps of kangaroo.predict (code/libs/kangaroo/kangaroo/predict.py:168-265,
+        deepity/node.py:317-338): the output Z (after the logistic for an nll model) is fed
+        back as dZ = Z - 0 with no minibatch mean, through the dense layers in test mode,
+        pooling, rectifier and scan, down to dX [npos, 4].  With strand_max only the
+        stronger row of each forward / reverse-complement pair feeds back.  Runs the
+        drop-in operators one by one (the activation [npos, nf] is materialised), as the
+        reference does.  Returns (Z [nrow, I], dX)."""
+        from . import kangaroo_smat as ks
+        bind_stream()
+        dll = _lib.load()
+        I = self.I
+        W, b = self.view("Wscan").contiguous(), self.view("bscan").view(-1)
+        sX, sR = sarray(X.view(-1, 1), np.uint8), sarray(R.view(torch.int32), np.uint32)
+        act = torch.zeros((X.numel(), self.nf), dtype=torch.float32, device=self.dev)
+        ks.corr1ord(_as_f32(W), sX, _as_f32(act), 4)
+        dll.db_bias_add(act.data_ptr(), act.data_ptr(), b.data_ptr(), act.shape[0], act.shape[1])
+        dll.db_relu(act.data_ptr(), act.data_ptr(), act.numel())
+        pooled, amax = ks.poolrgn(_as_f32(act), sR, self.pool, want_argmax=self.pool in ("max", "all"))
+        out, h1, a1 = self._head(self._test_dropout(pooled.tensor))
+        Z = out.clone()
+        if self.loss == "nll":
+            dll.db_logistic(Z.data_ptr(), out.data_ptr(), out.numel())
+        dZ = Z.clone()
+        if strand_max:
+            z = Z.view(-1, 2, I)
+            fwd = z[:, 0] >= z[:, 1]
+            dZ = torch.where(torch.stack([fwd, ~fwd], 1).reshape(-1, I), dZ, torch.zeros_like(dZ))
+        if self.hidden:
+            da1 = dsm.blockwise_dot_nt(_as_f32(dZ.contiguous()), _as_f32(self.view("W2")), I).tensor
+            dh = torch.empty_like(da1)
+            dll.db_relu_bprop(dh.data_ptr(), da1.data_ptr(), a1.data_ptr(), dh.numel())
+        else:
+            dh = dZ.contiguous()
+        dpd = dsm.blockwise_dot_nt(_as_f32(dh), _as_f32(self.view("W1")), I)
+        if self.dropout_rate is not None:
+            dpd = dsm.dropout_bp_te(dpd, sm_asarray(self.dropout_rate))
+        dact = torch.zeros_like(act)
+        ks.poolrgn_bprop(_as_f32(dact), sR, dpd, amax, self.pool)
+        dll.db_relu_bprop(dact.data_ptr(), dact.data_ptr(), act.data_ptr(), dact.numel())
+        dX = torch.zeros((X.numel(), 4), dtype=torch.float32, device=self.dev)
+        ks.corr1ord_bprop_X(_as_f32(dX), _as_f32(W), _as_f32(dact), 4)
+        return Z, dX
+
     # --------------------------------------------------------------- backward
     def grads(self, X, R, Y, dropmask=None):
         """Fills dP with the gradient of the mean loss at P; returns loss [I].

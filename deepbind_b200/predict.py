@@ -63,3 +63,39 @@ def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps
     if want_pmaps:
         out["pmaps"] = pmaps
     return out
+
+
+def gradient_maps(net, seqs, reverse_complement=False, batchsize=2048):
+    """Gradient maps of direct-mode scoring (predict.py:198-265): for every sequence the
+    [len, 4] gradient of the fed-back output with respect to the four channels of each
+    position (``DeepBindNet.input_gradients``), batch by batch of ``batchsize`` sequences
+    as the reference evaluates them.  With ``reverse_complement`` the map of the stronger
+    strand is kept (the forward one on ties), in that strand's own coordinates.
+
+    Returns (Z [nseq, I] CUDA tensor, maps: list of numpy [len_b, 4], strands: numpy int8
+    [nseq], 0 = forward, 1 = reverse complement).  Several models: the fed-back gradients
+    of all models add up in dX, as they do in the reference's shared input plug."""
+    seqs = list(seqs)
+    pad = net.m - 1
+    rc = bool(reverse_complement)
+    Zs, maps, strands = [], [], []
+    for lo in range(0, len(seqs), batchsize):
+        chunk = seqs[lo:lo + batchsize]
+        X, R = fused.build_batch(chunk, pad, rc, device=net.dev)
+        Z, dX = net.input_gradients(X, R, strand_max=rc)
+        Rh = R.cpu().numpy().view(np.uint32)
+        dXh = dX.cpu().numpy()
+        if rc:
+            z = Z.view(-1, 2, net.I)
+            fwd = (z[:, 0, 0] >= z[:, 1, 0]).cpu().numpy()          # the first model's outputs choose the strand
+            Zs.append(torch.where(z[:, 0] >= z[:, 1], z[:, 0], z[:, 1]))
+            for b in range(len(chunk)):
+                r = 2 * b + (0 if fwd[b] else 1)
+                maps.append(dXh[Rh[r, 0] + pad:Rh[r, 1]].copy())
+                strands.append(0 if fwd[b] else 1)
+        else:
+            Zs.append(Z)
+            for b in range(len(chunk)):
+                maps.append(dXh[Rh[b, 0] + pad:Rh[b, 1]].copy())
+                strands.append(0)
+    return torch.cat(Zs), maps, np.asarray(strands, np.int8)

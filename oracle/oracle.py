@@ -358,6 +358,41 @@ def score_net(params, X, R, pool="max", nmodel=1, strand_max=False):
     return h
 
 
+def input_gradients(params, X, R, pool="max", nmodel=1, loss="mse", strand_max=False, dropout_rate=None):
+    """Gradient maps of kangaroo.predict (predict.py:168-265 with deepity/node.py:317-338):
+    the model output Z (after the logistic when the loss is nll) is fed back through a loss
+    with target 0 and no minibatch mean, dZ = Z - 0 (loss.py:98-112), through the dense
+    layers in test mode (full.py:84-89, dropout as scaling by 1 - rate), pooling
+    (poolrgn_bprop), the rectifier and the scan (corr1ord.py:128-133) down to dX [npos, 4].
+    With strand_max, of each forward / reverse-complement row pair only the row with the
+    larger output feeds back (loss.py:113-117).  Returns (Z [nrow, I], dX)."""
+    I = nmodel
+    W, b = params["Wscan"], params["bscan"]
+    act = np.maximum(corr1ord(W, X) + b.reshape(1, -1), 0)
+    pooled, A = poolrgn(act, R, pool, True)
+    pd = pooled if dropout_rate is None else dropout_fp_te(pooled, np.asarray(dropout_rate, pooled.dtype))
+    h1 = blockwise_dot(pd, params["W1"], I) + params["b1"].reshape(1, -1)
+    if "W2" in params:
+        out = blockwise_dot(np.maximum(h1, 0), params["W2"], I) + params["b2"].reshape(1, -1)
+    else:
+        out = h1
+    Z = 1.0 / (1.0 + np.exp(-out)) if loss == "nll" else out
+    dZ = Z.copy()
+    if strand_max:
+        z = Z.reshape(-1, 2, I)
+        keep = np.stack([z[:, 0] >= z[:, 1], ~(z[:, 0] >= z[:, 1])], 1).reshape(-1, I)
+        dZ = np.where(keep, dZ, 0)
+    if "W2" in params:
+        dh = blockwise_dot_nt(dZ, params["W2"], I) * (h1 > 0)
+    else:
+        dh = dZ
+    dpd = blockwise_dot_nt(dh, params["W1"], I)
+    dpooled = dpd if dropout_rate is None else dropout_bp_te(dpd, np.asarray(dropout_rate, dpd.dtype))
+    dact = poolrgn_bprop(np.zeros_like(act), R, np.ascontiguousarray(dpooled.astype(act.dtype)), A, pool) * (act > 0)
+    dX = corr1ord_bprop_X(np.zeros((X.size, 4), W.dtype), W, np.ascontiguousarray(dact.astype(W.dtype)))
+    return Z, dX
+
+
 def train_grads(params, X, R, Y, pool="all", nmodel=1, loss="nll", dropmask=None,
                 decay=None, Ymask=None, strand_pairs=False):
     """One forward/backward pass of the training graph; returns (loss[I], grads).

@@ -73,3 +73,46 @@ def test_predict_host_equals_device_scoring(cuda, nseq):
     out2 = torch.empty_like(out_host)
     net.predict_host(X_host, R_host, out2, tc=False)
     assert torch.equal(out2, exact)
+
+
+@pytest.mark.parametrize("I,pool,hidden,loss,rate,rc", [(1, "max", 0, "mse", None, False), (3, "all", 32, "nll", 0.3, False),
+                                                        (2, "max", 32, "nll", None, True), (1, "avg", 0, "mse", 0.5, True)])
+def test_input_gradients_match_the_oracle_chain(cuda, orc, I, pool, hidden, loss, rate, rc):
+    """Z fed back as dZ = Z through the dense layers in test mode, pooling, rectifier and scan to dX."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m = 24
+    p = synth.model_params(I, m, 19, pool, hidden=hidden)
+    X, R = synth.ragged_batch(40, 25, 90, m, seed=20, n_frac=0.03, both_strands=rc)
+    net = DeepBindNet(p, I, pool, loss=loss)
+    if rate is not None:
+        net.set_dropout(rate)
+    Z, dX = net.input_gradients(torch.from_numpy(X).cuda(), torch.from_numpy(R.view(np.int32)).cuda(), strand_max=rc)
+    wZ, wdX = orc.input_gradients({k: v.astype(np.float64) for k, v in p.items()}, X, R, pool, I, loss, strand_max=rc,
+                                  dropout_rate=None if rate is None else np.full(I, rate))
+    np.testing.assert_allclose(Z.cpu().numpy(), wZ, rtol=2e-5, atol=1e-6)
+    assert np.abs(wdX).max() > 0
+    assert np.max(np.abs(dX.cpu().numpy() - wdX)) <= 2e-5 * np.abs(wdX).max()
+
+
+def test_gradient_maps_per_sequence(cuda, orc):
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    from deepbind_b200.predict import gradient_maps, predict
+    rng = np.random.default_rng(5)
+    m = 16
+    seqs = seqs_of(rng, 70, 18, 60)
+    p = synth.model_params(1, m, 21, "max")
+    net = DeepBindNet(p, 1, "max", loss="mse")
+    for rc in (False, True):
+        Z, maps, strands = gradient_maps(net, seqs, reverse_complement=rc, batchsize=32)
+        np.testing.assert_allclose(Z.cpu().numpy(), predict(net, seqs, reverse_complement=rc)["direct"].cpu().numpy(), rtol=1e-5, atol=1e-6)
+        assert len(maps) == len(seqs) and all(g.shape == (len(s), 4) for g, s in zip(maps, seqs))
+        assert (strands == 0).all() if not rc else set(strands.tolist()) <= {0, 1}
+        Xo, Ro = orc.asbatch(seqs, m - 1, rc)
+        _, wdX = orc.input_gradients(p, Xo, Ro, "max", 1, "mse", strand_max=rc)
+        for b in (0, 13, 69):
+            r = (2 * b + int(strands[b])) if rc else b
+            want = wdX[Ro[r, 0] + m - 1:Ro[r, 1]]
+            assert np.max(np.abs(maps[b] - want)) <= 2e-5 * max(np.abs(wdX).max(), 1e-12)

@@ -292,3 +292,39 @@ def test_scan_mode_windows(orc):
     from deepbind_b200 import fused
     for L, W, s in [(4, 3, 1), (4, 3, 4), (1, 1, 1), (0, 3, 1), (37, 20, 7), (5, 64, 64)]:
         assert int(fused.window_counts([L], W, s)[0]) == len(orc.scan_windows("A" * L, W, s))
+
+
+def test_input_gradients_against_finite_differences(orc):
+    """dX of the gradient-map chain = d(1/2 sum Z^2)/d(one-hot input), checked with central
+    differences on a dense float64 restatement (one-hot input times the filter taps)."""
+    rng = np.random.default_rng(12)
+    m, nf, L, nseq = 4, 16, 9, 3
+    pad = m - 1
+    seqs = [rng.integers(0, 4, L) for _ in range(nseq)]
+    X = np.concatenate([np.concatenate([np.full(pad, 255, np.uint8), s.astype(np.uint8)]) for s in seqs] + [np.full(pad, 255, np.uint8)])
+    R = np.array([[i * (L + pad), (i + 1) * (L + pad)] for i in range(nseq)], np.uint32)
+    p = {"Wscan": rng.standard_normal((4 * m, nf)) * 0.5, "bscan": rng.uniform(-0.2, 0.2, nf),
+         "W1": rng.standard_normal((nf, 1)), "b1": rng.standard_normal(1)}
+    Z, dX = orc.input_gradients(p, X, R, "max", 1, "mse")
+
+    def objective(H):                                    # H [npos, 4]: channel weights of every position
+        n = X.size - m + 1
+        act = np.zeros((X.size, nf))
+        for j in range(m):
+            act[:n] += H[j:j + n] @ p["Wscan"][4 * j:4 * j + 4]
+        act = np.maximum(act + p["bscan"], 0)
+        pooled = np.stack([act[a:b].max(axis=0) for a, b in R])
+        out = pooled @ p["W1"] + p["b1"]
+        return 0.5 * float((out ** 2).sum()), out
+    H0 = np.where(X[:, None] == 255, 0.25, (X[:, None] == np.arange(4)).astype(float))
+    _, out0 = objective(H0)
+    assert np.allclose(out0, Z, rtol=1e-12, atol=1e-12)
+    eps = 1e-6
+    fd = np.zeros_like(H0)
+    for i in range(X.size):
+        for k in range(4):
+            Hp, Hm = H0.copy(), H0.copy()
+            Hp[i, k] += eps; Hm[i, k] -= eps
+            fd[i, k] = (objective(Hp)[0] - objective(Hm)[0]) / (2 * eps)
+    assert np.abs(dX).max() > 0
+    assert np.max(np.abs(fd - dX)) <= 1e-6 * np.abs(dX).max() + 1e-8
