@@ -99,3 +99,48 @@ def gradient_maps(net, seqs, reverse_complement=False, batchsize=2048):
                 maps.append(dXh[Rh[b, 0] + pad:Rh[b, 1]].copy())
                 strands.append(0)
     return torch.cat(Zs), maps, np.asarray(strands, np.int8)
+
+
+_ORD = np.full(256, 255, np.uint8)
+for _k, _c in enumerate("ACGT"):
+    _ORD[ord(_c)] = _k
+    _ORD[ord(_c.lower())] = _k
+_ORD[ord("U")] = _ORD[ord("u")] = 3
+
+
+def mutation_maps(net, seqs, reverse_complement=False):
+    """Mutation maps of kangaroo.predict (``want_gmaps="finite_diff"``, predict.py:208-250):
+    every position of every sequence is set to each of the four bases in turn, the mutant
+    is scored like the sequence itself (both strands and the larger score with
+    ``reverse_complement``), and the map holds mtZ - Z, set to 0 where neither score is
+    positive.  The 4 * len mutants of a sequence are laid out as one batch directly in
+    ordinal form (no strings) and scored by the fused scan kernel in one pass.
+
+    Returns (Z [nseq, I] numpy, maps: list of numpy [len_b, 4, I])."""
+    pad = net.m - 1
+    rc = bool(reverse_complement)
+    Zs, maps = [], []
+    for s in seqs:
+        o = _ORD[np.frombuffer(s.encode("latin-1"), np.uint8)]
+        L = len(o)
+        rows = np.tile(o, (4 * L + 1, 1))                        # row 0: the sequence itself
+        idx = np.arange(L)
+        for j in range(4):
+            rows[1 + 4 * idx + j, idx] = j
+        if rc:
+            rev = rows[:, ::-1].copy()
+            acgt = rev < 4
+            rev[acgt] = 3 - rev[acgt]
+            rows = np.stack([rows, rev], 1).reshape(-1, L)       # forward, reverse complement, forward, ...
+        n = rows.shape[0]
+        Xh = np.full((n, pad + L), 255, np.uint8)
+        Xh[:, pad:] = rows
+        Xh = np.concatenate([Xh.ravel(), np.full(pad, 255, np.uint8)])
+        Rh = (np.arange(n, dtype=np.int64)[:, None] * (pad + L) + np.array([0, pad + L])).astype(np.int32)
+        Z = net.score(torch.from_numpy(Xh).to(net.dev), torch.from_numpy(Rh).to(net.dev), strand_max=rc).cpu().numpy()
+        z0, mt = Z[0], Z[1:].reshape(L, 4, net.I)
+        d = mt - z0
+        d *= np.maximum(0, np.sign(np.maximum(z0, mt)))
+        Zs.append(z0)
+        maps.append(d)
+    return np.stack(Zs), maps

@@ -116,3 +116,29 @@ def test_gradient_maps_per_sequence(cuda, orc):
             r = (2 * b + int(strands[b])) if rc else b
             want = wdX[Ro[r, 0] + m - 1:Ro[r, 1]]
             assert np.max(np.abs(maps[b] - want)) <= 2e-5 * max(np.abs(wdX).max(), 1e-12)
+
+
+@pytest.mark.parametrize("rc", [False, True])
+def test_mutation_maps(cuda, orc, rc):
+    """Every single-base mutant scored through the device path against the oracle scoring the mutated strings."""
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    from deepbind_b200.predict import mutation_maps
+    rng = np.random.default_rng(6)
+    m, I = 16, 2
+    seqs = seqs_of(rng, 4, 12, 30)
+    p = synth.model_params(I, m, 23, "max")
+    net = DeepBindNet(p, I, "max")
+    Z, maps = mutation_maps(net, seqs, reverse_complement=rc)
+    for b, s in enumerate(seqs):
+        mutants = [s] + [s[:i] + c + s[i + 1:] for i in range(len(s)) for c in "ACGT"]
+        want = orc.predict(p, mutants, m, "max", I, reverse_complement=rc)["direct"]
+        z0, mt = want[0], want[1:].reshape(len(s), 4, I)
+        d = (mt - z0) * np.maximum(0, np.sign(np.maximum(z0, mt)))
+        np.testing.assert_allclose(Z[b], z0, rtol=1e-5, atol=1e-6)
+        assert maps[b].shape == (len(s), 4, I)
+        assert np.max(np.abs(maps[b] - d)) <= 1e-5 * max(np.abs(want).max(), 1e-6)
+        # a mutation to the base already there changes nothing
+        for i, c in enumerate(s):
+            if c in "ACGT":
+                assert np.all(maps[b][i, "ACGT".index(c)] == 0)
