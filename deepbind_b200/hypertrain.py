@@ -155,3 +155,41 @@ def train_final(layers, trainer_spec, best, seqs, Y, ntrial=3, seed=0, motif_len
     Z = _validate(net, list(seqs), Yv)
     vals = np.asarray([calc_auc(Z[:, t], Yv[:, 0]) if net.loss == "nll" else pearson(Z[:, t], Yv[:, 0]) for t in range(ntrial)])
     return net, int(np.nanargmax(vals)), vals
+
+
+# ------------------------------------------------------------------ persistence
+def save_model(path, net, instance=None, meta=None):
+    """Writes the trained model to ``path`` (.npz): the parameter blocks, and what is
+    needed to rebuild the net (pooling, loss, dropout rates, number of instances) plus
+    ``meta`` (any JSON-serialisable record, e.g. the chosen hyper-parameters) -- the
+    counterpart of the reference's ``model.pkl`` (kangaroo/train.py:150-172).
+    ``instance``: keep only that instance (e.g. the best trial of ``train_final``)."""
+    P = net.params_numpy("P")
+    I = net.I
+    rate = None if net.dropout_rate is None else np.asarray(net.dropout_rate, np.float32)
+    if instance is not None:
+        t, out = int(instance), {}
+        for k, w in P.items():
+            if k in ("W1", "W2"):                 # instances stacked on rows
+                rows = w.shape[0] // I
+                out[k] = w[t * rows:(t + 1) * rows]
+            else:                                 # instances side by side on columns
+                cols = w.shape[-1] // I
+                out[k] = w[..., t * cols:(t + 1) * cols]
+        P, I = out, 1
+        rate = None if rate is None else rate[t:t + 1]
+    info = {"nmodel": I, "pool": net.pool, "loss": net.loss, "dropout_rate": None if rate is None else rate.tolist(),
+            "meta": meta}
+    np.savez(path, __info__=np.frombuffer(json.dumps(info).encode(), np.uint8), **P)
+
+
+def load_model(path, device=None):
+    """Rebuilds the net written by ``save_model``; returns (net, meta)."""
+    from .model import DeepBindNet
+    with np.load(path) as f:
+        info = json.loads(bytes(f["__info__"]).decode())
+        P = {k: f[k] for k in f.files if k != "__info__"}
+    net = DeepBindNet(P, info["nmodel"], info["pool"], loss=info["loss"], device=device)
+    if info["dropout_rate"] is not None:
+        net.set_dropout(np.asarray(info["dropout_rate"], np.float32))
+    return net, info["meta"]

@@ -46,3 +46,25 @@ def test_calibrate_then_train(cuda, tmp_path):
     assert [r["value"] for r in again] == [r["value"] for r in records]          # same seeds, same kernels: same numbers
     net, trial, vals = train_final(layers, spec, best, seqs, y, ntrial=3, seed=5)
     assert net.I == 3 and 0 <= trial < 3 and vals[trial] == np.nanmax(vals) and vals[trial] > 0.6
+
+
+def test_saved_model_scores_like_the_trained_one(cuda, tmp_path):
+    """save_model / load_model: all instances, and one instance cut out of a multi-instance net."""
+    import torch
+    from deepbind_b200 import cfg
+    from deepbind_b200.hypertrain import load_model, save_model
+    from deepbind_b200.predict import predict
+    rng = np.random.default_rng(4)
+    seqs, _ = planted(rng, 60)
+    net, _ = cfg.instantiate(cfg.loads(MODEL), ninst=3, seed=7)
+    want = predict(net, seqs)["direct"].cpu().numpy()
+    path = os.path.join(str(tmp_path), "model.npz")
+    save_model(path, net, meta={"sample": 2, "rate": [0.01]})
+    net2, meta = load_model(path)
+    assert meta == {"sample": 2, "rate": [0.01]} and net2.I == 3 and net2.pool == net.pool and net2.loss == net.loss
+    assert torch.equal(net2.P, net.P)
+    np.testing.assert_array_equal(predict(net2, seqs)["direct"].cpu().numpy(), want)
+    save_model(path, net, instance=1)
+    one, _ = load_model(path)
+    assert one.I == 1
+    np.testing.assert_allclose(predict(one, seqs)["direct"].cpu().numpy()[:, 0], want[:, 1], rtol=1e-6, atol=1e-7)
