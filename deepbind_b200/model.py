@@ -314,19 +314,30 @@ class DeepBindNet(object):
                         torch.empty(R_host.shape, dtype=torch.int32, device=self.dev),
                         torch.empty(out_host.shape, dtype=torch.float32, device=self.dev))
         X, R, out = dev_bufs
-        X.copy_(X_host, non_blocking=True)
-        R.copy_(R_host, non_blocking=True)
         cur = torch.cuda.current_stream()
         if tc and self.hidden == 0 and self.nf == 16 * self.I and self.dropout_rate is None and R.shape[0] >= 8 * 4096:
-            # Scores go back to the host piece by piece on a second stream while the
-            # next piece is being scanned: the 4*I bytes per sequence of the read-back
+            # Both transfers are pipelined with the scan, piece by piece: the bases of the next
+            # piece go up on one side stream and the scores of the last piece come back on another
+            # while the current piece is scanned; the 4*I bytes per sequence of the read-back
             # otherwise add their full PCIe time to the step.
             if not hasattr(self, "_copy_stream"):
                 self._copy_stream = torch.cuda.Stream(device=self.dev)
+                self._up_stream = torch.cuda.Stream(device=self.dev)
                 self._status = torch.zeros(1, dtype=torch.int32, device=self.dev)
-            nseq, npiece = R.shape[0], 8
+            R.copy_(R_host, non_blocking=True)
+            nseq, npiece, npos = R.shape[0], 16, X.numel()
+            cuts = [(nseq * c) // npiece for c in range(npiece + 1)]
+            first = [int(R_host[lo, 0]) for lo in cuts[:-1]] + [npos]          # regions ascend (the batch layout)
+            self._up_stream.wait_stream(cur)
+            ups = []
+            with torch.cuda.stream(self._up_stream):
+                for c in range(npiece):
+                    a0, a1 = first[c], min(npos, first[c + 1] + self.m - 1)    # the piece's rows and the taps' reach past them
+                    X[a0:a1].copy_(X_host[a0:a1], non_blocking=True)
+                    ev = torch.cuda.Event(); ev.record(self._up_stream); ups.append(ev)
             for c in range(npiece):
-                lo, hi = (nseq * c) // npiece, (nseq * (c + 1)) // npiece
+                lo, hi = cuts[c], cuts[c + 1]
+                cur.wait_event(ups[c])
                 self.score_tc(X, R[lo:hi], check=False, out=out[lo:hi], status=self._status)
                 done = torch.cuda.Event()
                 done.record(cur)
@@ -339,6 +350,8 @@ class DeepBindNet(object):
                 raise _lib.SmatException("scanpool_tc(...) raised an exception\nRuntimeError: tensor-core scan failed (status %d)"
                                          % int(self._status.item()))
             return out_host
+        X.copy_(X_host, non_blocking=True)
+        R.copy_(R_host, non_blocking=True)
         if tc:
             self.score_tc(X, R, check=False, out=out)
         else:
