@@ -280,13 +280,14 @@ def side_workloads(dev, with_cpu):
         Xs, Ys = Xall[0].clone(), Yall[0].clone()
         Ms = Mall[0].clone() if Mall is not None else None
         feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)] + ([(Mall, Ms)] if Ms is not None else []))
-        graph, _ = net.capture_train_step(Xs, R1, Ys, Ms, feed=feed)
+        K = 8                                         # steps per replay: the host's cost of a replay is above a small step's GPU time
+        graph, _ = net.capture_train_step(Xs, R1, Ys, Ms, feed=feed, steps=K)
 
         def step():
             graph.replay()
-        for _ in range(200):                          # replays are tens of microseconds: warm up past the clock ramp
+        for _ in range(200 // K):                     # replays are tens of microseconds: warm up past the clock ramp
             step()
-        ms = _events_ms(step, reps)
+        ms = _events_ms(step, reps // K) / K
         cpu = None
         if with_cpu:
             mk = (np.random.default_rng(1).random((B, npool * I)) >= 0.5) if hidden else None
@@ -296,7 +297,7 @@ def side_workloads(dev, with_cpu):
                 orc.train_grads(p, Xb, Rh[:B], np.tile(Yh[0], (1, I)), pool, I, loss, mk)
             cpu = cpu_steps * B * I / (time.perf_counter() - t)
         out[name] = {"unit": "train samples/s (model x sample)", "value": I * B / ms * 1e3, "ms_per_step": ms,
-                     "models": I, "minibatch": B, "kernel": "f32 fused scan+pool forward/backward, CUDA-graph replay",
+                     "models": I, "minibatch": B, "kernel": "f32 fused scan+pool forward/backward, CUDA-graph replay (%d steps per replay)" % K,
                      "cpu": cpu, "adds_counted": "dense equivalent: forward scan + recompute + filter gradient = 3 scans of the minibatch "
                                                 "(with max pooling alone the backward kernel visits only the argmax rows)",
                      **rates(B * (L + M - 1), NMOTIF * I, M, ms, passes=3)}
@@ -335,14 +336,15 @@ def calibration_sharded(dev, rank, world):
     net.set_rates(lr_all[ids], 0.9)
     Xs, Ys = Xall[0].clone(), Yall[0].clone()
     feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)])
-    graph, loss = net.capture_train_step(Xs, R1, Ys, None, feed=feed)
+    K = 8                                             # steps per replay
+    graph, loss = net.capture_train_step(Xs, R1, Ys, None, feed=feed, steps=K)
     nmax = (NMODEL + world - 1) // world
     mine = torch.zeros(nmax, dtype=torch.float32, device=dev)
     everyone = torch.empty(world * nmax, dtype=torch.float32, device=dev)
 
     def run(n):
-        for _ in range(n):
-            graph.replay()                            # fetch of the next minibatch + training step
+        for _ in range(n // K):
+            graph.replay()                            # K times: fetch of the next minibatch + training step
         mine[:I] = loss.view(-1)[:I]
         dist.all_gather_into_tensor(everyone, mine)
     run(200)

@@ -360,7 +360,7 @@ class DeepBindNet(object):
         cur.synchronize()
         return out_host
 
-    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3, feed=None, prologue=None):
+    def capture_train_step(self, X, R, Y, dropmask=None, warmup=3, feed=None, prologue=None, steps=1):
         """Captures one Nesterov step on the static buffers X, R, Y, dropmask into a
         CUDA graph and returns (graph, loss): refill the buffers in place (same
         shapes) and call ``graph.replay()`` for every further step.  A minibatch
@@ -374,7 +374,11 @@ class DeepBindNet(object):
         walks the dataset with no host work between steps; the feed's step counter is
         back at zero when this returns.  ``prologue`` (a callable launching further
         kernels, e.g. the draw of the step's dropout mask into ``dropmask``) runs inside
-        the graph between the fetch and the step."""
+        the graph between the fetch and the step.  ``steps`` > 1 (with a feed) captures that
+        many consecutive steps into the one graph: a replay of a small model's step costs
+        the host more than the step takes on the GPU, and several steps per replay bring
+        the loop back to the GPU's pace; ``loss`` is then that of the last step."""
+        assert steps == 1 or feed is not None, "several steps per graph need a feed that advances by itself"
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
@@ -392,11 +396,12 @@ class DeepBindNet(object):
             torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            if feed is not None:
-                feed.fetch()
-            if prologue is not None:
-                prologue()
-            loss = self.train_step(X, R, Y, dropmask)
+            for _ in range(steps):
+                if feed is not None:
+                    feed.fetch()
+                if prologue is not None:
+                    prologue()
+                loss = self.train_step(X, R, Y, dropmask)
         return graph, loss
 
     def capture_score(self, X, R, strand_max=False, warmup=3):

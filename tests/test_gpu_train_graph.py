@@ -155,3 +155,33 @@ def test_device_drawn_dropout_masks(cuda, matchrows):
         seen.append(M.clone())
     assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])
     assert counters.tolist() == [6, 0]
+
+
+def test_several_steps_per_graph_equal_single_steps(cuda):
+    """Four steps captured into one graph and replayed twice = eight eager steps over the dataset."""
+    import torch
+    from deepbind_b200 import fused, synth
+    from deepbind_b200.model import DeepBindNet
+    m, B, I, nbatch = 24, 32, 2, 3
+    p = synth.model_params(I, m, 3, "all", hidden=32)
+    Xh, Rh = synth.uniform_batch(B * nbatch, 40, m, seed=1)
+    rows = B * (40 + m - 1)
+    Xall = torch.from_numpy(np.stack([np.concatenate([Xh[i * rows:(i + 1) * rows], np.full(m - 1, 255, np.uint8)])
+                                      for i in range(nbatch)])).cuda()
+    R = torch.from_numpy(Rh[:B].view(np.int32)).cuda()
+    g = synth.rng(2)
+    Yall = torch.from_numpy(np.tile(g.integers(0, 2, size=(nbatch, B, 1)).astype(np.float32), (1, 1, I))).cuda()
+    Mall = torch.from_numpy(g.random((nbatch, B, 32 * I)) >= 0.5).cuda()
+    eager = DeepBindNet(p, I, "all", loss="nll"); eager.set_rates(0.02, 0.9)
+    for s in range(8):
+        eager.train_step(Xall[s % nbatch], R, Yall[s % nbatch], Mall[s % nbatch])
+    net = DeepBindNet(p, I, "all", loss="nll"); net.set_rates(0.02, 0.9)
+    P0, m0 = net.P.clone(), net.mP.clone()
+    Xs, Ys, Ms = Xall[0].clone(), Yall[0].clone(), Mall[0].clone()
+    feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys), (Mall, Ms)])
+    graph, _ = net.capture_train_step(Xs, R, Ys, Ms, feed=feed, steps=4)
+    net.P.copy_(P0); net.mP.copy_(m0)
+    graph.replay(); graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(net.P, eager.P) and torch.equal(net.mP, eager.mP)
+    assert feed.counters.tolist() == [8, 0]
