@@ -115,25 +115,36 @@ class Trainer(object):
                     _lib.load().db_dropout_mask(sM0.data_ptr(), sM0.shape[0], sM0.shape[1], rate_dev.data_ptr(), net.I,
                                                 int(self.reverse_complement), mask_counters.data_ptr())
         loss = None
-        for step in range(max_steps):
+        K = 8            # steps per replay where a run of K steps allows it: a replay costs the host more than a small step
+        cps = sorted(checkpoints)
+        step = 0
+        while step < max_steps:
             X, R, Yb = batches[step % nb]
             net.decay_on = step >= spec.weight_decay_start
+            ran = 1
             if static is not None and step % nb < nfull:
                 sX, sR, sY, sM = static
-                key = bool(net.decay_on)
+                # K steps in one replay if none of them is the short minibatch, switches the decay on,
+                # or passes a checkpoint before the run's last step
+                nextcp = next((c for c in cps if c > step), max_steps)
+                many = (step % nb) + K <= nfull and step + K <= min(max_steps, nextcp) and \
+                    (step >= spec.weight_decay_start or step + K <= spec.weight_decay_start)
+                key = (bool(net.decay_on), K if many else 1)
                 if key not in graphs:
                     # the capture's warm-up steps are real steps: put the state back afterwards
                     P0, mP0 = net.P.clone(), net.mP.clone()
                     graphs[key] = net.capture_train_step(sX, sR, sY, sM, warmup=1 if graphs else 3, feed=feed,
-                                                         prologue=draw_mask if sM is not None else None)
+                                                         prologue=draw_mask if sM is not None else None, steps=key[1])
                     net.P.copy_(P0); net.mP.copy_(mP0)
                     feed.counters[0] = (step // nb) * nfull + min(step % nb, nfull)     # captured steps run so far
                 graphs[key][0].replay()
                 loss = graphs[key][1]
+                ran = key[1]
             else:
                 draws = uniform_draws(step, (R.shape[0], self._mask_cols())) if uniform_draws else None
                 loss = net.train_step(X, R, Yb, self._mask(R.shape[0], draws))
-            self.step = step + 1
+            step += ran
+            self.step = step
             if self.step in checkpoints:
                 self.history.append((self.step, self.evaluate(batches[:100])))
                 if on_checkpoint:

@@ -130,3 +130,24 @@ def test_graph_training_with_device_drawn_dropout(cuda, rc):
     assert len(losses) == 3 and all(np.isfinite(l).all() for l in losses)
     assert (losses[-1] < losses[0]).all()
     assert np.isfinite(net.P.cpu().numpy()).all()
+
+
+def test_eight_step_replays_equal_eager_steps(cuda):
+    """Enough minibatches for runs of eight steps per replay, cut by checkpoints, the start of the
+    weight decay and the end of an epoch: same parameters and checkpoint losses as step-by-step calls."""
+    from deepbind_b200 import cfg
+    from deepbind_b200.trainer import Trainer
+    rng = np.random.default_rng(9)
+    seqs, Y = make_data(rng, 32 * 20 + 7, 40, False)               # 20 full minibatches and a short one
+    spec = cfg.sgd(rate=0.02, momentum=0.9, batchsize=32, max_epochs=100, max_steps=75, checkpoints=3, weight_decay_start=11)
+    out, hist = [], []
+    for use_graph in (False, True):
+        net, _ = cfg.instantiate(cfg.loads(LINEAR), ninst=3, seed=2)
+        t = Trainer(net, spec, seed=1)
+        t.fit(seqs, Y, use_graph=use_graph)
+        out.append(net.P.cpu().numpy())
+        hist.append([(s, np.asarray(l.cpu() if hasattr(l, "cpu") else l)) for s, l in t.history])
+    np.testing.assert_array_equal(out[0], out[1])
+    assert [s for s, _ in hist[0]] == [s for s, _ in hist[1]] == [25, 50, 75]
+    for (_, a), (_, b) in zip(*hist):
+        np.testing.assert_array_equal(a, b)
