@@ -64,6 +64,8 @@ _PROTOTYPES = {
     "api_fill_zero": (None, [c_smat_p]),
     "api_set_seed": (None, [c_uint64]),
     "api_launch_count": (c_uint64, []),
+    "db_reserve_scratch": (None, [c_size_t]),
+    "db_scratch_bytes": (c_size_t, []),
     "register_ext": (None, []),
     "api_autotune": (None, []),
     "api_corr1ord": (None, [c_smat_p, c_smat_p, c_smat_p, POINTER(c_corr1ord_options_t)]),
@@ -110,11 +112,12 @@ _PROTOTYPES = {
     "db_scanpool_bwd": (None, [c_uint32, c_uint32, P, c_uint32, P, c_uint32, c_int, P, P, P, P, P]),
     "db_tc_weights_bytes": (c_size_t, [c_uint32, c_uint32, c_int]),
     "db_tc_prepare": (None, [P, c_uint32, c_uint32, c_int, P]),
+    "db_scanpool_tc_debug": (None, [c_uint64, c_int]),
     "db_scanpool_tc": (None, [P, c_uint32, c_uint32, c_int, P, c_int, P, c_uint32, P, c_uint32, c_int,
                               P, P, P, c_uint32, P, P]),
 }
 
-_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count"}
+_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count", "db_scratch_bytes"}
 
 
 class _SafeFunc(object):

@@ -43,17 +43,29 @@ void ensure_device()
 	s.sm_count = prop.multiProcessorCount;
 }
 
+// Scratch for two-stage reductions.  A CUDA graph captured from a training or scoring
+// step holds the address it was captured with, so a buffer that has been handed out is
+// never freed: when a later call needs more, a larger buffer is allocated and the old
+// one is retired, alive until the process ends (growth is by half, so the retired ones
+// together stay below twice the live one).  Growing inside a stream capture is refused:
+// run the step once before capturing it, or reserve with db_reserve_scratch().
 void* scratch(size_t bytes)
 {
 	state_t& s = state();
 	if (bytes > s.scratch_bytes) {
-		if (s.scratch) {
-			DB_CUDA(cudaStreamSynchronize(s.stream));
-			DB_CUDA(cudaFree(s.scratch));
-			s.scratch = nullptr; s.scratch_bytes = 0;
-		}
+		cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+		DB_CUDA(cudaStreamIsCapturing(s.stream, &cap));
+		DB_REQUIRE(cap == cudaStreamCaptureStatusNone,
+		           "RuntimeError: %zu bytes of scratch needed while the stream is being captured (have %zu); run the step once "
+		           "before capturing it, or call db_reserve_scratch first", bytes, s.scratch_bytes);
 		size_t want = bytes < (1u << 20) ? (1u << 20) : bytes + bytes / 2;
-		DB_CUDA(cudaMalloc(&s.scratch, want));
+		void* fresh = nullptr;
+		cudaError_t e = cudaMalloc(&fresh, want);
+		if (e != cudaSuccess)
+			throw error(format("MemoryError: cudaMalloc of %zu bytes of scratch failed: %s", want, cudaGetErrorString(e)));
+		if (s.scratch)
+			s.retired_scratch.push_back(s.scratch);
+		s.scratch = fresh;
 		s.scratch_bytes = want;
 	}
 	return s.scratch;
@@ -128,6 +140,15 @@ DB_EXPORT void api_set_device(int device)
 }
 
 DB_EXPORT uint64_t api_launch_count(void) { return state().launches; }
+
+DB_EXPORT void db_reserve_scratch(size_t bytes)
+{
+	DB_API_TRY
+	scratch(bytes);
+	DB_API_CATCH
+}
+
+DB_EXPORT size_t db_scratch_bytes(void) { return state().scratch_bytes; }
 
 DB_EXPORT void api_set_seed(uint64_t seed)
 {

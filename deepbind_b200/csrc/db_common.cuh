@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <stdexcept>
 #include <string>
+#include <vector>
 #include "../../include/deepbind_b200.h"
 
 #define DB_EXPORT extern "C" __attribute__((visibility("default")))
@@ -25,6 +26,7 @@ struct state_t {
 	uint64_t     rng_calls = 0;     // advances per random-mask call
 	void*        scratch = nullptr; // grow-only device scratch for two-stage reductions
 	size_t       scratch_bytes = 0;
+	std::vector<void*> retired_scratch; // outgrown scratch buffers, kept: captured graphs may still use them
 	uint64_t     launches = 0;      // kernels launched by this library on this thread
 };
 state_t& state();
@@ -37,7 +39,7 @@ struct error : std::runtime_error {
 
 // Binds the calling thread's device on first use and caches its SM count.
 void ensure_device();
-void* scratch(size_t bytes);   // stream-ordered use only; grows with cudaMalloc
+void* scratch(size_t bytes);   // stream-ordered use only; grows with cudaMalloc, never frees (see db_api.cu)
 // FP32 motif scan writing Z [n, nf] (scanpool_f32.cu); n = rows written, X holds n + m - 1 bytes
 void launch_corr1ord_f32(const float* W, unsigned m, unsigned nf, const uint8_t* X, unsigned n, float* Z);
 // FP32 filter gradient of the scan from dZ [n, nf], accumulated into dW (scanpool_f32.cu)

@@ -5,6 +5,7 @@
 // order so that repeated runs agree bit for bit (the reference's reduce_y is
 // also free of atomics, smat_cuda/reduce_y.cuh:52-126).
 #include "db_common.cuh"
+#include <mutex>
 
 namespace db {
 
@@ -183,13 +184,17 @@ static __device__ __align__(256) float g_colsum_static_scratch[COLSUM_STATIC_FLO
 
 // In host code the array's name is only a handle for the runtime, not an address
 // a kernel may use.  The real device address is asked for once per device, with
-// that device current, and cached.
+// that device current, and cached; the cache is filled under a lock because host
+// threads bound to different devices may make their first calls at the same time.
+// (A cudaDeviceReset in the host process invalidates the cached address.)
 static float* colsum_static_scratch_ptr()
 {
+	static std::mutex lock;
 	static float* ptrs[64] = {nullptr};
 	int dev = 0;
 	DB_CUDA(cudaGetDevice(&dev));
 	DB_REQUIRE(dev >= 0 && dev < 64, "RuntimeError: device index %d out of range", dev);
+	std::lock_guard<std::mutex> guard(lock);
 	if (!ptrs[dev]) {
 		void* p = nullptr;
 		cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);

@@ -49,7 +49,7 @@ static constexpr int TC_EPI_SETS = 4;      // epilogue warps per TMEM lane quart
 static constexpr int TC_BUILD_WARPS = 2;   // warps that encode the B operand (one stage ahead; a stage lasts 8 tiles)
 static constexpr int TC_EPI_WARP0 = 1 + TC_BUILD_WARPS;             // first epilogue warp
 static constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + 4 * TC_EPI_SETS);
-static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // clock cycles (about 0.1 s)
+static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // default deadline of a wait, clock cycles (about 0.1 s)
 
 struct tc_args {
 	const uint8_t* X; const uint32_t* R; const __nv_bfloat16* Wt; const float* bias;
@@ -59,6 +59,8 @@ struct tc_args {
 	int ptype, relu;
 	unsigned f16;                   // operand type of both MMA inputs: 0 = bf16, 1 = f16 (weights prescaled by a power of two)
 	const uint32_t* maxabs;         // bit pattern of max |W|, kept behind the prepared tiles
+	unsigned long long timeout;     // clock cycles a wait may last before the CTA gives up
+	unsigned hold_operands;         // test aid: the operand encoders never announce their stage, so the issuer's wait runs out
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -86,14 +88,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity)
 // Bounded wait: false when the deadline passes or another role has aborted.
 // (A try_wait with a suspend-time hint instead of the short sleep was measured
 // 10 % slower: the waiters wake later than they do from a 40 ns sleep.)
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, unsigned long long timeout)
 {
 	if (mbar_try_wait(bar, parity)) return true;
 	const unsigned long long t0 = clock64();
 	while (true) {
 		if (mbar_try_wait(bar, parity)) return true;
 		if (*abort_flag) return false;
-		if (clock64() - t0 > TC_TIMEOUT) { *abort_flag = 1; return false; }
+		if (clock64() - t0 > timeout) { *abort_flag = 1; return false; }
 		__nanosleep(40);        // a spinning warp would take issue slots from the epilogue warp of its scheduler
 	}
 }
@@ -409,7 +411,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 		// waits (bounded) and the warp stays converged for the aligned TMEM loads.
 		if (!__all_sync(0xffffffffu, mbar_try_wait(&t_full[slot], (t >> 1) & 1))) {
 			unsigned okv = 0;
-			if (lane == 0) okv = mbar_wait(&t_full[slot], (t >> 1) & 1, abort_flag) ? 1u : 0u;
+			if (lane == 0) okv = mbar_wait(&t_full[slot], (t >> 1) & 1, abort_flag, a.timeout) ? 1u : 0u;
 			ok = __shfl_sync(0xffffffffu, okv, 0) != 0;
 			if (!ok) break;
 			mbar_try_wait(&t_full[slot], (t >> 1) & 1);    // completed: every lane observes the phase
@@ -451,6 +453,90 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	while (ok && g < g_last) ok = finish_region();
 }
 
+// Epilogue for region-aligned tiles (uniform batches): region i of the CTA lies in tile
+// i / k at column (i % k) * S and is P columns long.  The warps of a lane quarter take
+// the regions in turn as in tc_epilogue, but a region is always whole: wait for its
+// tile, reduce its P columns, hand the tile back, then write the outputs.
+template <bool WANT_MAX, bool WANT_SUM, bool RELU>
+__device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t tmem_base, uint64_t* t_full, uint64_t* t_empty,
+                                                    volatile int* abort_flag, unsigned tile, unsigned g_first, unsigned nreg,
+                                                    unsigned P, unsigned S, unsigned k, unsigned warp, unsigned lane)
+{
+	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
+	const unsigned set = (warp - TC_EPI_WARP0) >> 2;
+	const unsigned f = tile * 128 + q4 * 32 + lane;     // this thread's filter = its TMEM lane
+	const uint32_t maxabs_bits = *a.maxabs;
+	const float wscale = a.f16 ? tc_weight_scale(maxabs_bits) : 1.f, inv_wscale = 1.f / wscale;    // powers of two
+	const float b0 = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
+	const float b = b0 * wscale;
+	const float ssat = pow2_above((float)a.m * __uint_as_float(maxabs_bits) + fabsf(b0));
+	const float cm = inv_wscale / ssat, ca = b0 / ssat;
+	float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
+	const unsigned model = f / 16;
+	if (a.scores && f < a.nf) {
+		const unsigned npool = a.ptype == DB_PT_ALL ? 32u : 16u, kk = f % 16;
+		if (a.ptype == DB_PT_ALL) { hw_max = a.headW[model * npool + 2 * kk]; hw_sum = a.headW[model * npool + 2 * kk + 1]; }
+		else if (a.ptype == DB_PT_MAX) hw_max = a.headW[model * npool + kk];
+		else hw_sum = a.headW[model * npool + kk];
+		hb = a.headB ? a.headB[model] : 0.f;
+	}
+	const float fP = (float)P;
+	const uint32_t lane_base = tmem_base + ((q4 * 32u) << 16);
+	unsigned t = 0, j = set;                            // tile and place in the tile of this warp's region
+	while (j >= k) { j -= k; ++t; }
+	pool_state ps;
+	for (unsigned i = set; i < nreg; i += TC_EPI_SETS) {
+		const unsigned slot = t & 1, par = (t >> 1) & 1;
+		if (!__all_sync(0xffffffffu, mbar_try_wait(&t_full[slot], par))) {
+			unsigned okv = 0;
+			if (lane == 0) okv = mbar_wait(&t_full[slot], par, abort_flag, a.timeout) ? 1u : 0u;
+			if (__shfl_sync(0xffffffffu, okv, 0) == 0) return;
+			mbar_try_wait(&t_full[slot], par);          // completed: every lane observes the phase
+		}
+		tc_fence_after();
+		uint32_t ta = lane_base + slot * 256u + j * S;
+		ps.reset();
+		unsigned left = P;
+		float va[32];
+		#pragma unroll 1                                // P is loop-invariant: unrolled copies would only cost registers
+		while (left >= 32) {
+			tmem_ld32(ta, va);
+			tmem_ld_wait();
+			ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, cm, ca);
+			ta += 32; left -= 32;
+		}
+		if (left) {
+			load_piece(ta, left, va);
+			tmem_ld_wait();
+			ps.add_piece<WANT_MAX, WANT_SUM, RELU>(va, left, cm, ca);
+		}
+		// the region's columns are in registers: the tile goes back before the outputs are written
+		tc_fence_before();
+		__syncwarp();
+		if (lane == 0) mbar_arrive(&t_empty[slot]);
+		const unsigned g = g_first + i;
+		float pmax = ps.max_all() + b;                  // max_p relu(z_p + b) = relu(max_p z_p + b)
+		pmax = (RELU ? fmaxf(pmax, 0.f) : pmax) * inv_wscale;
+		const float psum = RELU ? ps.sum_all() * ssat : ps.sum_all() * inv_wscale + fP * b0;
+		const float second = a.ptype == DB_PT_SUM ? psum : __fdividef(psum, fP);
+		if (a.pooled && f < a.nf) {
+			const size_t o = (size_t)g * a.nf + f;
+			if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
+			else a.pooled[o] = WANT_MAX ? pmax : second;
+		}
+		if (a.scores) {
+			float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
+			part += __shfl_xor_sync(0xffffffffu, part, 8);
+			part += __shfl_xor_sync(0xffffffffu, part, 4);
+			part += __shfl_xor_sync(0xffffffffu, part, 2);
+			part += __shfl_xor_sync(0xffffffffu, part, 1);
+			if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
+		}
+		j += TC_EPI_SETS;
+		while (j >= k) { j -= k; ++t; }
+	}
+}
+
 #undef COMMA
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -461,7 +547,7 @@ scanpool_tc_kernel(const tc_args a)
 	const unsigned a_bytes = a.nsplit * KC * 2048u;
 	unsigned char* As = smem;                                    // [nsplit][KC][128][8] bf16
 	unsigned char* Es = smem + a_bytes;                          // [2][TC_ECHUNKS] 16-byte chunks
-	__shared__ __align__(8) uint64_t bar_a, e_full[2], e_empty[2], t_full[2], t_empty[2];
+	__shared__ __align__(8) uint64_t bar_a, bar_fin, e_full[2], e_empty[2], t_full[2], t_empty[2];
 	__shared__ uint32_t tmem_base_s;
 	__shared__ unsigned rows_s[2], blk_ok[2];
 	__shared__ int abort_s;
@@ -481,15 +567,32 @@ scanpool_tc_kernel(const tc_args a)
 	}
 	__syncthreads();
 	if (abort_s != 0) return;
-	// The CTA scans the flat rows [row_lo, row_hi) of its regions in tiles of 256.
+	// The CTA scans the flat rows [row_lo, row_hi) of its regions in tiles of 256 columns.
 	const unsigned row_lo = rows_s[0], row_hi = rows_s[1];
-	const unsigned ntile = (row_hi - row_lo + 255u) / 256u;
-	__syncthreads();
+	// Uniform batches (every region of this CTA P rows long, starting S rows after the one
+	// before: what equal-length sequences give) take region-aligned tiles: a tile starts at
+	// a region boundary and holds k whole regions, so no region straddles two tiles and
+	// the epilogue needs neither region bounds nor carried state.  Anything else (ragged
+	// lengths, gaps, rows past the scanned range) takes flat tiles of 256 rows.
+	const unsigned nreg = g_last - g_first;
+	const unsigned P0 = a.R[2 * g_first + 1] - a.R[2 * g_first];
+	const unsigned S0 = nreg > 1 ? a.R[2 * g_first + 2] - a.R[2 * g_first] : P0;
+	bool same = P0 >= 1u && P0 <= 256u && S0 >= P0 && S0 <= 256u && row_hi <= a.n;
+	for (unsigned i = threadIdx.x; same && i < nreg; i += TC_THREADS) {
+		const uint2 r = reinterpret_cast<const uint2*>(a.R)[g_first + i];
+		same = r.x == row_lo + i * S0 && r.y - r.x == P0;
+	}
+	const bool uni = __syncthreads_and(same) != 0;
+	const unsigned kreg = uni ? (256u - P0) / S0 + 1u : 0u;         // whole regions per tile
+	const unsigned tstep = uni ? kreg * S0 : 256u;                  // rows from one tile's first column to the next's
+	const unsigned ntile = uni ? (nreg + kreg - 1u) / kreg : (row_hi - row_lo + 255u) / 256u;
 	if (threadIdx.x == 0) {
-		mbar_init(&bar_a, 1);
+		mbar_init(&bar_a, 1); mbar_init(&bar_fin, 1);
 		for (int i = 0; i < 2; ++i) {
 			mbar_init(&e_full[i], TC_BUILD_WARPS); mbar_init(&e_empty[i], 1);
-			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 4 * TC_EPI_SETS);
+			// a tile is released by every warp that read it: all of them (flat tiles), or one
+			// per lane quarter and region (region-aligned tiles)
+			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], uni ? 4 * kreg : 4 * TC_EPI_SETS);
 		}
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
@@ -504,24 +607,24 @@ scanpool_tc_kernel(const tc_args a)
 		if (lane == 0) {
 			mbar_expect_tx(&bar_a, a_bytes);
 			bulk_g2s(As, reinterpret_cast<const unsigned char*>(a.Wt) + (size_t)tile * a_bytes, a_bytes, &bar_a);
-			bool ok = mbar_wait(&bar_a, 0, abort_flag);
+			bool ok = mbar_wait(&bar_a, 0, abort_flag, a.timeout);
 			const uint32_t a_addr = smem_u32(As), e_addr = smem_u32(Es);
 			const uint32_t desc_hi = (128u >> 4) | (1u << 14);                         // 8-row group stride 128 B; descriptor version 1
 			const uint32_t a_lo0 = ((a_addr >> 4) & 0x3fffu) | ((2048u >> 4) << 16);   // K-chunk stride 2048 B
 			for (unsigned t = 0; ok && t < ntile; ++t) {
 				const unsigned stage = t / TC_STAGE_TILES, st = stage & 1, tt = t % TC_STAGE_TILES;
 				if (tt == 0) {
-					ok = mbar_wait(&e_full[st], (stage >> 1) & 1, abort_flag);
+					ok = mbar_wait(&e_full[st], (stage >> 1) & 1, abort_flag, a.timeout);
 					if (!ok) break;
 				}
 				const unsigned slot = t & 1;
-				ok = mbar_wait(&t_empty[slot], ((t >> 1) & 1) ^ 1, abort_flag);
+				ok = mbar_wait(&t_empty[slot], ((t >> 1) & 1) ^ 1, abort_flag, a.timeout);
 				if (!ok) break;
 				tc_fence_after();
-				const unsigned ncols = min(256u, row_hi - (row_lo + t * 256u)), N = (ncols + 15u) & ~15u;
+				const unsigned ncols = min(256u, row_hi - (row_lo + t * tstep)), N = (ncols + 15u) & ~15u;
 				const uint32_t idesc = instr_desc(N, a.f16);
 				const uint32_t d = tmem_base + slot * 256u;
-				const uint32_t b0 = e_addr + st * (TC_ECHUNKS * 16) + tt * (256 * 16);
+				const uint32_t b0 = e_addr + st * (TC_ECHUNKS * 16) + tt * (tstep * 16);
 				// Descriptors differ only in the start-address field of their low word:
 				// the A tiles of all splits are contiguous (4096 bytes per MMA), B advances
 				// 64 bytes per MMA and restarts for each split.
@@ -539,6 +642,14 @@ scanpool_tc_kernel(const tc_args a)
 				// the stage may be rewritten once the MMAs that read it have finished
 				if (tt == TC_STAGE_TILES - 1 || t + 1 == ntile) umma_commit(&e_empty[st]);
 			}
+			// Leaving early (a wait ran out, or another role gave up): the tensor memory is
+			// released below, so every MMA issued so far has to finish first.  The commit
+			// arrives on bar_fin when they have; that wait is bounded like any other.
+			if (*abort_flag) {
+				umma_commit(&bar_fin);
+				const unsigned long long t0 = clock64();
+				while (!mbar_try_wait(&bar_fin, 0) && clock64() - t0 < a.timeout) __nanosleep(40);
+			}
 		}
 	} else if (warp < TC_EPI_WARP0) {
 		// ---------------------------------------------------------- E builders
@@ -548,10 +659,10 @@ scanpool_tc_kernel(const tc_args a)
 			const unsigned st = stage & 1;
 			// One thread waits (bounded) and publishes the outcome, so that all
 			// builder threads take the same path to the named barrier.
-			if (bt == 0) blk_ok[st] = mbar_wait(&e_empty[st], ((stage >> 1) & 1) ^ 1, abort_flag) ? 1u : 0u;
+			if (bt == 0) blk_ok[st] = mbar_wait(&e_empty[st], ((stage >> 1) & 1) ^ 1, abort_flag, a.timeout) ? 1u : 0u;
 			asm volatile("bar.sync 1, %0;" :: "n"(32 * TC_BUILD_WARPS) : "memory");
 			if (blk_ok[st] == 0) break;
-			const unsigned base_row = row_lo + stage * (TC_STAGE_TILES * 256u);
+			const unsigned base_row = row_lo + stage * (TC_STAGE_TILES * tstep);
 			uint4* E = reinterpret_cast<uint4*>(Es + (size_t)st * TC_ECHUNKS * 16);
 			// A thread encodes 16 consecutive chunks from 20 bytes fetched as aligned words;
 			// the words of its next 16 chunks are requested before it encodes these.
@@ -586,11 +697,13 @@ scanpool_tc_kernel(const tc_args a)
 			}
 			fence_async_smem();
 			__syncwarp();
-			if (lane == 0) mbar_arrive(&e_full[st]);
+			if (lane == 0 && !a.hold_operands) mbar_arrive(&e_full[st]);
 		}
 	} else {
 		// ------------------------------------------------------------ epilogue
-		#define TC_EPI(MX, SM, RL) tc_epilogue<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, g_last, row_lo, row_hi, warp, lane)
+		#define TC_EPI(MX, SM, RL) do { \
+			if (uni) tc_epilogue_uniform<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, nreg, P0, S0, kreg, warp, lane); \
+			else tc_epilogue<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, g_last, row_lo, row_hi, warp, lane); } while (0)
 		const bool wm = a.ptype == DB_PT_MAX || a.ptype == DB_PT_ALL, ws = a.ptype != DB_PT_MAX;
 		if (a.relu) { if (wm && ws) TC_EPI(true, true, true); else if (wm) TC_EPI(true, false, true); else TC_EPI(false, true, true); }
 		else        { if (wm && ws) TC_EPI(true, true, false); else if (wm) TC_EPI(true, false, false); else TC_EPI(false, true, false); }
@@ -657,6 +770,19 @@ static void tc_mode(int precision, unsigned& nsplit, unsigned& f16)
 	nsplit = precision == DB_TC_F16X2 ? 2u : precision == DB_TC_F16 ? 1u : (unsigned)precision;
 }
 
+// Test aid, per host thread: the deadline of the kernel's waits in clock cycles (0 = the
+// default) and whether the operand encoders withhold their "stage ready" signal, which
+// makes the issuer's first wait run out with no MMA in flight.  Nothing faults: the
+// kernel reports status 1 and returns.
+static thread_local unsigned long long g_tc_timeout = 0;
+static thread_local unsigned g_tc_hold_operands = 0;
+
+DB_EXPORT void db_scanpool_tc_debug(uint64_t timeout_clocks, int hold_operands)
+{
+	g_tc_timeout = timeout_clocks;
+	g_tc_hold_operands = hold_operands ? 1u : 0u;
+}
+
 DB_EXPORT size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int precision)
 {
 	DB_API_TRY_NODEV
@@ -713,6 +839,8 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int preci
 	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.m = m; a.KC = KC; a.nsplit = nsplit;
 	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu; a.f16 = f16;
 	a.maxabs = reinterpret_cast<const uint32_t*>(static_cast<const unsigned char*>(Wt) + (size_t)ntile * nsplit * KC * 2048);
+	a.timeout = g_tc_timeout ? g_tc_timeout : TC_TIMEOUT;
+	a.hold_operands = g_tc_hold_operands;
 	// Sequence chunks: about 8 waves of CTAs over the SMs (one CTA per SM), with the CTA
 	// count a multiple of the SM count so that the last wave is full; at least 64
 	// sequences per CTA.

@@ -287,8 +287,12 @@ class DeepBindNet(object):
             _, out = fused.scanpool_tc(tcw, X, R, self.pool, headW=self.view("W1").reshape(-1),
                                        headB=self.view("b1").view(-1), check=check, scores_out=out, status=status)
         else:
-            pooled, _ = fused.scanpool_tc(tcw, X, R, self.pool, check=check)
-            out, _, _ = self._head(self._test_dropout(pooled))
+            pooled, _ = fused.scanpool_tc(tcw, X, R, self.pool, check=check, status=status)
+            res, _, _ = self._head(self._test_dropout(pooled))
+            if out is not None:                 # the caller's buffer is honoured on every branch
+                out.copy_(res.view(out.shape))
+            else:
+                out = res
         if strand_max:
             out = out.view(-1, 2, self.I)
             out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
@@ -315,6 +319,10 @@ class DeepBindNet(object):
                         torch.empty(out_host.shape, dtype=torch.float32, device=self.dev))
         X, R, out = dev_bufs
         cur = torch.cuda.current_stream()
+        if tc:
+            if not hasattr(self, "_status"):
+                self._status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+            self._status.zero_()                # a failure of an earlier call must not outlive it
         if tc and self.hidden == 0 and self.nf == 16 * self.I and self.dropout_rate is None and R.shape[0] >= 8 * 4096:
             # Both transfers are pipelined with the scan, piece by piece: the bases of the next
             # piece go up on one side stream and the scores of the last piece come back on another
@@ -323,7 +331,6 @@ class DeepBindNet(object):
             if not hasattr(self, "_copy_stream"):
                 self._copy_stream = torch.cuda.Stream(device=self.dev)
                 self._up_stream = torch.cuda.Stream(device=self.dev)
-                self._status = torch.zeros(1, dtype=torch.int32, device=self.dev)
             R.copy_(R_host, non_blocking=True)
             nseq, npiece, npos = R.shape[0], 16, X.numel()
             cuts = [(nseq * c) // npiece for c in range(npiece + 1)]
@@ -346,19 +353,27 @@ class DeepBindNet(object):
                     out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
             self._copy_stream.synchronize()
             cur.synchronize()
-            if int(self._status.item()) != 0:
-                raise _lib.SmatException("scanpool_tc(...) raised an exception\nRuntimeError: tensor-core scan failed (status %d)"
-                                         % int(self._status.item()))
+            self._check_tc_status()
             return out_host
         X.copy_(X_host, non_blocking=True)
         R.copy_(R_host, non_blocking=True)
         if tc:
-            self.score_tc(X, R, check=False, out=out)
+            self.score_tc(X, R, check=False, out=out, status=self._status)
         else:
             self.score_chunked(X, R, out, chunk)
         out_host.copy_(out, non_blocking=True)
         cur.synchronize()
+        if tc:
+            self._check_tc_status()
         return out_host
+
+    def _check_tc_status(self):
+        """Raises if a tensor-core scan of the call just synchronised gave up (1 = a
+        bounded wait ran out, 3 = regions not in ascending order)."""
+        st = int(self._status.item())
+        if st != 0:
+            self._status.zero_()
+            raise _lib.SmatException("scanpool_tc(...) raised an exception\nRuntimeError: tensor-core scan failed (status %d)" % st)
 
     def capture_train_step(self, X, R, Y, dropmask=None, warmup=3, feed=None, prologue=None, steps=1):
         """Captures one Nesterov step on the static buffers X, R, Y, dropmask into a

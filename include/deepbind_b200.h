@@ -81,6 +81,13 @@ void        api_copy_to(const smat* M, void* host_dst, int32_t row_stride_bytes,
 void        api_fill_zero(smat* M);
 void        api_set_seed(uint64_t seed);            /* "seed=" backend option */
 uint64_t    api_launch_count(void);                 /* kernels launched so far by this thread; no counterpart */
+/* Scratch of the two-stage reductions (filter gradients, column sums).  It grows on
+ * demand with cudaMalloc and is never freed while the process lives, because a CUDA
+ * graph captured from a step keeps the address it saw.  It cannot grow while the
+ * stream is being captured: run the step once first, or reserve the largest size
+ * here.  No counterpart: the reference allocates per call from smat's heap. */
+void        db_reserve_scratch(size_t bytes);
+size_t      db_scratch_bytes(void);
 void        register_ext(void);                     /* extension.cpp:159-169; nothing to register here */
 void        api_autotune(void);                     /* kangaroo_smat.cpp (autotune.cu:91-113): no-op */
 
@@ -261,6 +268,12 @@ void db_scanpool_tc(const void* prepared, uint32_t m, uint32_t nf, int precision
                     const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion, int ptype,
                     float* pooled, const float* headW, const float* headB, uint32_t nmodel, float* scores,
                     int* status);
+/* Test aid (no counterpart): for later db_scanpool_tc launches of the calling thread,
+ * the deadline of the kernel's internal waits in clock cycles (0 = default, about 0.1 s)
+ * and, with hold_operands != 0, operand encoders that never signal "stage ready", so
+ * that the first wait of the MMA issuer runs out with nothing in flight.  The launch
+ * then reports status 1 and returns; nothing faults.  Call with (0, 0) to restore. */
+void db_scanpool_tc_debug(uint64_t timeout_clocks, int hold_operands);
 
 #ifdef __cplusplus
 }

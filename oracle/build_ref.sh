@@ -1,25 +1,33 @@
 #!/bin/sh
-# Compiles the reference's own motif-scan and pooling kernels, from the sources
-# where they lie in the reference tree, into oracle/_ref/libdeepbind_ref.so.
-# Nothing is copied: nvcc reads the reference files in place.  The two backward
-# sources include smat_cuda/launch_util.h, whose atomicAdd(double*) shim no longer
-# compiles; ref_shadow/ supplies a stand-in that comes first on the include path.
+# Compiles the reference's own kernels and launchers for this path, from the
+# sources where they lie in the reference tree, into oracle/_ref/libdeepbind_ref.so:
+# the motif scan and pooling kernels with their backward passes, input dropout
+# (kangaroo_smat), the update, mask, dropout and block-diagonal product launchers
+# (deepity_smat) and the element-wise launch rule (smat_cuda/launch_util.cpp).
+# Nothing is copied: nvcc reads the reference files in place.  ref_shadow/ comes
+# first on the include path and stands in for two headers: launch_util.h (its
+# atomicAdd(double*) shim no longer compiles) and cuda_context.h (the thread
+# context of libsmat's virtual machine, which is not built).
 #   usage: build_ref.sh <reference root> [nvcc]
 set -e
-REF="${1:-/root/reference}"
-NVCC="${2:-/usr/local/cuda/bin/nvcc}"
+REF="${1:-${DEEPBIND_REFERENCE_ROOT:?usage: build_ref.sh <reference root> [nvcc]}}"
+NVCC="${2:-${NVCC:-nvcc}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 L="$REF/code/libs"
 K="$L/kangaroo/kangaroo_smat"
+D="$L/deepity/deepity_smat"
 OUT="$HERE/_ref"
 mkdir -p "$OUT"
 FLAGS="-std=c++14 -O2 -use_fast_math -gencode arch=compute_100a,code=sm_100a -Xcompiler -fPIC -w
-       -I $HERE/ref_shadow -I $L/smat/src -I $K -include $L/smat/src/nvcc_preinclude.h"
-for f in corr1ord corr1ord_bprop poolrgn poolrgn_bprop; do
-	"$NVCC" $FLAGS -c "$K/$f.cu" -o "$OUT/$f.o"
+       -I $HERE/ref_shadow -I $L/smat/src -I $K -I $D -include $L/smat/src/nvcc_preinclude.h"
+OBJS=""
+for f in "$K/corr1ord.cu" "$K/corr1ord_bprop.cu" "$K/poolrgn.cu" "$K/poolrgn_bprop.cu" "$K/dropoutord.cu" \
+         "$D/gradstep.cu" "$D/madd_bcast.cu" "$D/maskout.cu" "$D/dropout.cu" "$D/blockwise_dot.cu" \
+         "$L/smat/src/smat_cuda/launch_util.cpp" "$HERE/ref_shim.cu"; do
+	o="$OUT/$(basename "$f" | sed 's/\.[a-z]*$//').o"
+	"$NVCC" $FLAGS -x cu -c "$f" -o "$o"
+	OBJS="$OBJS $o"
 done
-"$NVCC" $FLAGS -c "$HERE/ref_shim.cu" -o "$OUT/ref_shim.o"
-"$NVCC" -gencode arch=compute_100a,code=sm_100a -shared -o "$OUT/libdeepbind_ref.so" \
-	"$OUT/corr1ord.o" "$OUT/corr1ord_bprop.o" "$OUT/poolrgn.o" "$OUT/poolrgn_bprop.o" "$OUT/ref_shim.o"
-rm -f "$OUT"/*.o
+"$NVCC" -gencode arch=compute_100a,code=sm_100a -shared -o "$OUT/libdeepbind_ref.so" $OBJS -lcublas
+rm -f "${OUT:?}"/*.o
 echo "$OUT/libdeepbind_ref.so"

@@ -75,6 +75,32 @@ def test_predict_host_equals_device_scoring(cuda, nseq):
     assert torch.equal(out2, exact)
 
 
+@pytest.mark.parametrize("hidden,rate,I", [(32, 0.5, 3), (32, None, 2), (0, 0.25, 2)])
+def test_predict_host_tensor_core_with_a_dense_head(cuda, hidden, rate, I):
+    """Nets whose head is not the in-kernel linear one (hidden layer, test-mode dropout)
+    take the pooled-features branch of the tensor-core path; the caller's buffers must
+    still receive the scores."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m, nseq = 24, 500
+    net = DeepBindNet(synth.model_params(I, m, 7, "all", hidden=hidden), I, "all", loss="nll")
+    if rate is not None:
+        net.set_dropout(rate)
+    Xh, Rh = synth.uniform_batch(nseq, 60, m, seed=4)
+    X_host = torch.from_numpy(Xh).pin_memory(); R_host = torch.from_numpy(Rh.view(np.int32)).pin_memory()
+    out_host = torch.full((nseq, I), float("nan"), dtype=torch.float32).pin_memory()
+    net.prepare_tc("f16x2")
+    net.predict_host(X_host, R_host, out_host, tc=True)
+    exact = net.score(X_host.cuda(), R_host.cuda()).cpu()
+    assert torch.isfinite(out_host).all()
+    assert float((out_host - exact).abs().max()) <= 2e-5 * max(1.0, float(exact.abs().max()))
+    # a status left by a failed call does not poison the next one
+    net._status.fill_(3)
+    net.predict_host(X_host, R_host, out_host, tc=True)
+    assert float((out_host - exact).abs().max()) <= 2e-5 * max(1.0, float(exact.abs().max()))
+
+
 @pytest.mark.parametrize("I,pool,hidden,loss,rate,rc", [(1, "max", 0, "mse", None, False), (3, "all", 32, "nll", 0.3, False),
                                                         (2, "max", 32, "nll", None, True), (1, "avg", 0, "mse", 0.5, True)])
 def test_input_gradients_match_the_oracle_chain(cuda, orc, I, pool, hidden, loss, rate, rc):

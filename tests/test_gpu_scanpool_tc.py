@@ -102,6 +102,77 @@ def test_f16_prescale_covers_small_and_large_weights(cuda, orc, wscale):
         assert np.max(np.abs(got.cpu().numpy() - want)) <= tol * scale, precision
 
 
+@pytest.mark.parametrize("ptype", ["max", "all"])
+@pytest.mark.parametrize("m,L,nseq,gap", [(24, 101, 3000, 0),     # 124-row regions, two per tile: the benchmark's shape
+                                          (24, 40, 2500, 0),      # four 63-row regions per tile
+                                          (16, 20, 900, 0),       # seven 35-row regions per tile: a warp owns two regions of one tile
+                                          (24, 233, 700, 0),      # 256 rows: one region fills a tile
+                                          (24, 150, 900, 0),      # one region per tile, tiles 173 rows apart
+                                          (24, 234, 300, 0),      # 257 rows: too long for a tile, flat tiles take over
+                                          (8, 30, 1500, 5),       # equal regions with equal gaps between them
+                                          (24, 101, 5, 0), (24, 101, 1, 0)])
+def test_equal_length_batches_take_region_aligned_tiles(cuda, orc, ptype, m, L, nseq, gap):
+    """Equal-length batches run the kernel's region-aligned tiling (whole regions per
+    accumulator tile); the answers must be those of the oracle all the same, across many
+    tiles, operand stages and CTAs."""
+    from deepbind_b200 import fused
+    I = 8
+    nf = 16 * I
+    rng = np.random.default_rng(m * L + nseq)
+    P = L + m - 1
+    S = P + gap
+    X = np.full(nseq * S + m - 1 + gap, 255, np.uint8)
+    R = np.empty((nseq, 2), np.uint32)
+    for i in range(nseq):
+        R[i] = (i * S, i * S + P)
+        X[i * S + m - 1:i * S + P] = rng.integers(0, 4, L)
+    X[rng.random(X.size) < 0.01] = 254
+    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(f32)
+    b = rng.uniform(-0.1, 0.05, nf).astype(f32)
+    want, _ = orc.scanpool(W.astype(np.float64), b.astype(np.float64), True, X, R, ptype)
+    hW = rng.standard_normal(I * (32 if ptype == "all" else 16)).astype(f32); hB = rng.standard_normal(I).astype(f32)
+    for prec in (4, 1):
+        tcw = fused.TCWeights(dev(W), dev(b), prec)
+        got, scores = fused.scanpool_tc(tcw, dev(X), dev(R), ptype, headW=dev(hW), headB=dev(hB), want_pooled=True)
+        scale = np.abs(want).max()
+        assert np.max(np.abs(got.cpu().numpy() - want)) <= TOL[prec] * scale, prec
+        ws = (want.reshape(nseq, I, -1) * hW.reshape(I, -1)).sum(axis=2) + hB
+        assert np.max(np.abs(scores.cpu().numpy() - ws)) <= TOL[prec] * scale * np.abs(hW.reshape(I, -1)).sum(axis=1).max(), prec
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable(cuda):
+    """The kernel's waits are bounded.  With the operand encoders told never to announce
+    their stage (a test switch of the library) and a deadline of a millisecond, the MMA
+    issuer's first wait runs out with nothing in flight: the launch ends with status 1
+    (raised as an exception here) and the next ordinary launch gives correct results."""
+    import torch
+    from deepbind_b200 import _lib, fused, synth, SmatException
+    dll = _lib.load()
+    m, I = 24, 8
+    X, R = synth.uniform_batch(400, 101, m, seed=2)
+    p = synth.model_params(I, m, 3, "all")
+    tcw = fused.TCWeights(dev(p["Wscan"]), dev(p["bscan"]), "f16x2")
+    good, _ = fused.scanpool_tc(tcw, dev(X), dev(R), "all")
+    dll.db_scanpool_tc_debug(2_000_000, 1)
+    try:
+        with pytest.raises(SmatException, match="timed out"):
+            fused.scanpool_tc(tcw, dev(X), dev(R), "all")
+    finally:
+        dll.db_scanpool_tc_debug(0, 0)
+    torch.cuda.synchronize()
+    again, _ = fused.scanpool_tc(tcw, dev(X), dev(R), "all")
+    assert torch.equal(again, good)
+    Xr, Rr = synth.ragged_batch(300, 20, 150, m, seed=4)          # and the flat-tile path
+    dll.db_scanpool_tc_debug(2_000_000, 1)
+    try:
+        with pytest.raises(SmatException, match="timed out"):
+            fused.scanpool_tc(tcw, dev(Xr), dev(Rr), "all")
+    finally:
+        dll.db_scanpool_tc_debug(0, 0)
+    ok, _ = fused.scanpool_tc(tcw, dev(Xr), dev(Rr), "all")
+    assert bool(torch.isfinite(ok).all())
+
+
 def test_gaps_between_regions_and_tail_rows(cuda, orc):
     from deepbind_b200 import fused
     rng = np.random.default_rng(8)

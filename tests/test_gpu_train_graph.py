@@ -185,3 +185,55 @@ def test_several_steps_per_graph_equal_single_steps(cuda):
     torch.cuda.synchronize()
     assert torch.equal(net.P, eager.P) and torch.equal(net.mP, eager.mP)
     assert feed.counters.tolist() == [8, 0]
+
+
+def test_graph_survives_scratch_growth(cuda):
+    """A captured step keeps the scratch address it saw.  A later, larger call makes the
+    library take a bigger scratch buffer; the old one must stay alive, so replaying the
+    small graph afterwards still gives the eager result.  Growing inside a capture is refused."""
+    import torch
+    from deepbind_b200 import _lib, synth, SmatException
+    from deepbind_b200.model import DeepBindNet
+    dll = _lib.load()
+    m, B, I = 24, 64, 1
+    p = synth.model_params(I, m, 3, "all", hidden=32)
+    Xh, Rh = synth.uniform_batch(B, 60, m, seed=1)
+    g = synth.rng(2)
+    X = torch.from_numpy(Xh).cuda(); R = torch.from_numpy(Rh.view(np.int32)).cuda()
+    Y = torch.from_numpy(g.integers(0, 2, (B, I)).astype(np.float32)).cuda()
+    eager = DeepBindNet(p, I, "all", loss="nll"); eager.set_rates(0.02, 0.9)
+    for _ in range(3):
+        eager.train_step(X, R, Y)
+    net = DeepBindNet(p, I, "all", loss="nll"); net.set_rates(0.02, 0.9)
+    P0, m0 = net.P.clone(), net.mP.clone()
+    graph, _ = net.capture_train_step(X, R, Y)
+    net.P.copy_(P0); net.mP.copy_(m0)
+    graph.replay()
+    # a call that needs far more scratch than anything so far: column sums of 3 M rows
+    before = dll.db_scratch_bytes()
+    big = torch.ones((3_000_000, 64), dtype=torch.float32, device="cuda")
+    s = torch.empty(64, dtype=torch.float32, device="cuda")
+    dll.db_colsum(s.data_ptr(), big.data_ptr(), big.shape[0], 64)
+    torch.cuda.synchronize()
+    assert dll.db_scratch_bytes() > before and float(s[0]) == 3_000_000.0
+    del big
+    junk = torch.full((before // 4 + 1024,), float("nan"), device="cuda")      # would land on a freed scratch buffer
+    graph.replay(); graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(net.P, eager.P) and torch.equal(net.mP, eager.mP)
+    del junk
+    # growth while capturing is an error, not an allocation
+    need = dll.db_scratch_bytes() * 4
+    from deepbind_b200.smat import bind_stream
+    cg = torch.cuda.CUDAGraph()
+    msg = None
+    with torch.cuda.graph(cg):
+        bind_stream()
+        try:
+            dll.db_reserve_scratch(need)
+        except SmatException as e:
+            msg = str(e)
+    bind_stream()
+    assert msg is not None and "being captured" in msg
+    dll.db_reserve_scratch(need)
+    assert dll.db_scratch_bytes() >= need

@@ -28,6 +28,23 @@ def test_static_scratch_matches_allocating_entry_point_twice(cuda):
         assert torch.equal(got, want), "call %d differs" % call
         ref = A.double().sum(dim=0)
         assert float((got.double() - ref).abs().max()) <= 1e-5 * float(A.abs().sum(dim=0).max())
+    # No device memory is created by the static entry point: after the priming calls above
+    # (the address look-up happens in the first one), the driver's count of free bytes is the
+    # same before and after further calls, and so is torch's allocator (which the library
+    # never goes through).  The buffers are made before the first reading.
+    A = torch.from_numpy(rng.standard_normal((9000, 64)).astype(np.float32)).cuda()
+    got = torch.empty(64, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0 = torch.cuda.memory_reserved()
+    scratch0 = dll.db_scratch_bytes()
+    for _ in range(3):
+        dll.db_colsum_static(got.data_ptr(), A.data_ptr(), 9000, 64)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "db_colsum_static changed the device's free memory by %d bytes" % (free0 - free1)
+    assert torch.cuda.memory_reserved() == reserved0 and dll.db_scratch_bytes() == scratch0
+    assert float((got.double() - A.double().sum(dim=0)).abs().max()) <= 1e-5 * float(A.abs().sum(dim=0).max())
     # beyond the built-in array: a clear error, nothing launched
     big = torch.zeros((4, 8), dtype=torch.float32, device="cuda")
     out = torch.zeros(70000, dtype=torch.float32, device="cuda")
