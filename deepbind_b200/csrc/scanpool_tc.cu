@@ -49,6 +49,7 @@ static constexpr int TC_EPI_SETS = 4;      // epilogue warps per TMEM lane quart
 static constexpr int TC_BUILD_WARPS = 2;   // warps that encode the B operand (one stage ahead; a stage lasts 8 tiles)
 static constexpr int TC_EPI_WARP0 = 1 + TC_BUILD_WARPS;             // first epilogue warp
 static constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + 4 * TC_EPI_SETS);
+static_assert(TC_EPI_SETS == 4, "region-aligned tiles pair the four warps of a lane quarter with the two accumulator slots");
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // default deadline of a wait, clock cycles (about 0.1 s)
 
 struct tc_args {
@@ -453,10 +454,13 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	while (ok && g < g_last) ok = finish_region();
 }
 
-// Epilogue for region-aligned tiles (uniform batches): region i of the CTA lies in tile
-// i / k at column (i % k) * S and is P columns long.  The warps of a lane quarter take
-// the regions in turn as in tc_epilogue, but a region is always whole: wait for its
-// tile, reduce its P columns, hand the tile back, then write the outputs.
+// Epilogue for region-aligned tiles (uniform batches): tile t holds the CTA's regions
+// t*k .. t*k+k-1, region j of it at column j*S, P columns long.  The four warps of a
+// lane quarter split into two pairs: one follows the even tiles (accumulator slot 0),
+// the other the odd tiles (slot 1), so every warp sees every phase of the one slot it
+// waits on; the two warps of a pair take the regions of a tile alternately.  A region is
+// always whole: wait for the tile, reduce the P columns, write the outputs; the tile goes
+// back once the warp has read its last region of it.
 template <bool WANT_MAX, bool WANT_SUM, bool RELU>
 __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t tmem_base, uint64_t* t_full, uint64_t* t_empty,
                                                     volatile int* abort_flag, unsigned tile, unsigned g_first, unsigned nreg,
@@ -481,12 +485,12 @@ __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t t
 		hb = a.headB ? a.headB[model] : 0.f;
 	}
 	const float fP = (float)P;
-	const uint32_t lane_base = tmem_base + ((q4 * 32u) << 16);
-	unsigned t = 0, j = set;                            // tile and place in the tile of this warp's region
-	while (j >= k) { j -= k; ++t; }
+	const unsigned slot = set >> 1, sub = set & 1;      // this warp's accumulator slot and its place in the slot's pair
+	const unsigned ntile = (nreg + k - 1) / k;
+	const uint32_t slot_base = tmem_base + ((q4 * 32u) << 16) + slot * 256u;
 	pool_state ps;
-	for (unsigned i = set; i < nreg; i += TC_EPI_SETS) {
-		const unsigned slot = t & 1, par = (t >> 1) & 1;
+	unsigned par = 0;
+	for (unsigned t = slot; t < ntile; t += 2, par ^= 1) {
 		if (!__all_sync(0xffffffffu, mbar_try_wait(&t_full[slot], par))) {
 			unsigned okv = 0;
 			if (lane == 0) okv = mbar_wait(&t_full[slot], par, abort_flag, a.timeout) ? 1u : 0u;
@@ -494,46 +498,53 @@ __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t t
 			mbar_try_wait(&t_full[slot], par);          // completed: every lane observes the phase
 		}
 		tc_fence_after();
-		uint32_t ta = lane_base + slot * 256u + j * S;
-		ps.reset();
-		unsigned left = P;
-		float va[32];
-		#pragma unroll 1                                // P is loop-invariant: unrolled copies would only cost registers
-		while (left >= 32) {
-			tmem_ld32(ta, va);
-			tmem_ld_wait();
-			ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, cm, ca);
-			ta += 32; left -= 32;
+		const unsigned kt = min(k, nreg - t * k);       // regions in this tile
+		for (unsigned j = sub; j < kt; j += 2) {
+			uint32_t ta = slot_base + j * S;
+			ps.reset();
+			unsigned left = P;
+			float va[32];
+			#pragma unroll 1                            // P is loop-invariant: unrolled copies would only cost registers
+			while (left >= 32) {
+				tmem_ld32(ta, va);
+				tmem_ld_wait();
+				ps.add<WANT_MAX, WANT_SUM, RELU, 32>(va, cm, ca);
+				ta += 32; left -= 32;
+			}
+			if (left) {
+				load_piece(ta, left, va);
+				tmem_ld_wait();
+				ps.add_piece<WANT_MAX, WANT_SUM, RELU>(va, left, cm, ca);
+			}
+			if (j + 2 >= kt) {                          // last region of this warp in the tile: the tile goes back first
+				tc_fence_before();
+				__syncwarp();
+				if (lane == 0) mbar_arrive(&t_empty[slot]);
+			}
+			const unsigned g = g_first + t * k + j;
+			float pmax = ps.max_all() + b;              // max_p relu(z_p + b) = relu(max_p z_p + b)
+			pmax = (RELU ? fmaxf(pmax, 0.f) : pmax) * inv_wscale;
+			const float psum = RELU ? ps.sum_all() * ssat : ps.sum_all() * inv_wscale + fP * b0;
+			const float second = a.ptype == DB_PT_SUM ? psum : __fdividef(psum, fP);
+			if (a.pooled && f < a.nf) {
+				const size_t o = (size_t)g * a.nf + f;
+				if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
+				else a.pooled[o] = WANT_MAX ? pmax : second;
+			}
+			if (a.scores) {
+				float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
+				part += __shfl_xor_sync(0xffffffffu, part, 8);
+				part += __shfl_xor_sync(0xffffffffu, part, 4);
+				part += __shfl_xor_sync(0xffffffffu, part, 2);
+				part += __shfl_xor_sync(0xffffffffu, part, 1);
+				if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
+			}
 		}
-		if (left) {
-			load_piece(ta, left, va);
-			tmem_ld_wait();
-			ps.add_piece<WANT_MAX, WANT_SUM, RELU>(va, left, cm, ca);
+		if (sub >= kt) {                                // no region of this tile is ours: hand it back untouched
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive(&t_empty[slot]);
 		}
-		// the region's columns are in registers: the tile goes back before the outputs are written
-		tc_fence_before();
-		__syncwarp();
-		if (lane == 0) mbar_arrive(&t_empty[slot]);
-		const unsigned g = g_first + i;
-		float pmax = ps.max_all() + b;                  // max_p relu(z_p + b) = relu(max_p z_p + b)
-		pmax = (RELU ? fmaxf(pmax, 0.f) : pmax) * inv_wscale;
-		const float psum = RELU ? ps.sum_all() * ssat : ps.sum_all() * inv_wscale + fP * b0;
-		const float second = a.ptype == DB_PT_SUM ? psum : __fdividef(psum, fP);
-		if (a.pooled && f < a.nf) {
-			const size_t o = (size_t)g * a.nf + f;
-			if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
-			else a.pooled[o] = WANT_MAX ? pmax : second;
-		}
-		if (a.scores) {
-			float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
-			part += __shfl_xor_sync(0xffffffffu, part, 8);
-			part += __shfl_xor_sync(0xffffffffu, part, 4);
-			part += __shfl_xor_sync(0xffffffffu, part, 2);
-			part += __shfl_xor_sync(0xffffffffu, part, 1);
-			if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
-		}
-		j += TC_EPI_SETS;
-		while (j >= k) { j -= k; ++t; }
 	}
 }
 
@@ -590,9 +601,9 @@ scanpool_tc_kernel(const tc_args a)
 		mbar_init(&bar_a, 1); mbar_init(&bar_fin, 1);
 		for (int i = 0; i < 2; ++i) {
 			mbar_init(&e_full[i], TC_BUILD_WARPS); mbar_init(&e_empty[i], 1);
-			// a tile is released by every warp that read it: all of them (flat tiles), or one
-			// per lane quarter and region (region-aligned tiles)
-			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], uni ? 4 * kreg : 4 * TC_EPI_SETS);
+			// a tile is released by every warp that follows its slot: all of them (flat tiles),
+			// or the pair of each lane quarter bound to the slot (region-aligned tiles)
+			mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], uni ? 2 * TC_EPI_SETS : 4 * TC_EPI_SETS);
 		}
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
