@@ -124,6 +124,45 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
 	             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
 	             :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the accumulate flag fixed at compile time (the predicate folds away).
+template <bool ACC>
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
+{
+	if (ACC)
+		asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\t"
+		             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+		             :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+	else
+		asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, 0, 0;\n\t"
+		             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+		             :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+// All MMAs of one accumulator tile: per piece of the weights NK steps of K = 16.  The A
+// tiles of all pieces are contiguous (4096 bytes = 256 descriptor units per MMA), B
+// advances 64 bytes (4 units) per MMA and restarts for each piece.  NK > 0 unrolls the
+// steps with immediate offsets: the issuing thread is alone in its warp, so every
+// instruction it spends between two MMAs is latency the tensor pipe sits idle for.
+template <int NK>
+__device__ __forceinline__ void umma_tile(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, unsigned nsplit, unsigned nk)
+{
+	if (NK > 0) {
+		umma_f16<false>(d, adesc, bdesc, idesc);
+		#pragma unroll
+		for (int kk = 1; kk < NK; ++kk) umma_f16<true>(d, adesc + 256u * kk, bdesc + 4u * kk, idesc);
+		for (unsigned s = 1; s < nsplit; ++s) {
+			adesc += 256u * NK;
+			#pragma unroll
+			for (int kk = 0; kk < NK; ++kk) umma_f16<true>(d, adesc + 256u * kk, bdesc + 4u * kk, idesc);
+		}
+	} else {
+		unsigned acc = 0;
+		for (unsigned s = 0; s < nsplit; ++s)
+			for (unsigned kk = 0; kk < nk; ++kk) {
+				umma_bf16(d, adesc, bdesc + 4u * kk, idesc, acc);
+				acc = 1; adesc += 256u;
+			}
+	}
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
 	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
@@ -620,38 +659,41 @@ scanpool_tc_kernel(const tc_args a)
 			bulk_g2s(As, reinterpret_cast<const unsigned char*>(a.Wt) + (size_t)tile * a_bytes, a_bytes, &bar_a);
 			bool ok = mbar_wait(&bar_a, 0, abort_flag, a.timeout);
 			const uint32_t a_addr = smem_u32(As), e_addr = smem_u32(Es);
-			const uint32_t desc_hi = (128u >> 4) | (1u << 14);                         // 8-row group stride 128 B; descriptor version 1
-			const uint32_t a_lo0 = ((a_addr >> 4) & 0x3fffu) | ((2048u >> 4) << 16);   // K-chunk stride 2048 B
+			// Shared-memory descriptors (see smem_desc): 8-row group stride 128 B; A's K-chunk
+			// stride 2048 B, B's 32 B.  Only the start-address field (16-byte units) changes
+			// from MMA to MMA, and it never carries out of its 14 bits inside shared memory.
+			const uint64_t desc_hi = (uint64_t)((128u >> 4) | (1u << 14)) << 32;
+			const uint64_t adesc = desc_hi | (((a_addr >> 4) & 0x3fffu) | ((2048u >> 4) << 16));
+			const uint64_t bstage0 = desc_hi | (((e_addr >> 4) & 0x3fffu) | ((32u >> 4) << 16));
+			const uint32_t idesc_full = instr_desc(256u, a.f16);
+			// Running state instead of divisions per tile: place in the operand stage, stage
+			// buffer and its parity, parity of the accumulator slots, rows still to scan.
+			unsigned tt = 0, st = 0, par_e = 0, par_t = 1;
+			unsigned rows_left = row_hi - row_lo;
+			uint64_t bdesc = bstage0;
 			for (unsigned t = 0; ok && t < ntile; ++t) {
-				const unsigned stage = t / TC_STAGE_TILES, st = stage & 1, tt = t % TC_STAGE_TILES;
 				if (tt == 0) {
-					ok = mbar_wait(&e_full[st], (stage >> 1) & 1, abort_flag, a.timeout);
+					ok = mbar_wait(&e_full[st], par_e, abort_flag, a.timeout);
 					if (!ok) break;
 				}
 				const unsigned slot = t & 1;
-				ok = mbar_wait(&t_empty[slot], ((t >> 1) & 1) ^ 1, abort_flag, a.timeout);
+				ok = mbar_wait(&t_empty[slot], par_t, abort_flag, a.timeout);
 				if (!ok) break;
 				tc_fence_after();
-				const unsigned ncols = min(256u, row_hi - (row_lo + t * tstep)), N = (ncols + 15u) & ~15u;
-				const uint32_t idesc = instr_desc(N, a.f16);
+				const uint32_t idesc = rows_left >= 256u ? idesc_full : instr_desc((rows_left + 15u) & ~15u, a.f16);
 				const uint32_t d = tmem_base + slot * 256u;
-				const uint32_t b0 = e_addr + st * (TC_ECHUNKS * 16) + tt * (tstep * 16);
-				// Descriptors differ only in the start-address field of their low word:
-				// the A tiles of all splits are contiguous (4096 bytes per MMA), B advances
-				// 64 bytes per MMA and restarts for each split.
-				uint32_t a_lo = a_lo0;
-				const uint32_t b_lo0 = ((b0 >> 4) & 0x3fffu) | ((32u >> 4) << 16);
-				unsigned acc = 0;
-				for (unsigned s = 0; s < a.nsplit; ++s) {
-					uint32_t b_lo = b_lo0;
-					for (unsigned kk = 0; kk < NK; ++kk) {
-						umma_bf16(d, ((uint64_t)desc_hi << 32) | a_lo, ((uint64_t)desc_hi << 32) | b_lo, idesc, acc);
-						acc = 1; a_lo += 4096u >> 4; b_lo += 64u >> 4;
-					}
-				}
+				if (NK == 6) umma_tile<6>(d, adesc, bdesc, idesc, a.nsplit, NK);
+				else if (NK == 4) umma_tile<4>(d, adesc, bdesc, idesc, a.nsplit, NK);
+				else umma_tile<0>(d, adesc, bdesc, idesc, a.nsplit, NK);
 				umma_commit(&t_full[slot]);
-				// the stage may be rewritten once the MMAs that read it have finished
-				if (tt == TC_STAGE_TILES - 1 || t + 1 == ntile) umma_commit(&e_empty[st]);
+				++tt; bdesc += tstep;                       // the next tile's rows start tstep chunks further on
+				rows_left = rows_left > tstep ? rows_left - tstep : 0u;
+				par_t ^= slot;                              // both slots have been used once more after an odd tile
+				if (tt == TC_STAGE_TILES || t + 1 == ntile) {
+					umma_commit(&e_empty[st]);              // the stage may be rewritten once the MMAs that read it have finished
+					tt = 0; st ^= 1; par_e ^= (st == 0);
+					bdesc = bstage0 + st * (unsigned)TC_ECHUNKS;
+				}
 			}
 			// Leaving early (a wait ran out, or another role gave up): the tensor memory is
 			// released below, so every MMA issued so far has to finish first.  The commit
