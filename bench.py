@@ -6,7 +6,9 @@ independent DeepBind models (16 motifs x 24 taps each, max+mean pooling, linear
 head) score ``--nseq`` 101-nt sequences per GPU into a [nseq, nmodel] matrix.
 Synthetic, seeded inputs in the reference's batch layout.  One "step" is one
 pass over the whole batch.  With several GPUs every rank scores its own
-sequences (weak scaling) and the score shards are all-gathered with NCCL.
+sequences (weak scaling) and the score shards are all-gathered with NCCL; the same
+line also carries a strong-scaling leg (the 1,000,000 sequences of the named
+configuration split over the GPUs).
 
     python bench.py --gpus 1 --steps 5 --warmup 3
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
@@ -46,9 +48,13 @@ def parse():
     ap.add_argument("--nseq", type=int, default=1000000, help="sequences per GPU")
     ap.add_argument("--nmodel", type=int, default=512)
     ap.add_argument("--chunk", type=int, default=16384, help="sequences per launch of the FP32 variant")
-    ap.add_argument("--variant", default="f16x2", choices=["f16x2", "bf16x3", "bf16x2", "f16", "bf16", "f32"],
-                    help="arithmetic of the scan: 16-bit weight pieces on tcgen05 (f16x2, bf16x3 = fp32-grade) or FP32 lookup-add")
-    ap.add_argument("--gather-chunks", type=int, default=8, help="several GPUs: chunks of the shard whose all-gather overlaps the scan")
+    ap.add_argument("--variant", default="f16", choices=["f16x2", "bf16x3", "bf16x2", "f16", "bf16", "f32"],
+                    help="arithmetic of the scan: one 16-bit piece per weight on tcgen05 (f16 = TF32-grade, bf16), several pieces "
+                         "(f16x2, bf16x3 = fp32-grade), or the exact FP32 lookup-add kernel")
+    ap.add_argument("--gather-chunks", type=int, default=16, help="several GPUs: chunks of the shard whose all-gather overlaps the scan")
+    ap.add_argument("--nccl-max-ctas", type=int, default=8, help="several GPUs: CTAs NCCL may use per collective (0 = NCCL's default); "
+                                                                  "the scan wants every SM")
+    ap.add_argument("--no-variants", action="store_true", help="skip the short runs of the other arithmetic variants")
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the short runs of the other benchmark configurations")
@@ -59,7 +65,7 @@ def config(args, world):
     return {"workload": "many-model genome scan: %d models x %d motifs x %d taps, %d-nt uniform ACGT, max+avg pooling, "
                         "linear head, score matrix [nseq, %d]" % (args.nmodel, NMOTIF, M, L, args.nmodel),
             "nseq_per_gpu": args.nseq, "global_nseq": args.nseq * world, "nmodel": args.nmodel,
-            "parallelism": "sequences sharded over %d GPU(s), NCCL all-gather of score shards%s" % (world, " in %d chunks overlapped with the scan" % args.gather_chunks if world > 1 else ""),
+            "parallelism": "sequences sharded over %d GPU(s)%s" % (world, ", NCCL all-gather of the score shards in %d chunks overlapped with the scan" % args.gather_chunks if world > 1 else ""),
             "l2": "working set per step (input + score matrix) exceeds the 126 MB L2; no explicit flush"}
 
 
@@ -107,11 +113,13 @@ def reference_arm(args):
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config(args, world), "cpu_baseline": base,
+            "config": dict(config(args, world), variant=args.variant, tolerance_vs_fp32_reference=VARIANTS[args.variant][2]),
+            "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
             "note": "the reference has no CPU implementation of this path (CUDA-only); this arm times the CPU "
-                    "restatement used as the parity oracle"}
+                    "restatement used as the parity oracle (float32, exact) on a sample of %d of the workload's sequences "
+                    "per step: the cost per sequence does not depend on the batch size" % args.cpu_sample}
     print(json.dumps(line))
 
 
@@ -158,10 +166,11 @@ class ClockSampler(object):
 # ------------------------------------------------------------------ GPU arm
 VARIANTS = {
     # name: (16-bit pieces per weight, or None for the FP32 lookup-add kernel; dtype string; stated tolerance)
+    "f16":    (1, "f16 (one f16 piece per prescaled weight on tcgen05: 11-bit weights, exact one-hot operand, fp32 accumulate; "
+                  "<=5e-4 of the fp32 reference, inside the 2e-3 set for bf16/TF32 tensor-core paths)", 5e-4),
     "f16x2":  (2, "f16x2 (two f16 pieces per prescaled weight on tcgen05, fp32 accumulate; <=3e-6 of the fp32 reference)", 3e-6),
     "bf16x3": (3, "bf16x3 (three bf16 pieces per weight on tcgen05, fp32 accumulate; <=1e-5 of the fp32 reference)", 1e-5),
     "bf16x2": (2, "bf16x2 (two bf16 pieces per weight, fp32 accumulate; <=1e-5)", 1e-5),
-    "f16":    (1, "f16 (prescaled weights, fp32 accumulate; <=5e-4)", 5e-4),
     "bf16":   (1, "bf16 (fp32 accumulate; <=2e-3)", 2e-3),
     "f32":    (None, "f32 (lookup-add, bit-exact pooling)", 0.0),
 }
@@ -178,10 +187,12 @@ def _events_ms(fn, reps):
     return e0.elapsed_time(e1) / reps
 
 
+PEAKS_FILE = os.environ.get("DEEPBIND_PEAKS_FILE", os.path.join(ROOT, "MEASURED_PEAKS.json"))
+
+
 def _read_peaks():
-    """Peaks measured on this pool's GPUs (written beside this file by the harness); {} if absent."""
-    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    return json.load(open(pk)) if os.path.exists(pk) else {}
+    """Measured peaks of the GPU pool (copy bandwidth, cuBLAS bf16 burst and sustained); {} if the file is absent."""
+    return json.load(open(PEAKS_FILE)) if os.path.exists(PEAKS_FILE) else {}
 
 
 def side_workloads(dev, with_cpu):
@@ -361,6 +372,73 @@ def calibration_sharded(dev, rank, world):
             "parallelism": "models dealt round robin to %d GPUs, no gradient exchange; all-gather of the loss vector" % world}
 
 
+def reference_kernels(dev):
+    """Device time of the reference's own kernels (compiled for sm_100a from the reference
+    sources into the checker library, launched with the reference's geometry) beside the
+    drop-in operators and the fused kernel on the same inputs: 16384 x 101 nt, 16 filters x
+    24 taps, Z = 130 MB (larger than L2).  None when the checker library is not built."""
+    import ctypes
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libdeepbind_ref.so")
+    if not os.path.exists(so):
+        return None
+    ref = ctypes.CDLL(so)
+    from deepbind_b200 import fused, synth, smat as sm, kangaroo_smat as ks
+    m, nf, nseq = 24, 16, 16384
+    Xh, Rh = synth.uniform_batch(nseq, 101, m, seed=1)
+    rng = np.random.default_rng(2)
+    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(np.float32)
+    b = rng.uniform(-0.1, 0, nf).astype(np.float32)
+    n = Xh.size - m + 1
+    tX = torch.zeros(Xh.size + 256, dtype=torch.uint8, device=dev)      # the reference's loader reads whole words past the end
+    tX[:Xh.size] = torch.from_numpy(Xh).to(dev)
+    tX = tX[:Xh.size]
+    tW, tb = torch.from_numpy(W).to(dev), torch.from_numpy(b).to(dev)
+    tR = torch.from_numpy(Rh.view(np.int32)).to(dev)
+    Z = torch.zeros((Xh.size, nf), dtype=torch.float32, device=dev)
+    Pt = torch.empty((nseq, 2 * nf), dtype=torch.float32, device=dev)
+    At = torch.empty((nseq, nf), dtype=torch.int32, device=dev)
+    sW, sX, sR = sm.asarray(W), sm.asarray(Xh), sm.asarray(Rh)
+    sZ = sm.sarray(Z, np.float32)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    F32, ALL = 9, 3
+
+    def t_of(fn, reps=10):
+        for _ in range(3):
+            fn()
+        return _events_ms(fn, reps)
+    t = {}
+    t["ref_corr1ord"] = t_of(lambda: ref.ref_corr1ord(F32, P(tW), m, nf, P(tX), n, P(Z)))
+    t["new_corr1ord"] = t_of(lambda: ks.corr1ord(sW, sX, sZ, 4))
+    t["ref_poolrgn_all"] = t_of(lambda: ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), ALL))
+    t["new_poolrgn_all"] = t_of(lambda: ks.poolrgn(sZ, sR, "all", want_argmax=True))
+    t["new_fused_scan_bias_relu_pool"] = t_of(lambda: fused.scanpool(tW, tb, sX.tensor.view(-1), tR, "all", want_argmax=True))
+    dZ = torch.randn((Xh.size, nf), dtype=torch.float32, device=dev)
+    dW = torch.zeros((4 * m, nf), dtype=torch.float32, device=dev)
+    sdZ, sdW = sm.sarray(dZ, np.float32), sm.sarray(dW, np.float32)
+    t["ref_corr1ord_bprop_W"] = t_of(lambda: ref.ref_corr1ord_bprop_W(F32, P(dW), m, nf, P(tX), n, P(dZ)))
+    t["new_corr1ord_bprop_W"] = t_of(lambda: ks.corr1ord_bprop_W(sdW, sX, sdZ, 4))
+    dP = torch.randn((nseq, 2 * nf), dtype=torch.float32, device=dev)
+    sdP, sAt = sm.sarray(dP, np.float32), sm.sarray(At, np.uint32)
+    ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), ALL)
+    t["ref_poolrgn_bprop_all"] = t_of(lambda: ref.ref_poolrgn_bprop(F32, P(dZ), nf, P(tR), nseq, 2, P(dP), P(At), ALL))
+    t["new_poolrgn_bprop_all"] = t_of(lambda: ks.poolrgn_bprop(sdZ, sR, sdP, sAt, "all"))
+    dXs = sm.zeros((Xh.size, 4), np.float32)
+    t["new_corr1ord_bprop_X"] = t_of(lambda: ks.corr1ord_bprop_X(dXs, sW, sdZ, 4), reps=3)
+    zbytes = float(Xh.size) * nf * 4
+    peaks = _read_peaks()
+    hbm = (peaks.get("hbm_gbs") or 6650.0) * 1e9
+    out = {"unit": "ms per call", "case": "16384 x 101 nt, 16 filters x 24 taps; Z [npos, 16] f32 = %.0f MB" % (zbytes / 1e6),
+           "ms": t, "z_bytes": zbytes,
+           "scan_pool_chain_speedup": (t["ref_corr1ord"] + t["ref_poolrgn_all"]) / t["new_fused_scan_bias_relu_pool"],
+           "frac_hbm": {"new_poolrgn_all": zbytes / (t["new_poolrgn_all"] * 1e-3) / hbm,
+                        "new_poolrgn_bprop_all": zbytes / (t["new_poolrgn_bprop_all"] * 1e-3) / hbm,
+                        "new_corr1ord": zbytes / (t["new_corr1ord"] * 1e-3) / hbm},
+           "note": "reference kernels recompiled for sm_100a with their own launch geometry; frac_hbm = npos*nf*4 bytes per pass "
+                   "over the measured copy bandwidth (%s)" % ("measured" if "hbm_gbs" in peaks else "fallback 6650 GB/s")}
+    return out
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -370,6 +448,7 @@ def main():
     import torch.distributed as dist
     from deepbind_b200 import _lib, fused, shard, synth
     from deepbind_b200.model import DeepBindNet
+    from deepbind_b200.predict import ShardedScorer
 
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -379,7 +458,17 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        opts = None
+        if args.nccl_max_ctas > 0:
+            # The scan keeps one CTA on every SM (all of the SM's tensor memory); NCCL's copy CTAs take
+            # SMs away from it while a chunk is gathered, so they are held to a few.
+            try:
+                opts = dist.ProcessGroupNCCL.Options()
+                opts.config.max_ctas = args.nccl_max_ctas
+                opts.config.min_ctas = min(args.nccl_max_ctas, 4)
+            except (AttributeError, TypeError):
+                opts = None
+        dist.init_process_group("nccl", device_id=dev, **({"pg_options": opts} if opts is not None else {}))
     dll = _lib.load()
 
     I, nseq = args.nmodel, args.nseq
@@ -391,44 +480,31 @@ def main():
     R_host = torch.from_numpy(Rh.view(np.int32)).pin_memory()
     out_host = torch.empty((nseq, I), dtype=torch.float32).pin_memory()
     X = X_host.to(dev); R = R_host.to(dev)
-    scores = torch.empty((nseq, I), dtype=torch.float32, device=dev)
-    gathered = torch.empty((nseq * world, I), dtype=torch.float32, device=dev) if world > 1 else None
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
     if nsplit:
         net.prepare_tc(args.variant)
+    scorer = ShardedScorer(net, nseq, group=None, nchunk=args.gather_chunks if world > 1 else 1)
+    scores = scorer.scores
+    status = scorer.status
+    gathered = scorer.gathered
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def score():
-        if nsplit:
-            net.score_tc(X, R, check=False, out=scores, status=status)
-        else:
-            net.score_chunked(X, R, scores, args.chunk)
-
-    # Several GPUs: the shard is scored in chunks and every chunk's all-gather (NCCL, its own
-    # stream) runs while the next chunk is scored; `gathered_chunks` is chunk-major, rank-major
-    # inside a chunk (shard.gathered_rows gives the flat order).
-    gathered_chunks = None
-    if world > 1 and nsplit:
-        gathered_chunks = [gathered[world * lo:world * hi] for lo, hi in
-                           (shard.shard_range(nseq, c, args.gather_chunks) for c in range(args.gather_chunks))]
-
-    def score_rows(lo, hi):
-        net.score_tc(X, R[lo:hi], check=False, out=scores[lo:hi], status=status)
-
     def step():
-        if gathered_chunks is not None:
-            shard.chunked_gather(score_rows, scores, gathered_chunks)
+        if nsplit:
+            scorer.run(X, R)                 # several GPUs: every chunk's all-gather overlaps the scan of the next
             return
-        score()
+        net.score_chunked(X, R, scores, args.chunk)
         if world > 1:
             dist.all_gather_into_tensor(gathered, scores)
 
     def e2e_step():
-        net.predict_host(X_host, R_host, out_host, args.chunk, dev_bufs=(X, R, scores), tc=bool(nsplit))
+        if nsplit:
+            scorer.run_host(X_host, R_host, out_host, dev_bufs=(X, R, scores))
+            return
+        net.predict_host(X_host, R_host, out_host, args.chunk, dev_bufs=(X, R, scores), tc=False)
         if world > 1:
             dist.all_gather_into_tensor(gathered, scores)
 
@@ -453,10 +529,18 @@ def main():
     ms = timed(step, args.steps)
     launches = int(dll.api_launch_count() - l0)
     clocks = sampler.stop() if sampler else None
+    if nsplit:
+        scorer.check()
+    # outside the timed region: every rank's rows of the gathered matrix are its own scores, and all ranks
+    # hold the same matrix
+    gather_verified = scorer.verify() if (world > 1 and nsplit) else None
     e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
-    if int(status.item()) != 0:
-        raise SystemExit("tensor-core scan reported status %d" % int(status.item()))
+    if nsplit:
+        scorer.check()
+    e2e_matches = None
+    if nsplit:
+        e2e_matches = bool(torch.equal(out_host[:4096], scores[:4096].cpu()))
 
     # dominant kernel alone: CUDA events on the launch stream around the scan launches of one step
     peaks = _read_peaks()
@@ -464,31 +548,31 @@ def main():
     barrier()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = min(args.steps, 3)
-    if nsplit:
+    alg_bytes = nseq * ((L + M - 1) + I * 4)
+
+    def tc_kernel_ms(reps):
         k0.record()
         for _ in range(reps):
             net.score_tc(X, R, check=False, out=scores, status=status)
         k1.record(); k1.synchronize()
-        kernel_ms = k0.elapsed_time(k1) / reps
-        dense_flop = 2.0 * 4 * M * (L + M - 1) * NMOTIF * I * nseq          # 2*K*rows*filters
-        exec_flop = nsplit * dense_flop
-        peak = peaks.get("bf16_tflops_sustained") or 1400.0
-        src = "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS bf16 GEMM run back to back under the power cap)" \
-            if "bf16_tflops_sustained" in peaks else "fallback 1.4 PFLOP/s sustained"
+        return k0.elapsed_time(k1) / reps
+    dense_flop = 2.0 * 4 * M * (L + M - 1) * NMOTIF * I * nseq              # 2*K*rows*filters
+    peak = peaks.get("bf16_tflops_sustained") or 1400.0
+    src = "measured: cuBLAS bf16 GEMM run back to back under the power cap (sustained)" \
+        if "bf16_tflops_sustained" in peaks else "fallback 1.4 PFLOP/s sustained"
+    if nsplit:
+        kernel_ms = tc_kernel_ms(reps)
+        alg = dense_flop / (kernel_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": "scanpool_tc_kernel (tcgen05 kind::f16, %s: %d piece(s) per weight)" % (args.variant, nsplit),
-                    "achieved": exec_flop / (kernel_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
-                    "frac": exec_flop / (kernel_ms * 1e-3) / 1e12 / peak, "peak_source": src,
-                    "flops_counted": "executed tensor flops = %d x dense-equivalent 2*K*rows*filters (K=96); the pieces are what "
-                                     "fp32-grade results cost on 16-bit tensor cores (f16 and bf16 run at the same rate)" % nsplit,
-                    "dense_equiv_tflops": dense_flop / (kernel_ms * 1e-3) / 1e12,
-                    "burst_peak": peaks.get("bf16_tflops"),
-                    # ncu, one launch of 1,000,000 sequences x 512 models: dram__bytes_read.sum 277 MB +
-                    # dram__bytes_write.sum 2.01 GB (profiles/scanpool_tc_f16x2_genome_scan.md); it grows with the
-                    # sequence count once the score matrix exceeds L2, so it is scaled from that capture
-                    "traffic": (2.287e9 * nseq / 1e6) if (I == 512 and nseq >= 250000) else None,
-                    "traffic_unit": "bytes per launch (algorithmic: %d)" % (nseq * ((L + M - 1) + I * 4)),
-                    "ms_per_launch": kernel_ms,
-                    "hbm_gbs_algorithmic": (nseq * ((L + M - 1) + I * 4)) / (kernel_ms * 1e-3) / 1e9}
+                    "achieved": alg, "peak": peak, "unit": "TFLOP/s", "frac": alg / peak, "peak_source": src,
+                    "flops_counted": "algorithmic: dense-equivalent 2*K*rows*filters per sequence (K=96, 124 rows, 8192 filters at "
+                                     "512 models); frac_executed counts every 16-bit piece of a weight the tensor cores multiply",
+                    "frac_executed": nsplit * alg / peak, "executed_tflops": nsplit * alg,
+                    "burst_peak": peaks.get("bf16_tflops"), "frac_of_burst": alg / peaks["bf16_tflops"] if peaks.get("bf16_tflops") else None,
+                    "traffic": None,
+                    "traffic_unit": "bytes per launch; algorithmic: %d.  One single-pass ncu capture of this launch (dram bytes read + "
+                                    "written) gave 1.05 x the algorithmic bytes: the summary of the kernel's profile records it" % alg_bytes,
+                    "ms_per_launch": kernel_ms, "hbm_gbs_algorithmic": alg_bytes / (kernel_ms * 1e-3) / 1e9}
     else:
         Wd, bd = net.view("Wscan"), net.view("bscan").view(-1)
         nchunk = (nseq + args.chunk - 1) // args.chunk
@@ -503,12 +587,61 @@ def main():
         kernel_ms = ktime / (min(reps, 2) * nchunk)
         adds = adds_per_seq(I) * nseq / nchunk                    # per launch, on average (the last chunk may be short)
         sm_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz") or 1965.0
-        lut_peak = prop.multi_processor_count * 32 * sm_max * 1e6
-        roofline = {"bound": "smem-lookup", "kernel": "scanpool_fwd_kernel<24> (FP32 lookup-add)",
-                    "achieved": adds / (kernel_ms * 1e-3) / 1e12, "peak": lut_peak / 1e12, "unit": "Tadd/s",
-                    "frac": adds / (kernel_ms * 1e-3) / lut_peak,
-                    "peak_source": "SMs x 32 table operands/clk x max SM clock (shared-memory return path, one 4-byte operand "
-                                   "per add); FP32 add issue would be 4x this", "traffic": None, "ms_per_launch": kernel_ms}
+        issue_peak = prop.multi_processor_count * 128 * sm_max * 1e6
+        roofline = {"bound": "fp32-add-issue", "kernel": "scanpool_fwd_kernel<24> (FP32 lookup-add)",
+                    "achieved": adds / (kernel_ms * 1e-3) / 1e12, "peak": issue_peak / 1e12, "unit": "Tadd/s",
+                    "frac": adds / (kernel_ms * 1e-3) / issue_peak,
+                    "frac_smem_operand_ceiling": adds / (kernel_ms * 1e-3) / (issue_peak / 4),
+                    "peak_source": "SMs x 128 lanes x max SM clock (one FP32 add per lane and clock); the kernel fetches one 4-byte table "
+                                   "operand per add from shared memory, whose return path allows a quarter of that",
+                    "traffic": None, "ms_per_launch": kernel_ms}
+
+    # the other arithmetic variants of the same workload, device-resident, a few launches each
+    variants = None
+    if world == 1 and nsplit and not args.no_variants:
+        variants = {args.variant: {"value": nseq / (kernel_ms * 1e-3), "unit": UNIT, "tolerance_vs_fp32_reference": tol,
+                                   "frac_algorithmic": roofline["frac"], "frac_executed": roofline["frac_executed"]}}
+        for name in ("f16x2", "bf16", "f16", "bf16x3"):
+            if name in variants:
+                continue
+            ns, _, vtol = VARIANTS[name]
+            net.prepare_tc(name)
+            for _ in range(2):
+                net.score_tc(X, R, check=False, out=scores, status=status)
+            vms = tc_kernel_ms(2)
+            valg = dense_flop / (vms * 1e-3) / 1e12
+            variants[name] = {"value": nseq / (vms * 1e-3), "unit": UNIT, "tolerance_vs_fp32_reference": vtol,
+                              "frac_algorithmic": valg / peak, "frac_executed": ns * valg / peak}
+        net.prepare_tc(args.variant)
+        nsmall = min(nseq, 65536)                                # the exact FP32 kernel on a slice of the same batch
+        f32_out = torch.empty((nsmall, I), dtype=torch.float32, device=dev)
+        net.score_chunked(X, R[:nsmall], f32_out, args.chunk)
+        fms = _events_ms(lambda: net.score_chunked(X, R[:nsmall], f32_out, args.chunk), 1)
+        variants["f32"] = {"value": nsmall / (fms * 1e-3), "unit": UNIT, "tolerance_vs_fp32_reference": 0.0,
+                           "sample": "%d of the batch's sequences" % nsmall,
+                           "Tadd_per_s": adds_per_seq(I) * nsmall / (fms * 1e-3) / 1e12}
+        # the scores of the headline variant against the exact kernel's on the same rows
+        net.score_tc(X, R[:nsmall], check=True, out=scores[:nsmall])
+        variants[args.variant]["max_abs_err_vs_f32_over_max_abs_score"] = \
+            float((scores[:nsmall] - f32_out).abs().max() / f32_out.abs().max())
+        del f32_out
+
+    # strong scaling: the named configuration's 1,000,000 sequences split over the GPUs, gathered on every rank
+    strong = None
+    if world > 1 and nsplit:
+        gn = 1000000
+        lo, hi = shard.shard_range(gn, rank, world)
+        n_s = gn // world                                        # equal shards (the remainder, < world sequences, is left out)
+        sc = ShardedScorer(net, n_s, group=None, nchunk=max(1, min(args.gather_chunks, n_s // 8192)))
+        Xs, Rs = X, R[:n_s]
+        for _ in range(3):
+            sc.run(Xs, Rs)
+        ms_s = timed(lambda: sc.run(Xs, Rs), args.steps)
+        sc.check()
+        strong = {"global_nseq": n_s * world, "nseq_per_gpu": n_s, "value": n_s * world * args.steps / (ms_s * 1e-3), "unit": UNIT,
+                  "ms_per_step": ms_s / args.steps, "gather_verified": sc.verify(), "chunks": sc.nchunk,
+                  "note": "strong scaling: total work fixed at the configuration's 1,000,000 sequences; every rank ends with all scores"}
+        del sc
 
     calib = calibration_sharded(dev, rank, world) if (world > 1 and not args.no_side) else None
     if rank == 0:
@@ -519,14 +652,24 @@ def main():
                 "clocks": clocks,
                 "e2e": {"value": nseq * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": int(X_host.numel() + R_host.numel() * 4),
-                        "d2h_bytes_per_step": int(out_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
+                        "d2h_bytes_per_step": int(out_host.numel() * 4), "ms_per_step": ms_e2e / args.steps,
+                        "host_scores_match_device": e2e_matches},
                 "gpu_launches": launches, "roofline": roofline}
+        if gather_verified is not None:
+            line["gather_verified"] = gather_verified
+        if variants is not None:
+            line["variants"] = variants
+        if strong is not None:
+            line["strong_scaling"] = strong
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_run(args, args.cpu_sample, 1, 1)
         if world == 1 and not args.no_side:
-            del X, R, scores, X_host, R_host, out_host
+            del X, R, scores, X_host, R_host, out_host, scorer
             torch.cuda.empty_cache()
             line["other_configs"] = side_workloads(dev, not args.no_cpu_baseline)
+            rk = reference_kernels(dev)
+            if rk is not None:
+                line["other_configs"]["reference_kernels"] = rk
         if calib is not None:
             line["other_configs"] = {"calibration": calib}
         print(json.dumps(line))

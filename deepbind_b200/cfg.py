@@ -218,6 +218,21 @@ def plan(layers):
     return ModelPlan(layers[0], layers[3].pool, drops[0] if drops else None, fulls, "nll" if m.group(3) else "mse")
 
 
+def select_instances(params, ids, ninst):
+    """The parameter blocks of the instances ``ids`` cut out of blocks holding ``ninst``
+    instances: filter and bias columns are instance-major (corr1ord.py:57-58), dense
+    weights stack the instances on rows (full.py:57)."""
+    out = {}
+    for k, w in params.items():
+        if k in ("W1", "W2"):
+            out[k] = w.reshape(ninst, -1, w.shape[-1])[ids].reshape(-1, w.shape[-1])
+        elif w.ndim == 2:
+            out[k] = w.reshape(w.shape[0], ninst, -1)[:, ids].reshape(w.shape[0], -1)
+        else:
+            out[k] = w.reshape(ninst, -1)[ids].reshape(-1)
+    return out
+
+
 def _draw(value, rng, n, drawn, key):
     if isinstance(value, paramdef):
         drawn[key] = value.sample(rng, n)
@@ -225,7 +240,7 @@ def _draw(value, rng, n, drawn, key):
     return np.full(n, 0.0 if value is None else value, np.float64)
 
 
-def instantiate(layers, ninst=1, seed=0, motif_len=None, device=None):
+def instantiate(layers, ninst=1, seed=0, motif_len=None, device=None, instances=None):
     """Builds ``ninst`` independent instances of the model in one DeepBindNet, one
     hyper-parameter draw per instance (as hypertrain trains its samples side by
     side, code/libs/deepity/deepity/hypertrain.py:560-580).
@@ -233,7 +248,12 @@ def instantiate(layers, ninst=1, seed=0, motif_len=None, device=None):
     Returns (net, drawn): ``drawn`` maps "<layer index>.<layer>.<argument>" to the [ninst]
     values drawn from a range.  Weights start as N(0, init_scale[instance]^2),
     biases at ``init_mu`` (sgd.py:331-352).  ``motif_len`` overrides the filter
-    length the way the training scripts set ``fsize`` after loading."""
+    length the way the training scripts set ``fsize`` after loading.
+
+    ``instances`` (a list of instance numbers < ninst): the net holds only those
+    instances, with exactly the hyper-parameters and initial weights they have in the
+    full net -- what a rank needs when the instances are dealt to several GPUs
+    (hpsearch.py:316-330); ``drawn`` still lists all ``ninst`` draws."""
     from .model import DeepBindNet
     p = plan(layers)
     rng = np.random.default_rng(seed)
@@ -263,10 +283,17 @@ def instantiate(layers, ninst=1, seed=0, motif_len=None, device=None):
         params["W2"] = (rng.standard_normal((I, H, 1)) * f_init[1][:, None, None]).reshape(I * H, 1)
         params["b2"] = np.full(I, float(p.fulls[1].init_bias))
     params = {k: v.astype(np.float32) for k, v in params.items()}
-    net = DeepBindNet(params, I, p.pool, loss=p.loss, device=device)
     decay = {"Wscan": scan_decay, "W1": f_decay[0]}
     if H:
         decay["W2"] = f_decay[1]
+    if instances is not None:
+        ids = np.asarray(list(instances), np.int64)
+        assert ids.size > 0 and ids.min() >= 0 and ids.max() < I, "instances must be numbers below ninst"
+        params = select_instances(params, ids, I)
+        decay = {k: v[ids] for k, v in decay.items()}
+        scan_init, f_init, rate = scan_init[ids], [v[ids] for v in f_init], rate[ids]
+        I = int(ids.size)
+    net = DeepBindNet(params, I, p.pool, loss=p.loss, device=device)
     net.set_decay(decay)
     net.set_dropout(rate)
     net.hparams = {"dropout": rate, "decay": decay, "init": {"Wscan": scan_init, "W1": f_init[0]}}

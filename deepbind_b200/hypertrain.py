@@ -15,14 +15,32 @@ kangaroo/train.py:74-172) around the device-side trainer.
 
 The bookkeeping is host code; every model evaluation runs through the same
 kernels as training and scoring.
+
+Several GPUs (one process per GPU, ``group`` = a torch.distributed process group, or
+the default group with ``group="world"``): the hyper-parameter samples -- and the
+trials of the final training -- are dealt to the ranks round robin, as the reference
+hands them to one worker process per device (hpsearch.py:316-330,376); every rank
+trains its own instances on the full data with no gradient exchange, and only the
+validation records (host objects) and the winning trial's parameters are exchanged.
 """
 import json
 import os
 
 import numpy as np
 
-from . import cfg
+from . import cfg, shard
 from .trainer import Trainer
+
+
+def _group(group):
+    """``"world"`` -> the default process group (None for torch.distributed calls)."""
+    return None if (isinstance(group, str) and group == "world") else group
+
+
+def _rank_world(group):
+    if group is None:
+        return 0, 1
+    return shard.rank_world(_group(group))
 
 
 # --------------------------------------------------------------------- metrics
@@ -77,12 +95,16 @@ def _validate(net, seqs, Y, batch=4096):
 
 
 def calibrate(layers, trainer_spec, seqs, Y, ncalib=30, nfold=3, seed=0, motif_len=None, shuffle_seed=1234, outdir=None,
-              allfolds=True):
+              allfolds=True, group=None):
     """Draws ``ncalib`` hyper-parameter samples, trains each on every fold, validates
     every checkpoint.  Returns a list of records
     ``{"sample", "step", "hparams", "metric", "value", "folds"}`` (one per sample and
     checkpoint; ``value`` is the mean of the folds' validation metric) and the best
-    record.  With ``outdir`` the records are also written to ``calib.all.json``."""
+    record.  With ``outdir`` the records are also written to ``calib.all.json``
+    (by rank 0).  With ``group`` the samples are dealt to the group's ranks; every rank
+    returns the records of all samples."""
+    rank, world = _rank_world(group)
+    mine = shard.shard_models(ncalib, rank, world)          # this rank's samples
     seqs = list(seqs)
     Y = np.asarray(Y, np.float32).reshape(len(seqs), -1)
     perm = np.random.default_rng(shuffle_seed).permutation(len(seqs))       # always the same shuffle, hence the same folds
@@ -92,27 +114,32 @@ def calibrate(layers, trainer_spec, seqs, Y, ncalib=30, nfold=3, seed=0, motif_l
     for fold in range(nfold if allfolds else 1):
         A, B = split_folds(len(seqs), fold, nfold - 1)
         # the same draws for every fold: a sample is a hyper-parameter set, evaluated nfold times
-        net, drawn = cfg.instantiate(layers, ninst=ncalib, seed=seed, motif_len=motif_len)
-        tr = Trainer(net, trainer_spec, seed=seed)
+        # (a rank left without a sample still draws, for the record of hyper-parameters)
+        keep = (mine or [0]) if world > 1 else None
+        net, drawn = cfg.instantiate(layers, ninst=ncalib, seed=seed, motif_len=motif_len, instances=keep)
+        tr = Trainer(net, trainer_spec, seed=seed, ninst=ncalib, instances=keep)
         metric, _ = _metric_of(net, net.loss)
         vseqs, vY = ([seqs[i] for i in B], Y[B]) if len(B) else ([seqs[i] for i in A], Y[A])
 
         def on_checkpoint(step, trainer):
             Z = _validate(trainer.net, vseqs, vY)
-            for s in range(ncalib):
-                v = calc_auc(Z[:, s], vY[:, 0]) if metric == "auc" else pearson(Z[:, s], vY[:, 0])
+            for col, s in enumerate(mine):
+                v = calc_auc(Z[:, col], vY[:, 0]) if metric == "auc" else pearson(Z[:, col], vY[:, 0])
                 rec = records.setdefault((s, step), {"sample": s, "step": step, "metric": metric, "folds": []})
                 rec["folds"].append(v)
-        tr.fit([seqs[i] for i in A], Y[A], on_checkpoint=on_checkpoint)
+        if mine:
+            tr.fit([seqs[i] for i in A], Y[A], on_checkpoint=on_checkpoint)
         hp = {k: np.asarray(v).tolist() for k, v in drawn.items()}
-        hp["trainer.rate"], hp["trainer.momentum"] = tr.rate.tolist(), tr.momentum.tolist()
+        hp["trainer.rate"], hp["trainer.momentum"] = tr.rate_all.tolist(), tr.momentum_all.tolist()
+    if world > 1:                                            # every rank learns every sample's records
+        records = {k: v for part in shard.gather_objects(records, _group(group)) for k, v in part.items()}
     out = []
     for (s, step), rec in sorted(records.items()):
         rec["hparams"] = {k: v[s] for k, v in hp.items()}
         rec["value"] = float(np.mean(rec["folds"])) if not np.any(np.isnan(rec["folds"])) else float("nan")
         out.append(rec)
     best = get_best_sample(out, wantmax=True)
-    if outdir:
+    if outdir and rank == 0:
         os.makedirs(outdir, exist_ok=True)
         with open(os.path.join(outdir, "calib.all.json"), "w") as f:
             json.dump({"records": out, "best": best}, f, indent=1)
@@ -141,20 +168,48 @@ def _fix(layers, hparams, ntrial):
     return fixed_layers
 
 
-def train_final(layers, trainer_spec, best, seqs, Y, ntrial=3, seed=0, motif_len=None):
+def train_final(layers, trainer_spec, best, seqs, Y, ntrial=3, seed=0, motif_len=None, group=None):
     """Trains ``ntrial`` instances with the best record's hyper-parameters and step
     count on all the data; returns (net, index of the trial with the best training
-    metric, metrics [ntrial])."""
+    metric, metrics [ntrial]).  With ``group`` the trials are dealt to the ranks
+    (a rank without a trial idles); the returned net then holds this rank's trials
+    only (None on a rank without any), ``metrics`` all trials', and
+    :func:`best_trial_params` hands the winner's parameters to every rank."""
     import copy
+    rank, world = _rank_world(group)
+    mine = shard.shard_models(ntrial, rank, world)
     spec = copy.copy(trainer_spec)
     spec.rate, spec.momentum = best["hparams"]["trainer.rate"], best["hparams"]["trainer.momentum"]
     spec.max_steps, spec.checkpoints = int(best["step"]), 1
-    net, _ = cfg.instantiate(_fix(layers, best["hparams"], ntrial), ninst=ntrial, seed=seed + 1, motif_len=motif_len)
-    Trainer(net, spec, seed=seed).fit(list(seqs), Y)
     Yv = np.asarray(Y, np.float32).reshape(len(seqs), -1)
-    Z = _validate(net, list(seqs), Yv)
-    vals = np.asarray([calc_auc(Z[:, t], Yv[:, 0]) if net.loss == "nll" else pearson(Z[:, t], Yv[:, 0]) for t in range(ntrial)])
+    net, local = None, []
+    if mine:
+        net, _ = cfg.instantiate(_fix(layers, best["hparams"], ntrial), ninst=ntrial, seed=seed + 1, motif_len=motif_len,
+                                 instances=mine if world > 1 else None)
+        Trainer(net, spec, seed=seed, ninst=ntrial, instances=mine if world > 1 else None).fit(list(seqs), Y)
+        Z = _validate(net, list(seqs), Yv)
+        local = [calc_auc(Z[:, c], Yv[:, 0]) if net.loss == "nll" else pearson(Z[:, c], Yv[:, 0]) for c in range(len(mine))]
+    vals = np.asarray(shard.deal_back(shard.gather_objects(local, _group(group)), ntrial, world) if world > 1 else local)
     return net, int(np.nanargmax(vals)), vals
+
+
+def best_trial_params(net, best_trial, ntrial, group=None):
+    """The parameter blocks (numpy, one instance) of trial ``best_trial`` of a final
+    training whose ``ntrial`` trials were dealt to the ranks of ``group``: the owning
+    rank cuts them out of its net, every rank receives them."""
+    rank, world = _rank_world(group)
+    owner = best_trial % world
+    params = None
+    if rank == owner:
+        col = shard.shard_models(ntrial, rank, world).index(best_trial) if world > 1 else best_trial
+        params = cfg.select_instances(net.params_numpy("P"), np.asarray([col]), net.I)
+    if world > 1:
+        import torch.distributed as dist
+        box = [params]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(_group(group), owner) if _group(group) is not None else owner,
+                                   group=_group(group))
+        params = box[0]
+    return params
 
 
 # ------------------------------------------------------------------ persistence

@@ -308,11 +308,15 @@ class DeepBindNet(object):
             out[s:e].copy_(self.score(X, R[s:e]))
         return out
 
-    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False):
+    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False, npiece=16, on_piece=None):
         """The call a user makes for scoring: ordinal batch in (pinned) host
         memory -> scores in (pinned) host memory.  Mirrors what
         kangaroo.predict does per batch (code/libs/kangaroo/kangaroo/predict.py:168-176):
-        upload X and R, run the model, read the scores back."""
+        upload X and R, run the model, read the scores back.  On the pipelined
+        tensor-core path the batch is cut into ``npiece`` pieces of regions
+        (``shard.shard_range(nseq, c, npiece)``) and ``on_piece(lo, hi)``, if given, is
+        called right after piece [lo, hi) was enqueued on the current stream (a caller
+        with several GPUs starts that piece's all-gather there)."""
         if dev_bufs is None:
             dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.dev),
                         torch.empty(R_host.shape, dtype=torch.int32, device=self.dev),
@@ -332,8 +336,10 @@ class DeepBindNet(object):
                 self._copy_stream = torch.cuda.Stream(device=self.dev)
                 self._up_stream = torch.cuda.Stream(device=self.dev)
             R.copy_(R_host, non_blocking=True)
-            nseq, npiece, npos = R.shape[0], 16, X.numel()
-            cuts = [(nseq * c) // npiece for c in range(npiece + 1)]
+            from .shard import shard_range
+            nseq, npos = R.shape[0], X.numel()
+            npiece = max(1, min(int(npiece), nseq))
+            cuts = [shard_range(nseq, c, npiece)[0] for c in range(npiece)] + [nseq]
             first = [int(R_host[lo, 0]) for lo in cuts[:-1]] + [npos]          # regions ascend (the batch layout)
             self._up_stream.wait_stream(cur)
             ups = []
@@ -346,6 +352,8 @@ class DeepBindNet(object):
                 lo, hi = cuts[c], cuts[c + 1]
                 cur.wait_event(ups[c])
                 self.score_tc(X, R[lo:hi], check=False, out=out[lo:hi], status=self._status)
+                if on_piece is not None:
+                    on_piece(lo, hi)
                 done = torch.cuda.Event()
                 done.record(cur)
                 self._copy_stream.wait_event(done)

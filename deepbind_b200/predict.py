@@ -12,7 +12,7 @@ uploads the characters.
 import numpy as np
 import torch
 
-from . import fused
+from . import fused, shard
 from . import kangaroo_smat as ks
 from . import smat as sm
 
@@ -21,7 +21,7 @@ def _score(net, X, R, reverse_complement):
     return net.score(X, R, strand_max=bool(reverse_complement))
 
 
-def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps=False, max_windows=1 << 21):
+def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps=False, max_windows=1 << 21, group=None):
     """Scores the sequence strings ``seqs`` with every model of ``net``.
 
     Returns a dict of CUDA tensors [nseq, I]: ``direct``; with ``scan`` = window
@@ -29,8 +29,26 @@ def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps
     (a list of [nwindow_b, I] tensors, one per sequence) if ``want_pmaps``.  With
     ``reverse_complement`` both strands are scored and the larger score is kept,
     the forward strand on ties (predict.py:145-164).  Sequences are processed in
-    groups of at most ``max_windows`` windows."""
+    groups of at most ``max_windows`` windows.
+
+    ``group`` (a torch.distributed process group, or "world" for the default one; one
+    process per GPU, every rank holding the same ``net`` and ``seqs``): the sequences
+    are split into contiguous shards, one per rank, as the reference splits its work
+    over one process per device (predict.py:484-492); every rank scores its shard and
+    the score shards are all-gathered, so every rank returns all rows.  ``pmaps`` stay
+    those of the rank's own shard (``shard.shard_range(len(seqs), rank, world)``)."""
     seqs = list(seqs)
+    if group is not None:
+        grp = None if (isinstance(group, str) and group == "world") else group
+        rank, world = shard.rank_world(grp)
+        if world > 1:
+            lo, hi = shard.shard_range(len(seqs), rank, world)
+            mine = predict(net, seqs[lo:hi], scan, stride, reverse_complement, want_pmaps, max_windows) if hi > lo else \
+                {k: torch.empty((0, net.I), dtype=torch.float32, device=net.dev) for k in (("direct", "max", "avg", "sum") if scan else ("direct",))}
+            out = {k: shard.gather_scores(v.contiguous(), grp) for k, v in mine.items() if k != "pmaps"}
+            if want_pmaps and scan:
+                out["pmaps"] = mine.get("pmaps", [])
+            return out
     pad = net.m - 1
     dev = net.dev
     X, R = fused.build_batch(seqs, pad, reverse_complement, device=dev)
@@ -144,3 +162,90 @@ def mutation_maps(net, seqs, reverse_complement=False):
         Zs.append(z0)
         maps.append(d)
     return np.stack(Zs), maps
+
+
+class ShardedScorer(object):
+    """Scores a device-resident ordinal batch over the ranks of a process group with the
+    tensor-core scan: every rank scans its own regions in ``nchunk`` pieces and each
+    piece's all-gather (NCCL, asynchronous) runs while the next piece is scanned, so
+    that every rank ends up with the scores of all ranks' sequences -- the scoring path
+    of kangaroo.predict fanned out over the devices of one box (predict.py:484-492)
+    with the gather overlapped.  Buffers are allocated once and reused by every call.
+
+    ``net``: a DeepBindNet with the in-kernel linear head (no hidden layer) whose
+    tensor-core weights were prepared; ``nseq``: regions per rank (the same on every
+    rank)."""
+
+    def __init__(self, net, nseq, group=None, nchunk=8):
+        import torch.distributed as dist
+        self.net, self.group, self.nseq = net, group, int(nseq)
+        self.rank, self.world = shard.rank_world(group)
+        self.nchunk = max(1, min(int(nchunk), self.nseq))
+        self.scores = torch.empty((self.nseq, net.I), dtype=torch.float32, device=net.dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=net.dev)
+        self.gathered = self.chunks = None
+        if self.world > 1:
+            self.gathered = torch.empty((self.nseq * self.world, net.I), dtype=torch.float32, device=net.dev)
+            self.chunks = [self.gathered[self.world * lo:self.world * hi] for lo, hi in
+                           (shard.shard_range(self.nseq, c, self.nchunk) for c in range(self.nchunk))]
+        self._dist = dist
+
+    def run(self, X, R):
+        """Enqueues scan and gathers of this rank's batch (X ordinal buffer, R its
+        ``nseq`` regions); returns the local score shard.  Call :meth:`check` after a
+        synchronisation to learn of a failed scan."""
+        net = self.net
+
+        def rows(lo, hi):
+            net.score_tc(X, R[lo:hi], check=False, out=self.scores[lo:hi], status=self.status)
+        if self.world == 1:
+            rows(0, self.nseq)
+        else:
+            shard.chunked_gather(rows, self.scores, self.chunks, self.group)
+        return self.scores
+
+    def run_host(self, X_host, R_host, out_host, dev_bufs=None):
+        """The same from (pinned) host buffers to (pinned) host scores of this rank's
+        shard: upload, scan and read-back are pipelined piece by piece
+        (``DeepBindNet.predict_host``) and, with several ranks, every piece's all-gather
+        starts as soon as the piece is enqueued.  Synchronises before it returns."""
+        if dev_bufs is None:
+            dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.net.dev),
+                        torch.empty(R_host.shape, dtype=torch.int32, device=self.net.dev), self.scores)
+        works = []
+
+        def gather_piece(lo, hi):
+            c = len(works)
+            works.append(self._dist.all_gather_into_tensor(self.chunks[c], self.scores[lo:hi], group=self.group, async_op=True))
+        self.net.predict_host(X_host, R_host, out_host, dev_bufs=(dev_bufs[0], dev_bufs[1], self.scores), tc=True,
+                              npiece=self.nchunk, on_piece=gather_piece if self.world > 1 else None)
+        if self.world > 1 and not works:         # a batch too small for the pipelined path: gather it now
+            shard.chunked_gather(lambda lo, hi: None, self.scores, self.chunks, self.group)
+        for w in works:
+            w.wait()
+        if self.world > 1:
+            torch.cuda.current_stream().synchronize()
+        return out_host
+
+    def check(self):
+        st = int(self.status.item())
+        if st:
+            self.status.zero_()
+            raise RuntimeError("tensor-core scan failed on rank %d (status %d)" % (self.rank, st))
+
+    def all_scores(self):
+        """[world * nseq, I] in rank-major row order (a copy out of the chunk buffers)."""
+        if self.world == 1:
+            return self.scores
+        return shard.gathered_rows(self.chunks, self.nseq, self.world)
+
+    def verify(self):
+        """After a synchronised :meth:`run`: this rank's rows of the gathered matrix
+        equal its own shard, and all ranks hold the same matrix (checksums agree)."""
+        if self.world == 1:
+            return True
+        full = self.all_scores()
+        own = torch.equal(full[self.rank * self.nseq:(self.rank + 1) * self.nseq], self.scores)
+        ok = torch.tensor([1 if own else 0], device=self.scores.device)
+        self._dist.all_reduce(ok, op=self._dist.ReduceOp.MIN, group=self.group)
+        return bool(ok.item()) and shard.checksum_agrees(full, self.group)

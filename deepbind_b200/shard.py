@@ -10,6 +10,14 @@ import torch
 import torch.distributed as dist
 
 
+def rank_world(group=None):
+    """(rank, world) of this process in ``group``; (0, 1) when no process group is in
+    use (``group`` None and torch.distributed not initialised)."""
+    if group is None and not (dist.is_available() and dist.is_initialized()):
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
 def shard_range(n, rank, world):
     """Contiguous shard [lo, hi) of n units for `rank`; sizes differ by at most one."""
     base, rem = divmod(n, world)
@@ -83,3 +91,40 @@ def gather_scores(local, group=None):
     out = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(out, padded.contiguous(), group=group)
     return torch.cat([o[:s] for o, s in zip(out, sizes)])
+
+
+def gather_objects(local, group=None):
+    """Every rank's picklable ``local`` object -> the list of all of them, rank order,
+    on every rank (host-side bookkeeping such as calibration records)."""
+    rank, world = rank_world(group)
+    if world == 1:
+        return [local]
+    out = [None] * world
+    dist.all_gather_object(out, local, group=group)
+    return out
+
+
+def deal_back(per_rank_lists, n, world):
+    """Inverse of :func:`shard_models` for results: ``per_rank_lists[r][i]`` belongs to
+    unit ``r + i * world``; returns the n results in unit order."""
+    out = [None] * n
+    for r, lst in enumerate(per_rank_lists):
+        ids = shard_models(n, r, world)
+        assert len(lst) == len(ids), "rank %d returned %d results for %d units" % (r, len(lst), len(ids))
+        for i, v in zip(ids, lst):
+            out[i] = v
+    return out
+
+
+def checksum_agrees(t, group=None):
+    """True on every rank iff all ranks hold the same float tensor ``t`` up to its
+    float64 sum and sum of squares (a cheap check that a gather gave every rank the
+    same matrix; outside any timed region)."""
+    rank, world = rank_world(group)
+    c = torch.stack([t.double().sum(), (t.double() ** 2).sum()])
+    if world == 1:
+        return True
+    lo, hi = c.clone(), c.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+    return bool(torch.equal(lo, hi))

@@ -36,12 +36,19 @@ def _per_model(value, rng, I):
 
 
 class Trainer(object):
-    def __init__(self, net, spec=None, seed=0):
-        """``spec``: a :class:`deepbind_b200.cfg.sgd` (ranges are drawn once per model)."""
+    def __init__(self, net, spec=None, seed=0, ninst=None, instances=None):
+        """``spec``: a :class:`deepbind_b200.cfg.sgd` (ranges are drawn once per model).
+        ``ninst``/``instances``: the net holds the instances ``instances`` of a set of
+        ``ninst`` (cfg.instantiate); rates are drawn for all and those kept, so that an
+        instance trains the same on whichever GPU it lands."""
         self.net, self.spec = net, spec or cfg.sgd()
         rng = np.random.default_rng(seed)
-        self.rate = _per_model(self.spec.rate, rng, net.I)
-        self.momentum = _per_model(self.spec.momentum, rng, net.I)
+        n = int(ninst) if ninst is not None else net.I
+        self.rate_all = _per_model(self.spec.rate, rng, n)
+        self.momentum_all = _per_model(self.spec.momentum, rng, n)
+        ids = np.arange(n) if instances is None else np.asarray(list(instances), np.int64)
+        assert len(ids) == net.I, "the net must hold exactly the listed instances"
+        self.rate, self.momentum = self.rate_all[ids], self.momentum_all[ids]
         net.set_rates(self.rate, self.momentum)
         self.step = 0
         self.history = []                 # (step, mean training loss [I]) at every checkpoint

@@ -109,3 +109,106 @@ def test_chunked_gather_overlap_order(tmp_path):
     for r in range(2):
         assert np.array_equal(np.load(os.path.join(str(tmp_path), "chunked_%d.npy" % r)), want)
         assert np.load(os.path.join(str(tmp_path), "calls_%d.npy" % r)).tolist() == [[0, 4], [4, 7], [7, 10]]
+
+
+def _predict_worker(rank, world, port, out_dir):
+    """predict(..., group=) on two gloo ranks; the device kernels are replaced by the CPU
+    oracle (batch assembly and scoring), so what runs here is the package's sharding and
+    gathering of the sequence list."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from deepbind_b200 import fused, predict as P, synth
+    from oracle import oracle as orc
+    orc.set_num_threads(1)
+    m, I = 16, 2
+    params = synth.model_params(I, m, 6, "max")
+
+    def build_batch(seqs, padding, reverse_complement=False, device=None):
+        X, R = orc.asbatch(seqs, padding, reverse_complement)
+        return torch.from_numpy(X), torch.from_numpy(R.view(np.int32))
+
+    class Net(object):
+        dev = torch.device("cpu")
+
+        def __init__(self):
+            self.I, self.m = I, m
+
+        def score(self, X, R, strand_max=False):
+            return torch.from_numpy(orc.score_net(params, X.numpy(), R.numpy().view(np.uint32), "max", I, strand_max=strand_max))
+    fused.build_batch = build_batch
+    rng = np.random.default_rng(3)
+    seqs = ["".join(rng.choice(list("ACGT"), size=int(n))) for n in rng.integers(16, 50, size=11)]     # 11 = 6 + 5 per rank
+    for rc in (False, True):
+        got = P.predict(Net(), seqs, reverse_complement=rc, group="world")
+        np.save(os.path.join(out_dir, "predict_%d_%d.npy" % (rank, rc)), got["direct"].numpy())
+    # one rank without any sequence still takes part in the gather
+    got = P.predict(Net(), seqs[:1], group=dist.group.WORLD)
+    np.save(os.path.join(out_dir, "predict_one_%d.npy" % rank), got["direct"].numpy())
+    dist.destroy_process_group()
+
+
+def test_predict_shards_sequences_over_the_group(tmp_path):
+    sys.path.insert(0, ROOT)
+    from deepbind_b200 import synth
+    from oracle import oracle as orc
+    port = 33500 + (os.getpid() % 2000)
+    mp.spawn(_predict_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    rng = np.random.default_rng(3)
+    seqs = ["".join(rng.choice(list("ACGT"), size=int(n))) for n in rng.integers(16, 50, size=11)]
+    params = synth.model_params(2, 16, 6, "max")
+    for rc in (False, True):
+        X, R = orc.asbatch(seqs, 15, rc)
+        want = orc.score_net(params, X, R, "max", 2, strand_max=rc)
+        for r in range(2):
+            got = np.load(os.path.join(str(tmp_path), "predict_%d_%d.npy" % (r, rc)))
+            assert got.shape == (11, 2)
+            np.testing.assert_array_equal(got, want)
+    X, R = orc.asbatch(seqs[:1], 15, False)
+    for r in range(2):
+        np.testing.assert_array_equal(np.load(os.path.join(str(tmp_path), "predict_one_%d.npy" % r)),
+                                      orc.score_net(params, X, R, "max", 2))
+
+
+def _records_worker(rank, world, port, out_dir):
+    """The exchange of calibrate(..., group=): samples dealt round robin, per-rank record
+    dictionaries merged on every rank, per-trial values dealt back into trial order."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from deepbind_b200 import shard
+    ncalib = 7
+    mine = shard.shard_models(ncalib, rank, world)
+    records = {(s, step): {"sample": s, "step": step, "folds": [s + 0.1 * step]} for s in mine for step in (10, 20)}
+    merged = {k: v for part in shard.gather_objects(records) for k, v in part.items()}
+    vals = shard.deal_back(shard.gather_objects([10.0 * s for s in mine]), ncalib, world)
+    ok = shard.checksum_agrees(torch.arange(5.0) + 1) and not shard.checksum_agrees(torch.arange(5.0) + rank)
+    np.save(os.path.join(out_dir, "records_%d.npy" % rank), np.array([sorted(merged) == [(s, st) for s in range(ncalib) for st in (10, 20)],
+                                                                      vals == [10.0 * s for s in range(ncalib)], ok]))
+    dist.destroy_process_group()
+
+
+def test_calibration_records_are_merged_on_every_rank(tmp_path):
+    port = 35500 + (os.getpid() % 2000)
+    mp.spawn(_records_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert np.load(os.path.join(str(tmp_path), "records_%d.npy" % r)).all()
+
+
+def test_instances_cut_out_of_a_parameter_set():
+    """cfg.select_instances keeps exactly the columns / row blocks of the chosen instances."""
+    sys.path.insert(0, ROOT)
+    from deepbind_b200 import cfg
+    I, F, m, H = 5, 16, 4, 3
+    rng = np.random.default_rng(0)
+    p = {"Wscan": rng.standard_normal((4 * m, I * F)), "bscan": rng.standard_normal(I * F),
+         "W1": rng.standard_normal((I * 2 * F, H)), "b1": rng.standard_normal(I * H),
+         "W2": rng.standard_normal((I * H, 1)), "b2": rng.standard_normal(I)}
+    ids = np.array([3, 0])
+    q = cfg.select_instances(p, ids, I)
+    assert np.array_equal(q["Wscan"], np.concatenate([p["Wscan"][:, 3 * F:4 * F], p["Wscan"][:, :F]], axis=1))
+    assert np.array_equal(q["bscan"], np.concatenate([p["bscan"][3 * F:4 * F], p["bscan"][:F]]))
+    assert np.array_equal(q["W1"], np.concatenate([p["W1"][3 * 2 * F:4 * 2 * F], p["W1"][:2 * F]]))
+    assert np.array_equal(q["b1"], np.concatenate([p["b1"][3 * H:4 * H], p["b1"][:H]]))
+    assert np.array_equal(q["W2"], np.concatenate([p["W2"][3 * H:4 * H], p["W2"][:H]]))
+    assert np.array_equal(q["b2"], p["b2"][[3, 0]])

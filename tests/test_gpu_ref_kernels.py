@@ -135,63 +135,3 @@ def test_reference_backward_equals_oracle_and_fused_kernel(ref, orc, ptype):
     gW, gb = fused.scanpool_bprop(m, nf, dev(X), tR, ptype, dev(dP), fA, fM)
     assert float((gW - dW).abs().max()) <= 1e-5 * scale
     assert float((gb - dZ.sum(dim=0)).abs().max()) <= 1e-5 * scale
-
-
-def test_speed_against_the_reference_kernels(ref, capsys):
-    """Device time of the reference's kernels (its own launch geometry, recompiled for
-    sm_100a) beside the drop-in operators and the fused kernel, same inputs, CUDA
-    events.  Z is 130 MB (larger than L2), so the unfused operators are HBM-bound.
-    Run with `pytest -s` to see the table."""
-    import torch
-    from deepbind_b200 import fused, synth, smat as sm, kangaroo_smat as ks
-    m, nf, nseq = 24, 16, 16384
-    X, R = synth.uniform_batch(nseq, 101, m, seed=1)
-    rng = np.random.default_rng(2)
-    W = (rng.standard_normal((4 * m, nf)) * 0.05).astype(np.float32)
-    b = rng.uniform(-0.1, 0, nf).astype(np.float32)
-    n = X.size - m + 1
-    tW, tX, tR, tb = dev(W), dev(X, pad=256), dev(R), dev(b)
-    Z = torch.zeros((X.size, nf), dtype=torch.float32, device="cuda")
-    Pt = torch.empty((nseq, 2 * nf), dtype=torch.float32, device="cuda")
-    At = torch.empty((nseq, nf), dtype=torch.int32, device="cuda")
-    sW, sX, sR = sm.asarray(W), sm.asarray(X), sm.asarray(R)
-    sZ = sarr = sm.sarray(Z, np.float32)
-
-    def timeit(fn, reps=10):
-        for _ in range(3):
-            fn()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize(); e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record(); e1.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    t = {}
-    t["ref corr1ord"] = timeit(lambda: ref.ref_corr1ord(F32, P(tW), m, nf, P(tX), n, P(Z)))
-    t["new api_corr1ord"] = timeit(lambda: ks.corr1ord(sW, sX, sZ, 4))
-    t["ref poolrgn(all)"] = timeit(lambda: ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), PT["all"]))
-    t["new api_poolrgn(all)"] = timeit(lambda: ks.poolrgn(sarr, sR, "all", want_argmax=True))
-    t["new fused scan+bias+relu+pool"] = timeit(lambda: fused.scanpool(tW, tb, sX.tensor.view(-1), tR, "all", want_argmax=True))
-    # backward operators: filter gradient from dZ, pooling gradient scattered into the activation
-    dZ = torch.randn((X.size, nf), dtype=torch.float32, device="cuda")
-    dW = torch.zeros((4 * m, nf), dtype=torch.float32, device="cuda")
-    sdZ, sdW = sm.sarray(dZ, np.float32), sm.sarray(dW, np.float32)
-    t["ref corr1ord_bprop_W"] = timeit(lambda: ref.ref_corr1ord_bprop_W(F32, P(dW), m, nf, P(tX), n, P(dZ)))
-    t["new api_corr1ord_bprop_W"] = timeit(lambda: ks.corr1ord_bprop_W(sdW, sX, sdZ, 4))
-    dP = torch.randn((nseq, 2 * nf), dtype=torch.float32, device="cuda")
-    sdP, sAt = sm.sarray(dP, np.float32), sm.sarray(At, np.uint32)
-    ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), PT["all"])          # argmax of the activation in Z
-    t["ref poolrgn_bprop(all)"] = timeit(lambda: ref.ref_poolrgn_bprop(F32, P(dZ), nf, P(tR), nseq, 2, P(dP), P(At), PT["all"]))
-    t["new api_poolrgn_bprop(all)"] = timeit(lambda: ks.poolrgn_bprop(sdZ, sR, sdP, sAt, "all"))
-    zbytes = X.size * nf * 4
-    with capsys.disabled():
-        print("\n%-34s %9s %10s" % ("kernel (16384 x 101 nt, 16 x 24)", "ms", "GB/s of Z"))
-        for k, v in t.items():
-            print("%-34s %9.3f %10.0f" % (k, v, zbytes / v / 1e6))
-        chain = t["ref corr1ord"] + t["ref poolrgn(all)"]
-        print("reference scan+pool chain (without its bias and rectify passes) / fused kernel: %.1fx" %
-              (chain / t["new fused scan+bias+relu+pool"]))
-    assert t["new api_corr1ord"] <= 1.25 * t["ref corr1ord"]
-    assert t["new api_poolrgn(all)"] <= 1.25 * t["ref poolrgn(all)"]
-    assert t["new fused scan+bias+relu+pool"] < t["ref corr1ord"] + t["ref poolrgn(all)"]
