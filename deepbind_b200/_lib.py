@@ -98,6 +98,7 @@ _PROTOTYPES = {
     "db_colsum": (None, [P, P, c_uint32, c_uint32]),
     "db_colsum_static": (None, [P, P, c_uint32, c_uint32]),
     "db_logistic": (None, [P, P, c_size_t]),
+    "db_randn": (None, [P, c_size_t]),
     "db_loss": (None, [c_int, P, P, P, P, c_uint32, c_uint32, P, P]),
     "db_l1_decay": (None, [P, P, P, c_size_t]),
     "db_fadd_probe": (c_uint64, [P, c_uint32]),

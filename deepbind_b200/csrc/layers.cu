@@ -5,6 +5,7 @@
 // order so that repeated runs agree bit for bit (the reference's reduce_y is
 // also free of atomics, smat_cuda/reduce_y.cuh:52-126).
 #include "db_common.cuh"
+#include "db_rng.cuh"
 #include <mutex>
 
 namespace db {
@@ -153,6 +154,30 @@ DB_EXPORT void db_logistic(float* Z, const float* X, size_t n)
 	if (!n) return;
 	DB_REQUIRE(Z && X, "ValueError: db_logistic got a NULL pointer");
 	logistic_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(Z, X, n);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
+// Standard normal draws on the device (the reference initialises parameters with
+// smat's randn, cuRAND normals: smat_cuda/rand.cu:66-88, then scales them per model
+// with madd_bcast: sgd.py:331-340).  Counter-based: element i of call c is the
+// Box-Muller transform of two Philox uniforms keyed by (seed, c, i), so a given seed
+// gives the same parameters whatever the launch shape.  Streams of different
+// generators cannot agree with cuRAND's; what is kept is the distribution.
+__global__ void randn_kernel(float* __restrict__ out, size_t n, uint64_t seed, uint64_t call)
+{
+	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+		const float u1 = uniform_01(seed, 2 * call, i), u2 = uniform_01(seed, 2 * call + 1, i);
+		out[i] = sqrtf(-2.f * logf(u1)) * cospif(2.f * u2);
+	}
+}
+
+DB_EXPORT void db_randn(float* out, size_t n)
+{
+	DB_API_TRY
+	if (!n) return;
+	DB_REQUIRE(out, "ValueError: db_randn got a NULL pointer");
+	randn_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(out, n, state().seed ^ 0x9e3779b97f4a7c15ull, state().rng_calls++);
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }

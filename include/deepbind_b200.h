@@ -140,6 +140,9 @@ void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t ncol);       
  * (different streams) race on it. */
 void db_colsum_static(float* out, const float* A, uint32_t nrow, uint32_t ncol);
 void db_logistic(float* Z, const float* X, size_t n);
+/* n standard normal draws (smat's randn, smat_cuda/rand.cu:66-88, which the trainer scales per
+ * model with madd_bcast: sgd.py:331-340); the stream follows api_set_seed and advances per call. */
+void db_randn(float* out, size_t n);
 /* loss_node forward+backward (loss.py:52-112): kind 0 = mse, 1 = nll.  Z,Y [nrow,ncol];
  * Ymask/Zmask nullable bool [nrow,ncol]; loss_out [ncol] = scaled column means;
  * dZ (nullable) = maskout(Z-Y) / nrow. */
