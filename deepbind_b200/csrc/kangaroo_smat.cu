@@ -189,6 +189,49 @@ __global__ void corr1ord_bprop_X_kernel(T* __restrict__ dX, unsigned n, const T*
 	dX[t] = acc;
 }
 
+// The same sums for float, tiled: a CTA owns BXR consecutive rows; the dZ rows its taps
+// reach ([i0 - m + 1, i0 + BXR) x nf) and the filter bank, regrouped as [tap][filter][4
+// channels], wait in shared memory, and a thread owns one row and all four channels, so
+// that one dZ operand and one 16-byte weight operand feed four multiply-adds.  Order and
+// rounding per output are those of the kernel above (filters outer, taps inner, product
+// and sum rounded separately): the results are bit-identical.
+static constexpr int BXR = 128;
+
+__global__ void __launch_bounds__(BXR)
+corr1ord_bprop_X_tiled_kernel(float* __restrict__ dX, unsigned n, const float* __restrict__ W, unsigned m,
+                              unsigned nf, const float* __restrict__ dZ)
+{
+	extern __shared__ __align__(16) float bx_smem[];
+	float4* w4 = reinterpret_cast<float4*>(bx_smem);                // [m][nf] float4 (channels 0..3)
+	float* dz = bx_smem + (size_t)4 * m * nf;                       // [BXR + m - 1][nf + 1]
+	const unsigned i0 = blockIdx.x * BXR, ld = nf + 1;
+	for (unsigned e = threadIdx.x; e < m * nf; e += BXR) {
+		const unsigned k = e / nf, f = e - k * nf;
+		w4[e] = make_float4(W[(size_t)(4 * k) * nf + f], W[(size_t)(4 * k + 1) * nf + f],
+		                    W[(size_t)(4 * k + 2) * nf + f], W[(size_t)(4 * k + 3) * nf + f]);
+	}
+	const unsigned nrow = BXR + m - 1;
+	for (unsigned e = threadIdx.x; e < nrow * nf; e += BXR) {
+		const unsigned r = e / nf, f = e - r * nf;
+		const long long row = (long long)i0 + r - (long long)(m - 1);
+		dz[r * ld + f] = (row >= 0 && row < (long long)n) ? dZ[(size_t)row * nf + f] : 0.f;
+	}
+	__syncthreads();
+	const unsigned i = i0 + threadIdx.x;
+	if (i >= n) return;
+	float4 acc = reinterpret_cast<const float4*>(dX)[i];
+	const unsigned kmax = min(m, i + 1);
+	const float* zrow = dz + (size_t)(threadIdx.x + m - 1) * ld;   // dZ row i; row i - k lies k rows before it
+	for (unsigned f = 0; f < nf; ++f)
+		for (unsigned k = 0; k < kmax; ++k) {
+			const float z = zrow[(ptrdiff_t)f - (ptrdiff_t)k * (ptrdiff_t)ld];
+			const float4 w = w4[k * nf + f];
+			acc.x = __fadd_rn(acc.x, __fmul_rn(z, w.x)); acc.y = __fadd_rn(acc.y, __fmul_rn(z, w.y));
+			acc.z = __fadd_rn(acc.z, __fmul_rn(z, w.z)); acc.w = __fadd_rn(acc.w, __fmul_rn(z, w.w));
+		}
+	reinterpret_cast<float4*>(dX)[i] = acc;
+}
+
 // ------------------------------------------------------------------ poolrgn
 // One thread per (region, map): rows ascending, strict '>' so the first maximal
 // row wins, running sum in row order (poolrgn.cuh:60-78,99-114,133-159).
@@ -234,6 +277,77 @@ __global__ void poolrgn_kernel(const T* __restrict__ U, unsigned nf, const uint3
 	}
 }
 
+// float, unit step, nf in {4, 8, 16, 32}: a warp per region.  The rows of a
+// region are contiguous in memory, so the 32 lanes fetch 512 contiguous bytes per load
+// instruction (a lane owns four neighbouring maps of every (128/nf)-th row), four loads in
+// flight per lane, and park them in the warp's slice of shared memory; then one lane per map
+// walks the staged rows in order: strict '>' (first maximum wins) and the running sum in row
+// order, exactly as the scalar kernel.  The loads are what bounds this operator (npos*nf*4
+// bytes of HBM); the ordered reduction rides along.
+static constexpr int PRW = 8;                    // warps (regions) per CTA
+static constexpr int PRB = 2048;                 // bytes staged per warp and step (4 loads x 512 B)
+
+__global__ void __launch_bounds__(32 * PRW)
+poolrgn_warp_kernel(const float* __restrict__ U, unsigned nf, const uint32_t* __restrict__ R, unsigned nregion,
+                    float* __restrict__ P, uint32_t* __restrict__ A, int ptype)
+{
+	__shared__ __align__(16) float stage[PRW][PRB / 4];
+	const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	const unsigned q = nf / 4;                                     // 16-byte units per row
+	const unsigned rows_step = (PRB / 16) / q;                     // rows staged per step
+	float* mine = stage[warp];
+	for (unsigned r = blockIdx.x * PRW + warp; r < nregion; r += gridDim.x * PRW) {
+		const uint2 rg = reinterpret_cast<const uint2*>(R)[r];
+		const unsigned first = rg.x, last = rg.y;
+		float x = 0.f, y = 0.f;
+		unsigned xi = first;
+		if (lane < nf) { x = U[(size_t)first * nf + lane]; y = x; }             // the first row is read even if the region is empty
+		for (unsigned row = first + 1; row < last; row += rows_step) {
+			const unsigned nrow = min(rows_step, last - row);
+			const float4* src = reinterpret_cast<const float4*>(U + (size_t)row * nf);
+			const unsigned units = nrow * q;
+			float4 v[4];
+			#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				const unsigned u = lane + 32 * j;
+				v[j] = u < units ? src[u] : make_float4(0.f, 0.f, 0.f, 0.f);
+			}
+			#pragma unroll
+			for (int j = 0; j < 4; ++j) reinterpret_cast<float4*>(mine)[lane + 32 * j] = v[j];
+			__syncwarp();
+			if (lane < nf) {
+				for (unsigned k = 0; k < nrow; ++k) {
+					const float w = mine[k * nf + lane];
+					if (w > x) { x = w; xi = row + k; }
+					y += w;
+				}
+			}
+			__syncwarp();
+		}
+		if (lane < nf) {
+			const size_t t = (size_t)r * nf + lane;
+			const unsigned cnt = last - first;
+			switch (ptype) {
+			case DB_PT_MAX: P[t] = x; if (A) A[t] = xi * nf + lane; break;
+			case DB_PT_AVG: P[t] = y / (float)cnt; break;
+			case DB_PT_SUM: P[t] = y; break;
+			default:        P[2*t] = x; P[2*t+1] = y / (float)cnt; if (A) A[t] = xi * nf + lane; break;
+			}
+		}
+	}
+}
+
+// Do the regions ascend without overlap (each starts at or after the end of the one before)?
+// Then no two regions share a row of the unpooled maps and the backward pass may add without
+// atomics.  Writes 1 to *overlap otherwise (the caller zeroes it).
+__global__ void regions_overlap_kernel(const uint32_t* __restrict__ R, unsigned nregion, unsigned rcols, unsigned* __restrict__ overlap)
+{
+	for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x + 1; r < nregion; r += gridDim.x * blockDim.x) {
+		const unsigned prev_end = max(R[(r - 1) * rcols + 1], R[(r - 1) * rcols]);
+		if (R[r * rcols] < prev_end) *overlap = 1u;
+	}
+}
+
 template <typename T>
 __global__ void poolrgn_bprop_kernel(T* __restrict__ U, unsigned nf, const uint32_t* __restrict__ R, unsigned nregion,
                                      unsigned rcols, const T* __restrict__ P, const uint32_t* __restrict__ A, int ptype)
@@ -259,8 +373,11 @@ __global__ void poolrgn_bprop_kernel(T* __restrict__ U, unsigned nf, const uint3
 // the atomic operations of the scalar kernel, each fully coalesced.
 __global__ void __launch_bounds__(256)
 poolrgn_bprop_v4_kernel(float* __restrict__ U, unsigned nf, const uint32_t* __restrict__ R, unsigned nregion,
-                        const float* __restrict__ P, const uint32_t* __restrict__ A, int ptype)
+                        const float* __restrict__ P, const uint32_t* __restrict__ A, int ptype, const unsigned* __restrict__ overlap)
 {
+	// Disjoint regions (the batch layout): every element of U belongs to one region, hence to
+	// one warp, and is updated by plain loads and stores: deterministic, no atomic traffic.
+	const bool plain = *overlap == 0u;
 	const unsigned lane = threadIdx.x & 31, q = nf / 4, f = 4 * (lane % q), rl = lane / q, nrl = 32 / q;
 	for (unsigned r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nregion; r += gridDim.x * (blockDim.x >> 5)) {
 		const uint2 rg = reinterpret_cast<const uint2*>(R)[r];
@@ -276,6 +393,20 @@ poolrgn_bprop_v4_kernel(float* __restrict__ U, unsigned nf, const uint32_t* __re
 			d.x /= cnt; d.y /= cnt; d.z /= cnt; d.w /= cnt;
 		}
 		float4* Uf = reinterpret_cast<float4*>(U + f);
+		if (plain) {
+			for (unsigned row = rg.x + rl; row < rg.y; row += nrl) {
+				float4 u = Uf[(size_t)row * q];
+				u.x += d.x; u.y += d.y; u.z += d.z; u.w += d.w;
+				Uf[(size_t)row * q] = u;
+			}
+			__syncwarp();                                   // the mean shares are in place before the maximum's delta is added
+			if (ptype == DB_PT_ALL && rl == 0) {
+				const uint4 a = *reinterpret_cast<const uint4*>(A + t);
+				U[a.x] += x.x; U[a.y] += x.y; U[a.z] += x.z; U[a.w] += x.w;
+			}
+			__syncwarp();
+			continue;
+		}
 		for (unsigned row = rg.x + rl; row < rg.y; row += nrl)
 			atomicAdd(Uf + (size_t)row * q, d);
 		if (ptype == DB_PT_ALL && rl == 0) {
@@ -376,7 +507,14 @@ DB_EXPORT void api_corr1ord_bprop_X(smat* dX, const smat* W, const smat* dZ, con
 	if (n == 0 || nf == 0) return;
 	unsigned grid = (unsigned)divup((size_t)n * 4, (size_t)128);
 	if (dZ->dtype == DB_F32)
-		corr1ord_bprop_X_kernel<<<grid, 128, 0, state().stream>>>((float*)dX->data, n, (const float*)W->data, m, nf, (const float*)dZ->data);
+	{
+		const size_t smem = ((size_t)4 * m * nf + (size_t)(BXR + m - 1) * (nf + 1)) * sizeof(float);
+		if (smem <= 200 * 1024 && ((uintptr_t)dX->data & 15) == 0) {
+			DB_CUDA(cudaFuncSetAttribute(corr1ord_bprop_X_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, (size_t)48 * 1024)));
+			corr1ord_bprop_X_tiled_kernel<<<divup(n, (unsigned)BXR), BXR, smem, state().stream>>>((float*)dX->data, n, (const float*)W->data, m, nf, (const float*)dZ->data);
+		} else
+			corr1ord_bprop_X_kernel<<<grid, 128, 0, state().stream>>>((float*)dX->data, n, (const float*)W->data, m, nf, (const float*)dZ->data);
+	}
 	else
 		corr1ord_bprop_X_kernel<<<grid, 128, 0, state().stream>>>((double*)dX->data, n, (const double*)W->data, m, nf, (const double*)dZ->data);
 	DB_LAUNCH_CHECK();
@@ -424,7 +562,12 @@ DB_EXPORT void api_poolrgn(const smat* unpooledmaps, const smat* regions, smat* 
 	if (!n) return;
 	unsigned grid = (unsigned)divup(n, (size_t)128);
 	uint32_t* A = pooledmaps_argmax ? (uint32_t*)pooledmaps_argmax->data : nullptr;
-	if (unpooledmaps->dtype == DB_F32)
+	const bool vec = unpooledmaps->dtype == DB_F32 && regions->shape.x == 2 && nf % 4 == 0 && nf <= 32 && 32 % nf == 0 &&
+	                 ((uintptr_t)unpooledmaps->data & 15) == 0 && ((uintptr_t)regions->data & 7) == 0;
+	if (vec)
+		poolrgn_warp_kernel<<<std::min(divup(nregion, (unsigned)PRW), 32u * (unsigned)state().sm_count), 32 * PRW, 0, state().stream>>>(
+			(const float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion, (float*)pooledmaps->data, A, options->ptype);
+	else if (unpooledmaps->dtype == DB_F32)
 		poolrgn_kernel<<<grid, 128, 0, state().stream>>>((const float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion,
 		                                                 (unsigned)regions->shape.x, (float*)pooledmaps->data, A, options->ptype);
 	else
@@ -449,8 +592,12 @@ DB_EXPORT void api_poolrgn_bprop(smat* unpooledmaps, const smat* regions, const 
 	if (unpooledmaps->dtype == DB_F32 && options->ptype != DB_PT_MAX && regions->shape.x == 2 && nf % 4 == 0 && nf <= 128 &&
 	    32 % (nf / 4) == 0 && aligned && (options->ptype != DB_PT_ALL || A)) {
 		unsigned ncta = std::min(divup(nregion, 8u), 16u * (unsigned)state().sm_count);
+		unsigned* overlap = (unsigned*)scratch(256);
+		DB_CUDA(cudaMemsetAsync(overlap, 0, 4, state().stream));
+		regions_overlap_kernel<<<elemwise_grid(nregion), 256, 0, state().stream>>>((const uint32_t*)regions->data, nregion, 2u, overlap);
+		DB_LAUNCH_CHECK();
 		poolrgn_bprop_v4_kernel<<<ncta, 256, 0, state().stream>>>((float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion,
-		                                                          (const float*)pooledmaps->data, A, options->ptype);
+		                                                          (const float*)pooledmaps->data, A, options->ptype, overlap);
 	} else if (unpooledmaps->dtype == DB_F32)
 		poolrgn_bprop_kernel<<<grid, 128, 0, state().stream>>>((float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion,
 		                                                       (unsigned)regions->shape.x, (const float*)pooledmaps->data, A, options->ptype);

@@ -182,6 +182,29 @@ DB_EXPORT void db_randn(float* out, size_t n)
 	DB_API_CATCH
 }
 
+// Strand choice of kangaroo.predict (predict.py:145-164): rows come in forward /
+// reverse-complement pairs; the larger score of each pair is kept, the forward one on ties.
+__global__ void strand_max_kernel(float* __restrict__ out, const float* __restrict__ Z, size_t npair, unsigned ncol)
+{
+	const size_t n = npair * ncol;
+	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+		const size_t p = i / ncol, c = i - p * ncol;
+		const float f = Z[(2 * p) * ncol + c], r = Z[(2 * p + 1) * ncol + c];
+		out[i] = f >= r ? f : r;
+	}
+}
+
+DB_EXPORT void db_strand_max(float* out, const float* Z, uint32_t npair, uint32_t ncol)
+{
+	DB_API_TRY
+	const size_t n = (size_t)npair * ncol;
+	if (!n) return;
+	DB_REQUIRE(out && Z, "ValueError: db_strand_max got a NULL pointer");
+	strand_max_kernel<<<elemwise_grid(n), 256, 0, state().stream>>>(out, Z, npair, ncol);
+	DB_LAUNCH_CHECK();
+	DB_API_CATCH
+}
+
 DB_EXPORT void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t ncol)
 {
 	DB_API_TRY

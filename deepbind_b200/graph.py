@@ -1295,11 +1295,12 @@ class GraphTrainer(object):
         return self.cost.eval_model(batches)
 
 
-def gradcheck(trainer, batch, nprobe=12, step=1e-2, rtol=2e-2, atol=2e-4, seed=0):
+def gradcheck(trainer, batch, nprobe=12, step=2e-3, rtol=5e-2, atol=1e-3, seed=0):
     """Compares the graph's gradient with central differences of the summed cost at a
     few parameters of every trainable node, in test mode (deepity/gradcheck.py:42-130;
-    the reference perturbs by 1e-4 in float32 and accepts atol 1e-4).  Raises
-    AssertionError listing the parameters that disagree."""
+    the reference perturbs by 1e-4 in float32 and accepts atol 1e-4; the step here is
+    larger because the cost is a float32 mean, and small enough that few rectifiers
+    switch within it).  Raises AssertionError listing the parameters that disagree."""
     rng = np.random.default_rng(seed)
     failures = []
     flags.push("gradcheck", True)

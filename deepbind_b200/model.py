@@ -133,16 +133,25 @@ class DeepBindNet(object):
             return pooled
         return dsm.dropout_fp_test(_as_f32(pooled), sm_asarray(self.dropout_rate)).tensor
 
-    def score(self, X, R, strand_max=False):
+    def score(self, X, R, strand_max=False, exact=False):
         """Scores [nseq, I] (no output non-linearity).  With strand_max, rows are
         fwd/rc pairs and the larger score of each pair is kept, forward on ties
-        (code/libs/kangaroo/kangaroo/predict.py:145-164)."""
+        (code/libs/kangaroo/kangaroo/predict.py:145-164).  Scoring consumes no argmax, so
+        the scan runs through the k-mer kernel where it is built for this filter length
+        (regions ascending without overlap, as every batch builder here lays them out);
+        ``exact=True`` takes the tap-by-tap kernel whose pooled values are bit-identical
+        to the operator chain."""
         bind_stream()
-        pooled, _, _ = fused.scanpool(self.view("Wscan"), self.view("bscan").view(-1), X, R, self.pool, relu=True)
+        W, b = self.view("Wscan"), self.view("bscan").view(-1)
+        if not exact and fused.score_supported(self.m):
+            pooled = fused.scanpool_score(W, b, X, R, self.pool, relu=True)
+        else:
+            pooled, _, _ = fused.scanpool(W, b, X, R, self.pool, relu=True)
         out, _, _ = self._head(self._test_dropout(pooled))
         if strand_max:
-            out = out.view(-1, 2, self.I)
-            out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
+            both = out.contiguous()
+            out = torch.empty((both.shape[0] // 2, self.I), dtype=torch.float32, device=self.dev)
+            _lib.load().db_strand_max(out.data_ptr(), both.data_ptr(), out.shape[0], self.I)
         return out
 
     def input_gradients(self, X, R, strand_max=False):

@@ -140,6 +140,9 @@ void db_colsum(float* out, const float* A, uint32_t nrow, uint32_t ncol);       
  * (different streams) race on it. */
 void db_colsum_static(float* out, const float* A, uint32_t nrow, uint32_t ncol);
 void db_logistic(float* Z, const float* X, size_t n);
+/* Strand choice of scoring (kangaroo/predict.py:145-164): Z [2*npair, ncol] holds forward /
+ * reverse-complement row pairs; out [npair, ncol] keeps the larger score, the forward one on ties. */
+void db_strand_max(float* out, const float* Z, uint32_t npair, uint32_t ncol);
 /* n standard normal draws (smat's randn, smat_cuda/rand.cu:66-88, which the trainer scales per
  * model with madd_bcast: sgd.py:331-340); the stream follows api_set_seed and advances per call. */
 void db_randn(float* out, size_t n);
@@ -242,6 +245,19 @@ void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
                      const uint32_t* regions, uint32_t nregion, int ptype,
                      const float* dpooled, const uint32_t* argmax, const uint16_t* actmask,
                      float* dW, float* dbias);
+
+/* Scoring form of db_scanpool_fwd (no counterpart as one call: the forward chain
+ * corr1ord -> bias -> rectify -> poolrgn of kangaroo/_ext/corr1ord.py:97-118, poolrgn.py:54-75
+ * when only pooled values are wanted).  The taps are summed k-mer-wise from lookup tables
+ * (2 or 3 taps per table operand), so pooled values agree with db_scanpool_fwd up to the
+ * rounding of the regrouped FP32 sums (<= 1e-6 of the largest activation); no argmax.
+ * Built for filter lengths 8, 12, 16, 20, 24, 32 (db_scanpool_score_supported).  Regions
+ * (8-byte aligned table) must ascend without overlap; status (nullable device int the
+ * caller zeroes) becomes 3 otherwise. */
+int  db_scanpool_score_supported(uint32_t m);
+void db_scanpool_score(const float* W, uint32_t m, uint32_t nf, const float* bias, int relu,
+                       const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion,
+                       int ptype, float* pooled, int* status);
 
 /* ---- many-model scan on tcgen05 tensor cores (no counterpart: replaces `nf/16`
  * passes of kangaroo.predict over the same sequences, predict.py:394-420, and

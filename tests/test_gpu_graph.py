@@ -94,7 +94,8 @@ def test_a_model_outside_the_family_trains_and_its_gradient_checks(cuda):
     I, m = 3, 8
     rng = np.random.default_rng(1)
     seqs, Y = planted(rng, 192, 30)
-    spec = cfg.sgd(rate=cfg.loguniform(0.02, 0.05), momentum=0.9, batchsize=64, max_steps=150, checkpoints=3, weight_decay_start=0)
+    spec = cfg.sgd(rate=cfg.loguniform(0.02, 0.05), momentum=0.9, batchsize=64, max_steps=150, max_epochs=100, checkpoints=3,
+                   weight_decay_start=0)
     tr = g.GraphTrainer(g.from_layers(layers, motif_len=m), spec, ninst=I, data_shapes={"X_seq": 1, "R_seq": 2, "F": 16}, seed=4)
     bs = [b for b, _, _, _ in batches_of(seqs, Y, 64, m - 1, I)]
     assert g.gradcheck(tr, bs[0])
@@ -117,7 +118,7 @@ def test_input_dropout_in_front_of_the_scan(cuda):
     nodes = [g.dropoutord(rate), g.motif_scan(8, motif_len=8, init_scale=0.3), g.bias(), g.rectify(), g.maxpool(),
              g.full(1, init_scale=0.3), g.bias(), g.softmax()]
     model = g.from_layers(nodes)
-    spec = cfg.sgd(rate=0.05, momentum=0.9, batchsize=32, max_steps=40)
+    spec = cfg.sgd(rate=0.05, momentum=0.9, batchsize=32, max_steps=40, max_epochs=100)
     tr = g.GraphTrainer(model, spec, ninst=1, data_shapes={"X_seq": 1, "R_seq": 2, "regions": 2, "F": 16}, seed=2)
     rng = np.random.default_rng(2)
     seqs, Y = planted(rng, 64, 30)
@@ -163,10 +164,11 @@ def test_input_gradients_through_the_graph(cuda, orc):
     tr = g.GraphTrainer(model, cfg.sgd(), ninst=I, data_shapes={"X_seq": 1, "R_seq": 2, "F": 16}, seed=3)
     p = synth.model_params(I, m, 8, "max")
     p["Wscan"] *= 5
+    assert [q.name for q in tr.tplugs] == ["W0", "b0", "W1", "b1"]      # two biases at the same level: b0 (scan), b1 (output)
     tr.param("W0").tensor.copy_(torch.from_numpy(p["Wscan"]))
-    tr.param("b").tensor.copy_(torch.from_numpy(p["bscan"]).view(1, -1))
+    tr.param("b0").tensor.copy_(torch.from_numpy(p["bscan"]).view(1, -1))
     tr.param("W1").tensor.view(I, 32, 1)[:, :16].copy_(torch.from_numpy(p["W1"]).view(I, 16, 1))
-    tr.param("b0").tensor.copy_(torch.from_numpy(p["b1"]).view(1, -1))
+    tr.param("b1").tensor.copy_(torch.from_numpy(p["b1"]).view(1, -1))
     X, R = synth.ragged_batch(20, 20, 50, m, seed=9)
     res = tr.cost.model.eval(X_seq=sm.asarray(X.reshape(-1, 1)), R_seq=sm.asarray(R), F=sm.zeros((20, 16), f32),
                              want_bprop_inputs=True)
