@@ -238,7 +238,7 @@ def side_workloads(dev, with_cpu):
         return {"adds": adds, "Tadd_per_s": adds / (ms * 1e-3) / 1e12, "frac_fp32_add_issue": adds / (ms * 1e-3) / issue_peak,
                 "frac_smem_operand_ceiling": adds / (ms * 1e-3) / (issue_peak / 4)}
 
-    # config 1: PBM-style forward scoring, 4096 x 40 nt, one model, FP32 k-mer lookup kernel (two taps per table operand)
+    # config 1: PBM-style forward scoring, 4096 x 40 nt, one model, exact FP32 kernel
     p = synth.model_params(1, M, 21, "max")
     Xh, Rh = synth.uniform_batch(4096, 40, M, seed=22)
     net = DeepBindNet(p, 1, "max"); X, R = to_dev(Xh, Rh)
@@ -249,13 +249,8 @@ def side_workloads(dev, with_cpu):
     for _ in range(3):
         graph.replay()
     ms = _events_ms(graph.replay, 50)
-    for _ in range(3):
-        net.score(X, R, exact=True)
-    ms_exact = _events_ms(lambda: net.score(X, R, exact=True), 20)
     out["pbm_forward"] = {"unit": "sequences/s", "value": 4096 / ms * 1e3, "ms": ms, "ms_separate_launches": ms_eager,
-                          "ms_separate_launches_exact_kernel": ms_exact,
-                          "kernel": "f32 k-mer lookup (2 taps per operand; <= 1e-6 of the tap-by-tap kernel); scan + linear head replayed "
-                                    "from a CUDA graph",
+                          "kernel": "f32 lookup-add, bit-exact; scan + linear head replayed from a CUDA graph",
                           "cpu": cpu_time(lambda: orc.score_net(p, Xh, Rh, "max", 1), 4096),
                           "bound": "launch latency (99 M adds; one scan launch + two head launches)",
                           **rates(int((Rh[:, 1] - Rh[:, 0]).sum()), NMOTIF, M, ms)}
@@ -267,17 +262,11 @@ def side_workloads(dev, with_cpu):
     for _ in range(3):
         net.score(X, R, strand_max=True)
     ms = _events_ms(lambda: net.score(X, R, strand_max=True), 10)
-    for _ in range(3):
-        net.score(X, R, strand_max=True, exact=True)
-    ms_exact = _events_ms(lambda: net.score(X, R, strand_max=True, exact=True), 10)
-    chk = torch.zeros(1, dtype=torch.int32, device=dev)
-    fused.scanpool_score(net.view("Wscan"), net.view("bscan").view(-1), X, R, "max", status=chk)
     ns = 20000
-    out["ragged_rna"] = {"unit": "sequences/s", "value": 200000 / ms * 1e3, "ms": ms, "ms_exact_kernel": ms_exact,
-                         "value_exact_kernel": 200000 / ms_exact * 1e3, "regions_ok": int(chk.item()) == 0,
-                         "kernel": "f32 k-mer lookup (3 taps per operand; <= 1e-6 of the tap-by-tap kernel), strand maximum by db_strand_max",
+    out["ragged_rna"] = {"unit": "sequences/s", "value": 200000 / ms * 1e3, "ms": ms,
+                         "kernel": "f32 lookup-add, bit-exact; strand maximum by db_strand_max",
                          "cpu": cpu_time(lambda: orc.score_net(p, Xh[:Rh[2 * ns - 1, 1] + 15], Rh[:2 * ns], "max", 1, strand_max=True), ns),
-                         "bound": "shared-memory operand return path (one 16-byte table entry per 3 taps x 4 filters)", "hbm_gbs_algorithmic": (Xh.size + 4 * 200000) / (ms * 1e-3) / 1e9,
+                         "bound": "shared-memory operand return path", "hbm_gbs_algorithmic": (Xh.size + 4 * 200000) / (ms * 1e-3) / 1e9,
                          **rates(int((Rh[:, 1] - Rh[:, 0]).sum()), NMOTIF, 16, ms)}
     del X, R
 
@@ -415,28 +404,37 @@ def reference_kernels(dev):
     P = lambda t: ctypes.c_void_p(t.data_ptr())
     F32, ALL = 9, 3
 
-    def t_of(fn, reps=10):
+    def t_of(fn, reps=20):
         for _ in range(3):
             fn()
         return _events_ms(fn, reps)
+    # the new operators are called through the C ABI with their outputs allocated beforehand, as the
+    # reference's are: a Python wrapper that allocates per call costs more than these kernels take
+    from deepbind_b200 import _lib
+    from ctypes import byref
+    dll = _lib.load()
+    sm.bind_stream()
+    popt = _lib.c_poolrgn_options_t(); popt.ptype = ALL
+    copt = _lib.c_corr1ord_options_t(); copt.padmode = 0; copt.nchannel = 4
+    sPt, sAt0 = sm.sarray(Pt, np.float32), sm.sarray(At, np.uint32)
     t = {}
     t["ref_corr1ord"] = t_of(lambda: ref.ref_corr1ord(F32, P(tW), m, nf, P(tX), n, P(Z)))
-    t["new_corr1ord"] = t_of(lambda: ks.corr1ord(sW, sX, sZ, 4))
+    t["new_corr1ord"] = t_of(lambda: dll.api_corr1ord(sW._ptr, sX._ptr, sZ._ptr, byref(copt)))
     t["ref_poolrgn_all"] = t_of(lambda: ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), ALL))
-    t["new_poolrgn_all"] = t_of(lambda: ks.poolrgn(sZ, sR, "all", want_argmax=True))
+    t["new_poolrgn_all"] = t_of(lambda: dll.api_poolrgn(sZ._ptr, sR._ptr, sPt._ptr, sAt0._ptr, byref(popt)))
     t["new_fused_scan_bias_relu_pool"] = t_of(lambda: fused.scanpool(tW, tb, sX.tensor.view(-1), tR, "all", want_argmax=True))
     dZ = torch.randn((Xh.size, nf), dtype=torch.float32, device=dev)
     dW = torch.zeros((4 * m, nf), dtype=torch.float32, device=dev)
     sdZ, sdW = sm.sarray(dZ, np.float32), sm.sarray(dW, np.float32)
     t["ref_corr1ord_bprop_W"] = t_of(lambda: ref.ref_corr1ord_bprop_W(F32, P(dW), m, nf, P(tX), n, P(dZ)))
-    t["new_corr1ord_bprop_W"] = t_of(lambda: ks.corr1ord_bprop_W(sdW, sX, sdZ, 4))
+    t["new_corr1ord_bprop_W"] = t_of(lambda: dll.api_corr1ord_bprop_W(sdW._ptr, sX._ptr, sdZ._ptr, byref(copt)))
     dP = torch.randn((nseq, 2 * nf), dtype=torch.float32, device=dev)
     sdP, sAt = sm.sarray(dP, np.float32), sm.sarray(At, np.uint32)
     ref.ref_poolrgn(F32, P(Z), nf, P(tR), nseq, 2, P(Pt), P(At), ALL)
     t["ref_poolrgn_bprop_all"] = t_of(lambda: ref.ref_poolrgn_bprop(F32, P(dZ), nf, P(tR), nseq, 2, P(dP), P(At), ALL))
-    t["new_poolrgn_bprop_all"] = t_of(lambda: ks.poolrgn_bprop(sdZ, sR, sdP, sAt, "all"))
+    t["new_poolrgn_bprop_all"] = t_of(lambda: dll.api_poolrgn_bprop(sdZ._ptr, sR._ptr, sdP._ptr, sAt._ptr, byref(popt)))
     dXs = sm.zeros((Xh.size, 4), np.float32)
-    t["new_corr1ord_bprop_X"] = t_of(lambda: ks.corr1ord_bprop_X(dXs, sW, sdZ, 4), reps=3)
+    t["new_corr1ord_bprop_X"] = t_of(lambda: dll.api_corr1ord_bprop_X(dXs._ptr, sW._ptr, sdZ._ptr, byref(copt)), reps=5)
     zbytes = float(Xh.size) * nf * 4
     peaks = _read_peaks()
     hbm = (peaks.get("hbm_gbs") or 6650.0) * 1e9

@@ -99,8 +99,6 @@ _PROTOTYPES = {
     "db_colsum_static": (None, [P, P, c_uint32, c_uint32]),
     "db_logistic": (None, [P, P, c_size_t]),
     "db_strand_max": (None, [P, P, c_uint32, c_uint32]),
-    "db_scanpool_score_supported": (c_int, [c_uint32]),
-    "db_scanpool_score": (None, [P, c_uint32, c_uint32, P, c_int, P, c_uint32, P, c_uint32, c_int, P, P]),
     "db_randn": (None, [P, c_size_t]),
     "db_loss": (None, [c_int, P, P, P, P, c_uint32, c_uint32, P, P]),
     "db_l1_decay": (None, [P, P, P, c_size_t]),
@@ -121,7 +119,7 @@ _PROTOTYPES = {
                               P, P, P, c_uint32, P, P]),
 }
 
-_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count", "db_scratch_bytes", "db_scanpool_score_supported"}
+_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count", "db_scratch_bytes"}
 
 
 class _SafeFunc(object):

@@ -46,27 +46,6 @@ def scanpool(W, bias, X, R, ptype="max", relu=True, want_argmax=False, want_actm
     return pooled, argmax, actmask
 
 
-def score_supported(m):
-    """Is the k-mer scoring kernel built for filters of ``m`` taps?"""
-    return bool(_lib.load().db_scanpool_score_supported(int(m)))
-
-
-def scanpool_score(W, bias, X, R, ptype="max", relu=True, status=None):
-    """Pooled features as :func:`scanpool` gives them, for scoring: the taps are summed
-    k-mer-wise (2 or 3 per lookup), which is 2-3 times faster and differs from the exact
-    kernel by FP32 rounding only (<= 1e-6 of the largest activation); no argmax, no
-    activity mask.  Regions must ascend without overlap (the batch layout); ``status``
-    (a zeroed int32 tensor of one element, optional) is set to 3 otherwise."""
-    _check(W, torch.float32, "W"); _check(X, torch.uint8, "X"); _check(R, torch.int32, "R")
-    if bias is not None:
-        _check(bias, torch.float32, "bias")
-    m, nf = W.shape[0] // 4, W.shape[1]
-    pooled = torch.empty((R.shape[0], nf * (2 if ptype == "all" else 1)), dtype=torch.float32, device=W.device)
-    _dll().db_scanpool_score(_ptr(W), m, nf, _ptr(bias), int(bool(relu)), _ptr(X), X.numel(), _ptr(R), R.shape[0],
-                             PT[ptype], _ptr(pooled), _ptr(status))
-    return pooled
-
-
 def scanpool_bprop(m, nf, X, R, ptype, dpooled, argmax, actmask, dW_out=None, db_out=None):
     """Returns (dW [4m, nf], dbias [nf]) of the fused stage; ``dW_out`` / ``db_out``
     (contiguous f32) receive them in place, e.g. slices of a flat gradient vector."""

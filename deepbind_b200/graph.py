@@ -464,10 +464,14 @@ class supernode(node):
     @staticmethod
     def _names(plugs):
         raw = [p.name for p in plugs]
+        keep = {n for n in raw if raw.count(n) == 1}       # names that are unique stay as they are
         out = []
         for i, nm in enumerate(raw):
-            while (raw + out).count(nm) > 1:
-                nm = nm + str(raw[:i].count(raw[i]))
+            if nm not in keep:                             # R, R -> R0, R1 (skipping numbers already in use)
+                k = raw[:i].count(nm)
+                while nm + str(k) in keep or nm + str(k) in out:
+                    k += 1
+                nm = nm + str(k)
             out.append(nm)
         return out
 

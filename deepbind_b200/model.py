@@ -133,20 +133,12 @@ class DeepBindNet(object):
             return pooled
         return dsm.dropout_fp_test(_as_f32(pooled), sm_asarray(self.dropout_rate)).tensor
 
-    def score(self, X, R, strand_max=False, exact=False):
+    def score(self, X, R, strand_max=False):
         """Scores [nseq, I] (no output non-linearity).  With strand_max, rows are
         fwd/rc pairs and the larger score of each pair is kept, forward on ties
-        (code/libs/kangaroo/kangaroo/predict.py:145-164).  Scoring consumes no argmax, so
-        the scan runs through the k-mer kernel where it is built for this filter length
-        (regions ascending without overlap, as every batch builder here lays them out);
-        ``exact=True`` takes the tap-by-tap kernel whose pooled values are bit-identical
-        to the operator chain."""
+        (code/libs/kangaroo/kangaroo/predict.py:145-164)."""
         bind_stream()
-        W, b = self.view("Wscan"), self.view("bscan").view(-1)
-        if not exact and fused.score_supported(self.m):
-            pooled = fused.scanpool_score(W, b, X, R, self.pool, relu=True)
-        else:
-            pooled, _, _ = fused.scanpool(W, b, X, R, self.pool, relu=True)
+        pooled, _, _ = fused.scanpool(self.view("Wscan"), self.view("bscan").view(-1), X, R, self.pool, relu=True)
         out, _, _ = self._head(self._test_dropout(pooled))
         if strand_max:
             both = out.contiguous()

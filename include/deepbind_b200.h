@@ -246,19 +246,6 @@ void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
                      const float* dpooled, const uint32_t* argmax, const uint16_t* actmask,
                      float* dW, float* dbias);
 
-/* Scoring form of db_scanpool_fwd (no counterpart as one call: the forward chain
- * corr1ord -> bias -> rectify -> poolrgn of kangaroo/_ext/corr1ord.py:97-118, poolrgn.py:54-75
- * when only pooled values are wanted).  The taps are summed k-mer-wise from lookup tables
- * (2 or 3 taps per table operand), so pooled values agree with db_scanpool_fwd up to the
- * rounding of the regrouped FP32 sums (<= 1e-6 of the largest activation); no argmax.
- * Built for filter lengths 8, 12, 16, 20, 24, 32 (db_scanpool_score_supported).  Regions
- * (8-byte aligned table) must ascend without overlap; status (nullable device int the
- * caller zeroes) becomes 3 otherwise. */
-int  db_scanpool_score_supported(uint32_t m);
-void db_scanpool_score(const float* W, uint32_t m, uint32_t nf, const float* bias, int relu,
-                       const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion,
-                       int ptype, float* pooled, int* status);
-
 /* ---- many-model scan on tcgen05 tensor cores (no counterpart: replaces `nf/16`
  * passes of kangaroo.predict over the same sequences, predict.py:394-420, and
  * deepity's instance batching, hypertrain.py:576) ---------------------------

@@ -106,8 +106,9 @@ def test_a_model_outside_the_family_trains_and_its_gradient_checks(cuda):
     last = tr.loss(bs)
     assert np.all(np.isfinite(last)) and np.all(last < 0.8 * first), (first, last)
     # device-side initialisation: per-model scale, zero-mean
-    W = tr.param("W2").asnumpy()
+    W = [t.P for t, q in zip(tr.trnodes, tr.tplugs) if isinstance(q.origin().node, g.full) and q.origin().node.size == 4][0].asnumpy()
     assert W.shape == (I * 8, 4)
+    assert len({q.name for q in tr.tplugs}) == len(tr.tplugs)        # exported plug names are unique
 
 
 def test_input_dropout_in_front_of_the_scan(cuda):

@@ -132,7 +132,10 @@ def test_model_file_becomes_a_sequencenet_with_inferred_shapes():
     c2 = g.cost(m2)
     assert isinstance(c2.loss, g.mse)
     c2.F.shape = (None, 16)
-    assert {p.name: p.shape for p in c2.iplugs}["W1"] == (8 + 16, 8)
+    names = [p.name for p in c2.iplugs]
+    assert len(set(names)) == len(names)               # W, W beside the output net's W0, W1: numbered past them
+    comb = [p for p in c2.iplugs if p.origin().node is m2.combiner][0]
+    assert comb.shape == (8 + 16, 8)
 
 
 def test_constraints_and_missing_gradient_are_reported():
