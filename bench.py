@@ -52,6 +52,9 @@ def parse():
                     help="arithmetic of the scan: one 16-bit piece per weight on tcgen05 (f16 = TF32-grade, bf16), several pieces "
                          "(f16x2, bf16x3 = fp32-grade), or the exact FP32 lookup-add kernel")
     ap.add_argument("--gather-chunks", type=int, default=16, help="several GPUs: chunks of the shard whose all-gather overlaps the scan")
+    ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
+                    help="several GPUs: 'peer' = the scan kernel stores every score into all ranks' matrices over NVLink "
+                         "(symmetric memory, no collective pass); 'nccl' = chunked all-gather overlapped with the scan")
     ap.add_argument("--nccl-max-ctas", type=int, default=8, help="several GPUs: CTAs NCCL may use per collective (0 = NCCL's default); "
                                                                   "the scan wants every SM")
     ap.add_argument("--no-variants", action="store_true", help="skip the short runs of the other arithmetic variants")
@@ -65,7 +68,10 @@ def config(args, world):
     return {"workload": "many-model genome scan: %d models x %d motifs x %d taps, %d-nt uniform ACGT, max+avg pooling, "
                         "linear head, score matrix [nseq, %d]" % (args.nmodel, NMOTIF, M, L, args.nmodel),
             "nseq_per_gpu": args.nseq, "global_nseq": args.nseq * world, "nmodel": args.nmodel,
-            "parallelism": "sequences sharded over %d GPU(s)%s" % (world, ", NCCL all-gather of the score shards in %d chunks overlapped with the scan" % args.gather_chunks if world > 1 else ""),
+            "parallelism": "sequences sharded over %d GPU(s)%s" % (world, "" if world == 1 else
+                                                                   ", scores stored by the scan kernel into every rank's matrix over NVLink (peer stores), one-element all-reduce as barrier"
+                                                                   if args.gather == "peer" else
+                                                                   ", NCCL all-gather of the score shards in %d chunks overlapped with the scan" % args.gather_chunks),
             "l2": "working set per step (input + score matrix) exceeds the 126 MB L2; no explicit flush"}
 
 
@@ -442,9 +448,9 @@ def reference_kernels(dev):
            "ms": t, "z_bytes": zbytes,
            "scan_pool_chain_speedup": (t["ref_corr1ord"] + t["ref_poolrgn_all"]) / t["new_fused_scan_bias_relu_pool"],
            "frac_hbm": {"new_poolrgn_all": zbytes / (t["new_poolrgn_all"] * 1e-3) / hbm,
-                        "new_poolrgn_bprop_all": zbytes / (t["new_poolrgn_bprop_all"] * 1e-3) / hbm,
+                        "new_poolrgn_bprop_all": 2 * zbytes / (t["new_poolrgn_bprop_all"] * 1e-3) / hbm,
                         "new_corr1ord": zbytes / (t["new_corr1ord"] * 1e-3) / hbm},
-           "note": "reference kernels recompiled for sm_100a with their own launch geometry; frac_hbm = npos*nf*4 bytes per pass "
+           "note": "reference kernels recompiled for sm_100a with their own launch geometry; frac_hbm = npos*nf*4 bytes per pass (read and written back by poolrgn_bprop, which adds into Z: twice that) "
                    "over the measured copy bandwidth (%s)" % ("measured" if "hbm_gbs" in peaks else "fallback 6650 GB/s")}
     return out
 
@@ -468,6 +474,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer stores only
         opts = None
         if args.nccl_max_ctas > 0:
             # The scan keeps one CTA on every SM (all of the SM's tensor memory); NCCL's copy CTAs take
@@ -492,7 +499,7 @@ def main():
     X = X_host.to(dev); R = R_host.to(dev)
     if nsplit:
         net.prepare_tc(args.variant)
-    scorer = ShardedScorer(net, nseq, group=None, nchunk=args.gather_chunks if world > 1 else 1)
+    scorer = ShardedScorer(net, nseq, group=None, nchunk=args.gather_chunks if world > 1 else 1, gather=args.gather)
     scores = scorer.scores
     status = scorer.status
     gathered = scorer.gathered
@@ -642,14 +649,14 @@ def main():
         gn = 1000000
         lo, hi = shard.shard_range(gn, rank, world)
         n_s = gn // world                                        # equal shards (the remainder, < world sequences, is left out)
-        sc = ShardedScorer(net, n_s, group=None, nchunk=max(1, min(args.gather_chunks, n_s // 8192)))
+        sc = ShardedScorer(net, n_s, group=None, nchunk=max(1, min(args.gather_chunks, n_s // 8192)), gather=args.gather)
         Xs, Rs = X, R[:n_s]
         for _ in range(3):
             sc.run(Xs, Rs)
         ms_s = timed(lambda: sc.run(Xs, Rs), args.steps)
         sc.check()
         strong = {"global_nseq": n_s * world, "nseq_per_gpu": n_s, "value": n_s * world * args.steps / (ms_s * 1e-3), "unit": UNIT,
-                  "ms_per_step": ms_s / args.steps, "gather_verified": sc.verify(), "chunks": sc.nchunk,
+                  "ms_per_step": ms_s / args.steps, "gather_verified": sc.verify(), "gather": sc.gather, "chunks": sc.nchunk,
                   "note": "strong scaling: total work fixed at the configuration's 1,000,000 sequences; every rank ends with all scores"}
         del sc
 

@@ -115,6 +115,7 @@ _PROTOTYPES = {
     "db_tc_weights_bytes": (c_size_t, [c_uint32, c_uint32, c_int]),
     "db_tc_prepare": (None, [P, c_uint32, c_uint32, c_int, P]),
     "db_scanpool_tc_debug": (None, [c_uint64, c_int]),
+    "db_scanpool_tc_peers": (None, [c_void_p, c_uint32, c_uint32]),
     "db_scanpool_tc": (None, [P, c_uint32, c_uint32, c_int, P, c_int, P, c_uint32, P, c_uint32, c_int,
                               P, P, P, c_uint32, P, P]),
 }

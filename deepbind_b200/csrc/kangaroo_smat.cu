@@ -337,17 +337,6 @@ poolrgn_warp_kernel(const float* __restrict__ U, unsigned nf, const uint32_t* __
 	}
 }
 
-// Do the regions ascend without overlap (each starts at or after the end of the one before)?
-// Then no two regions share a row of the unpooled maps and the backward pass may add without
-// atomics.  Writes 1 to *overlap otherwise (the caller zeroes it).
-__global__ void regions_overlap_kernel(const uint32_t* __restrict__ R, unsigned nregion, unsigned rcols, unsigned* __restrict__ overlap)
-{
-	for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x + 1; r < nregion; r += gridDim.x * blockDim.x) {
-		const unsigned prev_end = max(R[(r - 1) * rcols + 1], R[(r - 1) * rcols]);
-		if (R[r * rcols] < prev_end) *overlap = 1u;
-	}
-}
-
 template <typename T>
 __global__ void poolrgn_bprop_kernel(T* __restrict__ U, unsigned nf, const uint32_t* __restrict__ R, unsigned nregion,
                                      unsigned rcols, const T* __restrict__ P, const uint32_t* __restrict__ A, int ptype)
@@ -370,14 +359,13 @@ __global__ void poolrgn_bprop_kernel(T* __restrict__ U, unsigned nf, const uint3
 // float, unit step, nf in {4, 8, ..., 128}: a warp per region.  A lane owns four
 // neighbouring filters and every (128/nf)-th row, so one warp instruction adds a
 // contiguous 512-byte run of the unpooled maps with 16-byte vector adds: a quarter of
-// the atomic operations of the scalar kernel, each fully coalesced.
+// the atomic operations of the scalar kernel, each fully coalesced.  With disjoint regions
+// (the batch layout) every element receives one add, so the result does not depend on the
+// order; the adds resolve in L2 and the pass moves one read and one write of U through HBM.
 __global__ void __launch_bounds__(256)
 poolrgn_bprop_v4_kernel(float* __restrict__ U, unsigned nf, const uint32_t* __restrict__ R, unsigned nregion,
-                        const float* __restrict__ P, const uint32_t* __restrict__ A, int ptype, const unsigned* __restrict__ overlap)
+                        const float* __restrict__ P, const uint32_t* __restrict__ A, int ptype)
 {
-	// Disjoint regions (the batch layout): every element of U belongs to one region, hence to
-	// one warp, and is updated by plain loads and stores: deterministic, no atomic traffic.
-	const bool plain = *overlap == 0u;
 	const unsigned lane = threadIdx.x & 31, q = nf / 4, f = 4 * (lane % q), rl = lane / q, nrl = 32 / q;
 	for (unsigned r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < nregion; r += gridDim.x * (blockDim.x >> 5)) {
 		const uint2 rg = reinterpret_cast<const uint2*>(R)[r];
@@ -393,20 +381,6 @@ poolrgn_bprop_v4_kernel(float* __restrict__ U, unsigned nf, const uint32_t* __re
 			d.x /= cnt; d.y /= cnt; d.z /= cnt; d.w /= cnt;
 		}
 		float4* Uf = reinterpret_cast<float4*>(U + f);
-		if (plain) {
-			for (unsigned row = rg.x + rl; row < rg.y; row += nrl) {
-				float4 u = Uf[(size_t)row * q];
-				u.x += d.x; u.y += d.y; u.z += d.z; u.w += d.w;
-				Uf[(size_t)row * q] = u;
-			}
-			__syncwarp();                                   // the mean shares are in place before the maximum's delta is added
-			if (ptype == DB_PT_ALL && rl == 0) {
-				const uint4 a = *reinterpret_cast<const uint4*>(A + t);
-				U[a.x] += x.x; U[a.y] += x.y; U[a.z] += x.z; U[a.w] += x.w;
-			}
-			__syncwarp();
-			continue;
-		}
 		for (unsigned row = rg.x + rl; row < rg.y; row += nrl)
 			atomicAdd(Uf + (size_t)row * q, d);
 		if (ptype == DB_PT_ALL && rl == 0) {
@@ -592,12 +566,8 @@ DB_EXPORT void api_poolrgn_bprop(smat* unpooledmaps, const smat* regions, const 
 	if (unpooledmaps->dtype == DB_F32 && options->ptype != DB_PT_MAX && regions->shape.x == 2 && nf % 4 == 0 && nf <= 128 &&
 	    32 % (nf / 4) == 0 && aligned && (options->ptype != DB_PT_ALL || A)) {
 		unsigned ncta = std::min(divup(nregion, 8u), 16u * (unsigned)state().sm_count);
-		unsigned* overlap = (unsigned*)scratch(256);
-		DB_CUDA(cudaMemsetAsync(overlap, 0, 4, state().stream));
-		regions_overlap_kernel<<<elemwise_grid(nregion), 256, 0, state().stream>>>((const uint32_t*)regions->data, nregion, 2u, overlap);
-		DB_LAUNCH_CHECK();
 		poolrgn_bprop_v4_kernel<<<ncta, 256, 0, state().stream>>>((float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion,
-		                                                          (const float*)pooledmaps->data, A, options->ptype, overlap);
+		                                                          (const float*)pooledmaps->data, A, options->ptype);
 	} else if (unpooledmaps->dtype == DB_F32)
 		poolrgn_bprop_kernel<<<grid, 128, 0, state().stream>>>((float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion,
 		                                                       (unsigned)regions->shape.x, (const float*)pooledmaps->data, A, options->ptype);

@@ -52,6 +52,8 @@ static constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + 4 * TC_EPI_SETS);
 static_assert(TC_EPI_SETS == 4, "region-aligned tiles pair the four warps of a lane quarter with the two accumulator slots");
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // default deadline of a wait, clock cycles (about 0.1 s)
 
+static constexpr int DB_TC_MAX_PEERS = 8;
+
 struct tc_args {
 	const uint8_t* X; const uint32_t* R; const __nv_bfloat16* Wt; const float* bias;
 	const float* headW; const float* headB;
@@ -60,6 +62,8 @@ struct tc_args {
 	int ptype, relu;
 	unsigned f16;                   // operand type of both MMA inputs: 0 = bf16, 1 = f16 (weights prescaled by a power of two)
 	const uint32_t* maxabs;         // bit pattern of max |W|, kept behind the prepared tiles
+	float* peers[DB_TC_MAX_PEERS];  // score matrices of the ranks of a multi-GPU scan (peer-mapped), or none
+	unsigned npeer, row_off;        // this launch's region g is row row_off + g of each of them
 	unsigned long long timeout;     // clock cycles a wait may last before the CTA gives up
 	unsigned hold_operands;         // test aid: the operand encoders never announce their stage, so the issuer's wait runs out
 };
@@ -296,6 +300,18 @@ __device__ __forceinline__ float pow2_above(float bound)
 	return __uint_as_float((uint32_t)(e + 1 + 127) << 23);
 }
 
+// A score goes to the caller's matrix and, in a multi-GPU scan, straight into every rank's
+// gathered matrix over NVLink (plain peer stores; posted writes, nothing is read back): the
+// all-gather of the score shards happens inside the scan, column by column, and costs no
+// pass of its own.  The ranks synchronise after their launches before anyone reads.
+__device__ __forceinline__ void store_score(const tc_args& a, unsigned g, unsigned model, float v)
+{
+	const size_t o = (size_t)g * a.nmodel + model;
+	if (a.scores) a.scores[o] = v;
+	const size_t po = (size_t)a.row_off * a.nmodel + o;
+	for (unsigned p = 0; p < a.npeer; ++p) a.peers[p][po] = v;
+}
+
 struct pool_state {
 	float mx[4];
 	unsigned long long sm2[4];      // four packed pairs of partial sums
@@ -380,7 +396,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	// linear head of the model this filter belongs to (16 filters per model)
 	float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
 	const unsigned model = f / 16;
-	if (a.scores && f < a.nf) {
+	if ((a.scores || a.npeer) && f < a.nf) {
 		const unsigned npool = a.ptype == DB_PT_ALL ? 32u : 16u, k = f % 16;
 		if (a.ptype == DB_PT_ALL) { hw_max = a.headW[model * npool + 2 * k]; hw_sum = a.headW[model * npool + 2 * k + 1]; }
 		else if (a.ptype == DB_PT_MAX) hw_max = a.headW[model * npool + k];
@@ -423,13 +439,13 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 			if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
 			else a.pooled[o] = WANT_MAX ? pmax : second;
 		}
-		if (a.scores) {
+		if (a.scores || a.npeer) {
 			float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
 			part += __shfl_xor_sync(0xffffffffu, part, 8);
 			part += __shfl_xor_sync(0xffffffffu, part, 4);
 			part += __shfl_xor_sync(0xffffffffu, part, 2);
 			part += __shfl_xor_sync(0xffffffffu, part, 1);
-			if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
+			if ((lane & 15) == 0 && f < a.nf) store_score(a, g, model, part + hb);
 		}
 		ps.reset();
 		g += TC_EPI_SETS;
@@ -516,7 +532,7 @@ __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t t
 	const float cm = inv_wscale / ssat, ca = b0 / ssat;
 	float hw_max = 0.f, hw_sum = 0.f, hb = 0.f;
 	const unsigned model = f / 16;
-	if (a.scores && f < a.nf) {
+	if ((a.scores || a.npeer) && f < a.nf) {
 		const unsigned npool = a.ptype == DB_PT_ALL ? 32u : 16u, kk = f % 16;
 		if (a.ptype == DB_PT_ALL) { hw_max = a.headW[model * npool + 2 * kk]; hw_sum = a.headW[model * npool + 2 * kk + 1]; }
 		else if (a.ptype == DB_PT_MAX) hw_max = a.headW[model * npool + kk];
@@ -570,13 +586,13 @@ __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t t
 				if (a.ptype == DB_PT_ALL) reinterpret_cast<float2*>(a.pooled)[o] = make_float2(pmax, second);
 				else a.pooled[o] = WANT_MAX ? pmax : second;
 			}
-			if (a.scores) {
+			if (a.scores || a.npeer) {
 				float part = (WANT_MAX ? hw_max * pmax : 0.f) + (WANT_SUM ? hw_sum * second : 0.f);
 				part += __shfl_xor_sync(0xffffffffu, part, 8);
 				part += __shfl_xor_sync(0xffffffffu, part, 4);
 				part += __shfl_xor_sync(0xffffffffu, part, 2);
 				part += __shfl_xor_sync(0xffffffffu, part, 1);
-				if ((lane & 15) == 0 && f < a.nf) a.scores[(size_t)g * a.nmodel + model] = part + hb;
+				if ((lane & 15) == 0 && f < a.nf) store_score(a, g, model, part + hb);
 			}
 		}
 		if (sub >= kt) {                                // no region of this tile is ours: hand it back untouched
@@ -827,8 +843,23 @@ static void tc_mode(int precision, unsigned& nsplit, unsigned& f16)
 // default) and whether the operand encoders withhold their "stage ready" signal, which
 // makes the issuer's first wait run out with no MMA in flight.  Nothing faults: the
 // kernel reports status 1 and returns.
+static thread_local float* g_tc_peers[DB_TC_MAX_PEERS];
+static thread_local unsigned g_tc_npeer = 0, g_tc_row_off = 0;
 static thread_local unsigned long long g_tc_timeout = 0;
 static thread_local unsigned g_tc_hold_operands = 0;
+
+DB_EXPORT void db_scanpool_tc_peers(float* const* peer_scores, uint32_t npeer, uint32_t row_offset)
+{
+	DB_API_TRY_NODEV
+	DB_REQUIRE(npeer <= (uint32_t)DB_TC_MAX_PEERS, "ValueError: at most %d peer score matrices (got %u)", DB_TC_MAX_PEERS, npeer);
+	DB_REQUIRE(npeer == 0 || peer_scores != nullptr, "ValueError: db_scanpool_tc_peers got a NULL table");
+	for (unsigned p = 0; p < npeer; ++p) {
+		DB_REQUIRE(peer_scores[p] != nullptr, "ValueError: peer score matrix %u is NULL", p);
+		g_tc_peers[p] = peer_scores[p];
+	}
+	g_tc_npeer = npeer; g_tc_row_off = row_offset;
+	DB_API_CATCH
+}
 
 DB_EXPORT void db_scanpool_tc_debug(uint64_t timeout_clocks, int hold_operands)
 {
@@ -892,6 +923,8 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int preci
 	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.m = m; a.KC = KC; a.nsplit = nsplit;
 	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu; a.f16 = f16;
 	a.maxabs = reinterpret_cast<const uint32_t*>(static_cast<const unsigned char*>(Wt) + (size_t)ntile * nsplit * KC * 2048);
+	a.npeer = scores ? g_tc_npeer : 0u; a.row_off = g_tc_row_off;
+	for (unsigned p = 0; p < a.npeer; ++p) a.peers[p] = g_tc_peers[p];
 	a.timeout = g_tc_timeout ? g_tc_timeout : TC_TIMEOUT;
 	a.hold_operands = g_tc_hold_operands;
 	// Sequence chunks: about 8 waves of CTAs over the SMs (one CTA per SM), with the CTA

@@ -309,7 +309,7 @@ class DeepBindNet(object):
             out[s:e].copy_(self.score(X, R[s:e]))
         return out
 
-    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False, npiece=16, on_piece=None):
+    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False, npiece=16, on_piece=None, before_piece=None):
         """The call a user makes for scoring: ordinal batch in (pinned) host
         memory -> scores in (pinned) host memory.  Mirrors what
         kangaroo.predict does per batch (code/libs/kangaroo/kangaroo/predict.py:168-176):
@@ -317,7 +317,8 @@ class DeepBindNet(object):
         tensor-core path the batch is cut into ``npiece`` pieces of regions
         (``shard.shard_range(nseq, c, npiece)``) and ``on_piece(lo, hi)``, if given, is
         called right after piece [lo, hi) was enqueued on the current stream (a caller
-        with several GPUs starts that piece's all-gather there)."""
+        with several GPUs starts that piece's all-gather there); ``before_piece(lo, hi)``
+        is called just before the piece's scan is enqueued."""
         if dev_bufs is None:
             dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.dev),
                         torch.empty(R_host.shape, dtype=torch.int32, device=self.dev),
@@ -352,6 +353,8 @@ class DeepBindNet(object):
             for c in range(npiece):
                 lo, hi = cuts[c], cuts[c + 1]
                 cur.wait_event(ups[c])
+                if before_piece is not None:
+                    before_piece(lo, hi)
                 self.score_tc(X, R[lo:hi], check=False, out=out[lo:hi], status=self._status)
                 if on_piece is not None:
                     on_piece(lo, hi)
@@ -367,6 +370,8 @@ class DeepBindNet(object):
         X.copy_(X_host, non_blocking=True)
         R.copy_(R_host, non_blocking=True)
         if tc:
+            if before_piece is not None:
+                before_piece(0, R.shape[0])
             self.score_tc(X, R, check=False, out=out, status=self._status)
         else:
             self.score_chunked(X, R, out, chunk)

@@ -172,19 +172,43 @@ class ShardedScorer(object):
     of kangaroo.predict fanned out over the devices of one box (predict.py:484-492)
     with the gather overlapped.  Buffers are allocated once and reused by every call.
 
+    ``gather="peer"`` does without the collective: the gathered matrix of every rank
+    lies in symmetric memory (torch.distributed._symmetric_memory, every rank's buffer
+    mapped into every process), the scan kernel stores each score straight into all of
+    them over NVLink while it runs (``db_scanpool_tc_peers``), one launch scans the whole
+    shard, and a one-element all-reduce afterwards is the barrier that tells every rank
+    that all stores have landed.  No second pass over the scores, no NCCL kernels
+    competing with the scan for SMs.  Only plain peer stores are used (no multicast).
+
     ``net``: a DeepBindNet with the in-kernel linear head (no hidden layer) whose
     tensor-core weights were prepared; ``nseq``: regions per rank (the same on every
     rank)."""
 
-    def __init__(self, net, nseq, group=None, nchunk=8):
+    def __init__(self, net, nseq, group=None, nchunk=8, gather="nccl"):
         import torch.distributed as dist
         self.net, self.group, self.nseq = net, group, int(nseq)
         self.rank, self.world = shard.rank_world(group)
         self.nchunk = max(1, min(int(nchunk), self.nseq))
         self.scores = torch.empty((self.nseq, net.I), dtype=torch.float32, device=net.dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=net.dev)
-        self.gathered = self.chunks = None
-        if self.world > 1:
+        self.gathered = self.chunks = self._peers = None
+        if gather not in ("nccl", "peer"):
+            raise ValueError("gather must be 'nccl' or 'peer', got %r" % (gather,))
+        self.gather = gather if self.world > 1 else "nccl"
+        if self.gather == "peer":
+            import ctypes
+            import torch.distributed._symmetric_memory as symm
+            if self.world > 8:
+                raise ValueError("the peer gather serves at most 8 ranks (one box)")
+            self.gathered = symm.empty((self.nseq * self.world, net.I), dtype=torch.float32, device=net.dev)
+            self._symm = symm.rendezvous(self.gathered, dist.group.WORLD if group is None else group)
+            ptrs = [int(q) for q in self._symm.buffer_ptrs]
+            if len(ptrs) != self.world or ptrs[self.rank] != self.gathered.data_ptr():
+                raise RuntimeError("symmetric memory rendezvous returned an unexpected buffer table")
+            self._peers = (ctypes.c_void_p * self.world)(*ptrs)
+            self._flag = torch.zeros(1, dtype=torch.int32, device=net.dev)
+            self.scores = self.gathered[self.rank * self.nseq:(self.rank + 1) * self.nseq]
+        elif self.world > 1:
             self.gathered = torch.empty((self.nseq * self.world, net.I), dtype=torch.float32, device=net.dev)
             self.chunks = [self.gathered[self.world * lo:self.world * hi] for lo, hi in
                            (shard.shard_range(self.nseq, c, self.nchunk) for c in range(self.nchunk))]
@@ -200,9 +224,30 @@ class ShardedScorer(object):
             net.score_tc(X, R[lo:hi], check=False, out=self.scores[lo:hi], status=self.status)
         if self.world == 1:
             rows(0, self.nseq)
+        elif self.gather == "peer":
+            self._scan_to_peers(lambda: rows(0, self.nseq), 0)
+            self._peer_barrier()
         else:
             shard.chunked_gather(rows, self.scores, self.chunks, self.group)
         return self.scores
+
+    def _scan_to_peers(self, launch, row_lo):
+        """Runs ``launch`` (scans that write rows row_lo.. of this rank's shard) with the
+        peer stores switched on; the scan's own output is its rows of this rank's
+        gathered matrix, the stores go to the other ranks' copies."""
+        from ._lib import load as dll
+        others = [q for r, q in enumerate(self._peers) if r != self.rank]
+        tab = (type(self._peers)._type_ * len(others))(*others)
+        dll().db_scanpool_tc_peers(tab, len(others), self.rank * self.nseq + row_lo)
+        try:
+            launch()
+        finally:
+            dll().db_scanpool_tc_peers(None, 0, 0)
+
+    def _peer_barrier(self):
+        """Stream-ordered barrier: the one-element all-reduce of a rank completes only
+        after every rank's scan, enqueued before it, has finished."""
+        self._dist.all_reduce(self._flag, group=self.group)
 
     def run_host(self, X_host, R_host, out_host, dev_bufs=None):
         """The same from (pinned) host buffers to (pinned) host scores of this rank's
@@ -213,6 +258,21 @@ class ShardedScorer(object):
             dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.net.dev),
                         torch.empty(R_host.shape, dtype=torch.int32, device=self.net.dev), self.scores)
         works = []
+        if self.gather == "peer":
+            from ._lib import load as dll
+            others = [q for r, q in enumerate(self._peers) if r != self.rank]
+            tab = (type(self._peers)._type_ * len(others))(*others)
+
+            def piece_rows(lo, hi):              # predict_host calls this before it enqueues piece lo..hi
+                dll().db_scanpool_tc_peers(tab, len(others), self.rank * self.nseq + lo)
+            try:
+                self.net.predict_host(X_host, R_host, out_host, dev_bufs=(dev_bufs[0], dev_bufs[1], self.scores), tc=True,
+                                      npiece=self.nchunk, before_piece=piece_rows)
+            finally:
+                dll().db_scanpool_tc_peers(None, 0, 0)
+            self._peer_barrier()
+            torch.cuda.current_stream().synchronize()
+            return out_host
 
         def gather_piece(lo, hi):
             c = len(works)
@@ -237,6 +297,8 @@ class ShardedScorer(object):
         """[world * nseq, I] in rank-major row order (a copy out of the chunk buffers)."""
         if self.world == 1:
             return self.scores
+        if self.gather == "peer":
+            return self.gathered
         return shard.gathered_rows(self.chunks, self.nseq, self.world)
 
     def verify(self):

@@ -274,6 +274,15 @@ void db_scanpool_tc(const void* prepared, uint32_t m, uint32_t nf, int precision
                     const uint8_t* X, uint32_t npos, const uint32_t* regions, uint32_t nregion, int ptype,
                     float* pooled, const float* headW, const float* headB, uint32_t nmodel, float* scores,
                     int* status);
+/* Multi-GPU scan (no counterpart: the reference gathers per-device results on the host,
+ * kangaroo/predict.py:484-492).  For later db_scanpool_tc launches of the calling thread that
+ * produce scores, every score is also stored into each of the `npeer` (<= 8) matrices
+ * peer_scores[p] ([rows, nmodel] f32, device memory of this or of a peer GPU mapped into this
+ * process), at row row_offset + region index: the all-gather of the ranks' score shards done
+ * by the scan kernel itself with plain peer stores over NVLink.  The ranks must synchronise
+ * (e.g. a barrier collective on the same stream) after their launches and before reading.
+ * npeer = 0 switches it off. */
+void db_scanpool_tc_peers(float* const* peer_scores, uint32_t npeer, uint32_t row_offset);
 /* Test aid (no counterpart): for later db_scanpool_tc launches of the calling thread,
  * the deadline of the kernel's internal waits in clock cycles (0 = default, about 0.1 s)
  * and, with hold_operands != 0, operand encoders that never signal "stage ready", so

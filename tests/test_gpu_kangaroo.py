@@ -108,6 +108,32 @@ def test_poolrgn_forward_and_backward(cuda, orc, dtype, ptype, nf, step):
     assert np.array_equal(dU.asnumpy(), want)
 
 
+def test_poolrgn_bprop_overlapping_and_disjoint_regions(cuda, orc):
+    """Disjoint ascending regions take plain read-modify-writes: two runs agree bit for bit and equal
+    the oracle; overlapping (or descending) regions fall back to atomic adds and still give the sums."""
+    import torch
+    from deepbind_b200 import smat as sm, kangaroo_smat as ks
+    rng = np.random.default_rng(5)
+    nf, nrow = 16, 4000
+    dis = np.array([[i * 40, i * 40 + 33] for i in range(100)], np.uint32)
+    ovl = np.array([[0, 300], [100, 180], [150, 900], [2000, 2100], [1500, 2050]], np.uint32)
+    for R, exact in ((dis, True), (ovl, False)):
+        U0 = (rng.standard_normal((nrow, nf)) * 0.1).astype(f32)           # the operator accumulates into what is there
+        act = np.maximum(rng.standard_normal((nrow, nf)), 0).astype(f32)
+        P, A = orc.poolrgn(act, R, "all", True)
+        dP = rng.standard_normal(P.shape).astype(f32)
+        want = orc.poolrgn_bprop(U0.copy(), R, dP, A, "all")
+        runs = []
+        for _ in range(2):
+            dU = sm.asarray(U0)
+            ks.poolrgn_bprop(dU, sm.asarray(R), sm.asarray(dP), sm.asarray(A), "all")
+            runs.append(dU.asnumpy())
+        if exact:
+            assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], want)
+        else:
+            assert np.max(np.abs(runs[0] - want)) <= 1e-5 * np.abs(want).max()
+
+
 def test_poolrgn_validation_messages(cuda):
     from deepbind_b200 import smat as sm, kangaroo_smat as ks, SmatException
     from deepbind_b200 import _lib

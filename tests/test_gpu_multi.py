@@ -23,7 +23,8 @@ def _init(rank, world, port):
     import torch
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     return torch, dist
@@ -55,6 +56,17 @@ def _scorer_worker(rank, world, port, out_dir):
     Xo, Ro = synth.uniform_batch(nseq, 101, m, seed=100 + other)
     want = net.score_tc(torch.from_numpy(Xo).cuda(), torch.from_numpy(Ro.view(np.int32)).cuda())
     ok = ok and float((full[other * nseq:(other + 1) * nseq] - want).abs().max()) <= 1e-6 * float(want.abs().max())
+    # the gather done by the scan kernel itself (peer stores into symmetric memory): same matrix
+    sp = ShardedScorer(net, nseq, nchunk=5, gather="peer")
+    sp.run(X, R)
+    torch.cuda.synchronize()
+    sp.check()
+    ok = ok and sp.verify() and bool(torch.equal(sp.all_scores(), full))
+    sp.gathered.zero_()
+    torch.cuda.synchronize(); dist.barrier()
+    out_host.zero_()
+    sp.run_host(X_host, R_host, out_host)
+    ok = ok and sp.verify() and bool(torch.equal(sp.all_scores(), full)) and bool(torch.equal(out_host, sp.scores.cpu()))
     # predict() over the group: every rank gets all rows
     rng = np.random.default_rng(5)
     seqs = ["".join(rng.choice(list("ACGT"), size=int(n))) for n in rng.integers(30, 90, size=101)]
