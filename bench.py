@@ -61,6 +61,8 @@ def parse():
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the short runs of the other benchmark configurations")
+    ap.add_argument("--only-reference-kernels", action="store_true",
+                    help="run only the comparison of the unfused operators with the reference's own kernels and print its JSON")
     return ap.parse_args()
 
 
@@ -487,6 +489,9 @@ def main():
                 opts = None
         dist.init_process_group("nccl", device_id=dev, **({"pg_options": opts} if opts is not None else {}))
     dll = _lib.load()
+    if args.only_reference_kernels:
+        print(json.dumps({"reference_kernels": reference_kernels(dev)}))
+        return
 
     I, nseq = args.nmodel, args.nseq
     nsplit, dtype_name, tol = VARIANTS[args.variant]

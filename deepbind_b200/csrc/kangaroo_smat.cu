@@ -277,61 +277,95 @@ __global__ void poolrgn_kernel(const T* __restrict__ U, unsigned nf, const uint3
 	}
 }
 
-// float, unit step, nf in {4, 8, 16, 32}: a warp per region.  The rows of a
-// region are contiguous in memory, so the 32 lanes fetch 512 contiguous bytes per load
-// instruction (a lane owns four neighbouring maps of every (128/nf)-th row), four loads in
-// flight per lane, and park them in the warp's slice of shared memory; then one lane per map
-// walks the staged rows in order: strict '>' (first maximum wins) and the running sum in row
-// order, exactly as the scalar kernel.  The loads are what bounds this operator (npos*nf*4
-// bytes of HBM); the ordered reduction rides along.
-static constexpr int PRW = 8;                    // warps (regions) per CTA
-static constexpr int PRB = 2048;                 // bytes staged per warp and step (4 loads x 512 B)
+// float, unit step, NF in {4, 8, 16, 32}: a warp takes 32/NF regions at a time, lane =
+// (region, map), so that the ordered reduction keeps all 32 lanes busy.  The rows of a
+// region are contiguous in memory: for each of its regions the warp copies the next 16 rows
+// into its slice of shared memory with 16-byte cp.async (512 contiguous bytes per
+// instruction, L2 only), two buffers deep, so that the copies of the next step are in flight
+// while every lane walks the staged rows of its own region and map in order: strict '>'
+// (first maximum wins) and the running sum in row order, exactly as the scalar kernel.  The
+// reads are what should bound this operator (npos*nf*4 bytes of HBM); what is left above
+// them is the issue cost of the ordered reduction (about five instructions per row).
+static constexpr int PRW = 8;                    // warps per CTA
 
+__device__ __forceinline__ void pool_cp16(void* dst, const void* src)
+{
+	unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(src) : "memory");
+}
+
+template <int NF, int PRR, int NBUF>             // maps; rows staged per region and step; buffers
 __global__ void __launch_bounds__(32 * PRW)
-poolrgn_warp_kernel(const float* __restrict__ U, unsigned nf, const uint32_t* __restrict__ R, unsigned nregion,
+poolrgn_warp_kernel(const float* __restrict__ U, const uint32_t* __restrict__ R, unsigned nregion,
                     float* __restrict__ P, uint32_t* __restrict__ A, int ptype)
 {
-	__shared__ __align__(16) float stage[PRW][PRB / 4];
+	constexpr int NSUB = 32 / NF;                                  // regions per warp
+	constexpr int Q = NF / 4;                                      // 16-byte units per row
+	constexpr int PRL = PRR * Q / 32 > 0 ? PRR * Q / 32 : 1;       // copies per lane, region and step
+	__shared__ __align__(16) float stage[PRW][NBUF][NSUB][PRR * NF];
 	const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-	const unsigned q = nf / 4;                                     // 16-byte units per row
-	const unsigned rows_step = (PRB / 16) / q;                     // rows staged per step
-	float* mine = stage[warp];
-	for (unsigned r = blockIdx.x * PRW + warp; r < nregion; r += gridDim.x * PRW) {
-		const uint2 rg = reinterpret_cast<const uint2*>(R)[r];
-		const unsigned first = rg.x, last = rg.y;
+	const unsigned sub = lane / NF, f = lane % NF;
+	for (unsigned r0 = (blockIdx.x * PRW + warp) * NSUB; r0 < nregion; r0 += gridDim.x * PRW * NSUB) {
+		// bounds of the warp's regions (lane s fetches region r0+s), then this lane's own
+		uint2 rg = make_uint2(0u, 0u);
+		if (lane < NSUB && r0 + lane < nregion) rg = reinterpret_cast<const uint2*>(R)[r0 + lane];
+		unsigned fs[NSUB], ls[NSUB], longest = 0;
+		#pragma unroll
+		for (int s = 0; s < NSUB; ++s) {
+			fs[s] = __shfl_sync(0xffffffffu, rg.x, s); ls[s] = __shfl_sync(0xffffffffu, rg.y, s);
+			longest = max(longest, ls[s] > fs[s] ? ls[s] - fs[s] : 0u);
+		}
+		const unsigned first = __shfl_sync(0xffffffffu, rg.x, sub), last = __shfl_sync(0xffffffffu, rg.y, sub);
+		const bool live = r0 + sub < nregion;
+		auto fetch = [&](unsigned off, unsigned buf) {             // always commits a group, an empty one past the end
+			#pragma unroll
+			for (int s = 0; s < NSUB; ++s) {
+				const unsigned row = fs[s] + off;
+				const unsigned units = row < ls[s] ? min((unsigned)PRR, ls[s] - row) * Q : 0u;
+				const float4* src = reinterpret_cast<const float4*>(U + (size_t)row * NF);
+				#pragma unroll
+				for (int j = 0; j < PRL; ++j)
+					if (lane + 32 * j < units) pool_cp16(reinterpret_cast<float4*>(stage[warp][buf][s]) + lane + 32 * j, src + lane + 32 * j);
+			}
+			asm volatile("cp.async.commit_group;" ::: "memory");
+		};
+		#pragma unroll
+		for (int b = 0; b < NBUF - 1; ++b) fetch(1 + b * PRR, b);
 		float x = 0.f, y = 0.f;
 		unsigned xi = first;
-		if (lane < nf) { x = U[(size_t)first * nf + lane]; y = x; }             // the first row is read even if the region is empty
-		for (unsigned row = first + 1; row < last; row += rows_step) {
-			const unsigned nrow = min(rows_step, last - row);
-			const float4* src = reinterpret_cast<const float4*>(U + (size_t)row * nf);
-			const unsigned units = nrow * q;
-			float4 v[4];
-			#pragma unroll
-			for (int j = 0; j < 4; ++j) {
-				const unsigned u = lane + 32 * j;
-				v[j] = u < units ? src[u] : make_float4(0.f, 0.f, 0.f, 0.f);
-			}
-			#pragma unroll
-			for (int j = 0; j < 4; ++j) reinterpret_cast<float4*>(mine)[lane + 32 * j] = v[j];
+		if (live) { x = U[(size_t)first * NF + f]; y = x; }                     // the first row is read even if the region is empty
+		unsigned buf = 0;
+		for (unsigned off = 1; off < longest; off += PRR, buf = buf + 1 == NBUF ? 0 : buf + 1) {
+			fetch(off + (NBUF - 1) * PRR, buf == 0 ? NBUF - 1 : buf - 1);
+			asm volatile("cp.async.wait_group %0;" :: "n"(NBUF - 1) : "memory");
 			__syncwarp();
-			if (lane < nf) {
+			const unsigned row = first + off;
+			const unsigned nrow = (live && row < last) ? min((unsigned)PRR, last - row) : 0u;
+			const float* col = stage[warp][buf][sub] + f;
+			if (nrow == PRR) {
+				#pragma unroll
+				for (unsigned k = 0; k < PRR; ++k) {
+					const float w = col[k * NF];
+					if (w > x) { x = w; xi = row + k; }
+					y += w;
+				}
+			} else {
 				for (unsigned k = 0; k < nrow; ++k) {
-					const float w = mine[k * nf + lane];
+					const float w = col[k * NF];
 					if (w > x) { x = w; xi = row + k; }
 					y += w;
 				}
 			}
-			__syncwarp();
+			__syncwarp();                                                       // all lanes are done with this buffer before it is refilled
 		}
-		if (lane < nf) {
-			const size_t t = (size_t)r * nf + lane;
+		if (live) {
+			const size_t t = (size_t)(r0 + sub) * NF + f;
 			const unsigned cnt = last - first;
 			switch (ptype) {
-			case DB_PT_MAX: P[t] = x; if (A) A[t] = xi * nf + lane; break;
+			case DB_PT_MAX: P[t] = x; if (A) A[t] = xi * NF + f; break;
 			case DB_PT_AVG: P[t] = y / (float)cnt; break;
 			case DB_PT_SUM: P[t] = y; break;
-			default:        P[2*t] = x; P[2*t+1] = y / (float)cnt; if (A) A[t] = xi * nf + lane; break;
+			default:        P[2*t] = x; P[2*t+1] = y / (float)cnt; if (A) A[t] = xi * NF + f; break;
 			}
 		}
 	}
@@ -538,9 +572,18 @@ DB_EXPORT void api_poolrgn(const smat* unpooledmaps, const smat* regions, smat* 
 	uint32_t* A = pooledmaps_argmax ? (uint32_t*)pooledmaps_argmax->data : nullptr;
 	const bool vec = unpooledmaps->dtype == DB_F32 && regions->shape.x == 2 && nf % 4 == 0 && nf <= 32 && 32 % nf == 0 &&
 	                 ((uintptr_t)unpooledmaps->data & 15) == 0 && ((uintptr_t)regions->data & 7) == 0;
-	if (vec)
-		poolrgn_warp_kernel<<<std::min(divup(nregion, (unsigned)PRW), 32u * (unsigned)state().sm_count), 32 * PRW, 0, state().stream>>>(
-			(const float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion, (float*)pooledmaps->data, A, options->ptype);
+	if (vec) {
+		const unsigned ncta = std::min(divup(nregion, (unsigned)PRW * (32u / nf)), 32u * (unsigned)state().sm_count);
+#define DB_POOL_LAUNCH(NF_) poolrgn_warp_kernel<NF_, 16, 2><<<ncta, 32 * PRW, 0, state().stream>>>( \
+			(const float*)unpooledmaps->data, (const uint32_t*)regions->data, nregion, (float*)pooledmaps->data, A, options->ptype)
+		switch (nf) {
+		case 4:  DB_POOL_LAUNCH(4); break;
+		case 8:  DB_POOL_LAUNCH(8); break;
+		case 16: DB_POOL_LAUNCH(16); break;
+		default: DB_POOL_LAUNCH(32); break;
+		}
+#undef DB_POOL_LAUNCH
+	}
 	else if (unpooledmaps->dtype == DB_F32)
 		poolrgn_kernel<<<grid, 128, 0, state().stream>>>((const float*)unpooledmaps->data, nf, (const uint32_t*)regions->data, nregion,
 		                                                 (unsigned)regions->shape.x, (float*)pooledmaps->data, A, options->ptype);
