@@ -36,6 +36,18 @@ class c_corr1ord_options_t(Structure):
     _fields_ = [("padmode", c_int), ("nchannel", c_uint32)]
 
 
+class c_ministep_args(Structure):
+    """struct db_ministep_args of include/deepbind_b200.h."""
+    _fields_ = [(k, ctypes.c_uint32) for k in ("nmodel", "nfilt", "m", "ptype", "hidden", "loss_kind", "strand_pairs", "B",
+                                               "max_rows", "npos")] + \
+               [("X", ctypes.c_void_p), ("X_stride", ctypes.c_size_t), ("R", ctypes.c_void_p), ("R_stride", ctypes.c_size_t),
+                ("Y", ctypes.c_void_p), ("Y_stride", ctypes.c_size_t), ("dropmask", ctypes.c_void_p), ("mask_stride", ctypes.c_size_t),
+                ("counters", ctypes.c_void_p), ("order", ctypes.c_void_p), ("nbatch", ctypes.c_uint32)] + \
+               [(k, ctypes.c_void_p) for k in ("P", "PL", "mP", "dP", "drate", "mrate", "decay")] + \
+               [(k, ctypes.c_uint32) for k in ("off_Wscan", "off_bscan", "off_W1", "off_b1", "off_W2", "off_b2")] + \
+               [("loss", ctypes.c_void_p), ("status", ctypes.c_void_p)]
+
+
 class c_poolrgn_options_t(Structure):
     _fields_ = [("ptype", c_int)]
 
@@ -107,6 +119,10 @@ _PROTOTYPES = {
     "db_minibatch_fetch": (None, [P, P, c_uint32, P, P, c_size_t, P, P, c_size_t, P, P, c_size_t]),
     "db_head_max_batch": (c_uint32, [c_uint32, c_uint32]),
     "db_head_train": (None, [c_uint32, c_uint32, c_uint32, c_int, c_int, c_uint32, P, P, P, P, P, P, P, P, P, P, P, P, P]),
+    "db_ministep_supported": (c_int, [POINTER(c_ministep_args)]),
+    "db_ministep_scratch_bytes": (c_size_t, [POINTER(c_ministep_args)]),
+    "db_ministep_lookahead": (None, [P, P, P, P, c_size_t]),
+    "db_ministep": (None, [POINTER(c_ministep_args)]),
     "db_batch_bytes": (c_size_t, [c_uint32, c_size_t, c_uint32, c_int]),
     "db_build_batch": (None, [P, P, c_uint32, c_uint32, c_int, P, P]),
     "db_build_windows": (None, [P, P, P, c_uint32, c_uint32, c_uint32, c_uint32, c_uint32, c_int, P, P]),
@@ -120,7 +136,8 @@ _PROTOTYPES = {
                               P, P, P, c_uint32, P, P]),
 }
 
-_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count", "db_scratch_bytes"}
+_NO_ERROR_CHECK = {"api_get_last_error", "api_clear_last_error", "api_device_count", "api_get_stream", "api_launch_count", "db_scratch_bytes",
+                   "db_ministep_supported", "db_ministep_scratch_bytes"}
 
 
 class _SafeFunc(object):

@@ -53,6 +53,7 @@ static_assert(TC_EPI_SETS == 4, "region-aligned tiles pair the four warps of a l
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // default deadline of a wait, clock cycles (about 0.1 s)
 
 static constexpr int DB_TC_MAX_PEERS = 8;
+static constexpr unsigned TC_RING_K = 8;         // regions per tile the score ring of a multi-GPU scan holds
 
 struct tc_args {
 	const uint8_t* X; const uint32_t* R; const __nv_bfloat16* Wt; const float* bias;
@@ -519,7 +520,8 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 template <bool WANT_MAX, bool WANT_SUM, bool RELU>
 __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t tmem_base, uint64_t* t_full, uint64_t* t_empty,
                                                     volatile int* abort_flag, unsigned tile, unsigned g_first, unsigned nreg,
-                                                    unsigned P, unsigned S, unsigned k, unsigned warp, unsigned lane)
+                                                    unsigned P, unsigned S, unsigned k, unsigned warp, unsigned lane,
+                                                    float* ring, unsigned* ring_cnt)
 {
 	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
 	const unsigned set = (warp - TC_EPI_WARP0) >> 2;
@@ -592,7 +594,34 @@ __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t t
 				part += __shfl_xor_sync(0xffffffffu, part, 4);
 				part += __shfl_xor_sync(0xffffffffu, part, 2);
 				part += __shfl_xor_sync(0xffffffffu, part, 1);
-				if ((lane & 15) == 0 && f < a.nf) store_score(a, g, model, part + hb);
+				if (a.npeer && k <= TC_RING_K) {
+					// Multi-GPU scan: the eight scores of this region and filter tile (two per lane
+					// quarter) meet in shared memory, and the warp that brings the last pair writes
+					// them as one 32-byte run to this rank's matrix and to every peer's: an NVLink
+					// write packet per (region, tile, peer) instead of four small ones.  The entry of
+					// tile t is free again by tile t+4: a warp reaches tile t+4 only after all eight
+					// warps of its slot have handed back tile t+2, which each does after its deposit
+					// (and, for the last arriver, its stores) of tile t.
+					float* e = ring + ((t & 3u) * TC_RING_K + j) * 8u;
+					if ((lane & 15) == 0) e[q4 * 2 + (lane >> 4)] = part + hb;
+					__syncwarp();
+					unsigned last = 0;
+					if (lane == 0) {
+						__threadfence_block();
+						last = atomicAdd(&ring_cnt[(t & 3u) * TC_RING_K + j], 1u) == 3u ? 1u : 0u;
+						if (last) { ring_cnt[(t & 3u) * TC_RING_K + j] = 0u; __threadfence_block(); }
+					}
+					if (__shfl_sync(0xffffffffu, last, 0)) {
+						const unsigned col = tile * 8u + (lane & 7u);
+						const float v = e[lane & 7u];
+						if (col < a.nmodel) {
+							const size_t o = (size_t)g * a.nmodel + col;
+							if (a.scores && lane < 8) a.scores[o] = v;
+							const size_t po = (size_t)a.row_off * a.nmodel + o;
+							for (unsigned p = lane >> 3; p < a.npeer; p += 4) a.peers[p][po] = v;
+						}
+					}
+				} else if ((lane & 15) == 0 && f < a.nf) store_score(a, g, model, part + hb);
 			}
 		}
 		if (sub >= kt) {                                // no region of this tile is ours: hand it back untouched
@@ -617,6 +646,8 @@ scanpool_tc_kernel(const tc_args a)
 	__shared__ uint32_t tmem_base_s;
 	__shared__ unsigned rows_s[2], blk_ok[2];
 	__shared__ int abort_s;
+	__shared__ __align__(16) float score_ring[4 * TC_RING_K * 8];
+	__shared__ unsigned score_ring_cnt[4 * TC_RING_K];
 	volatile int* abort_flag = &abort_s;
 
 	const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -626,6 +657,7 @@ scanpool_tc_kernel(const tc_args a)
 
 	// A CTA of a launch that has already failed returns at once.  One thread reads
 	// the status word so that the whole CTA takes the same decision.
+	if (threadIdx.x < 4 * TC_RING_K) score_ring_cnt[threadIdx.x] = 0u;
 	if (threadIdx.x == 0) {
 		abort_s = *reinterpret_cast<volatile int*>(a.status);
 		rows_s[0] = a.R[2 * g_first];
@@ -771,7 +803,7 @@ scanpool_tc_kernel(const tc_args a)
 	} else {
 		// ------------------------------------------------------------ epilogue
 		#define TC_EPI(MX, SM, RL) do { \
-			if (uni) tc_epilogue_uniform<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, nreg, P0, S0, kreg, warp, lane); \
+			if (uni) tc_epilogue_uniform<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, nreg, P0, S0, kreg, warp, lane, score_ring, score_ring_cnt); \
 			else tc_epilogue<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, g_last, row_lo, row_hi, warp, lane); } while (0)
 		const bool wm = a.ptype == DB_PT_MAX || a.ptype == DB_PT_ALL, ws = a.ptype != DB_PT_MAX;
 		if (a.relu) { if (wm && ws) TC_EPI(true, true, true); else if (wm) TC_EPI(true, false, true); else TC_EPI(false, true, true); }

@@ -13,6 +13,8 @@ forward, backward and the Nesterov update entirely through libdeepbind_b200.so.
 It is the composite the benchmark and parity tests drive; the node/plug graph
 engine of the reference is not reproduced here.
 """
+import ctypes
+
 import numpy as np
 import torch
 
@@ -273,6 +275,12 @@ class DeepBindNet(object):
                      grad=lambda: out.setdefault("loss", self.grads(X, R, Y, dropmask)), nesterov=True)
         return out["loss"]
 
+    def ministep(self, X, R, Y, dropmask=None, order=None, max_rows=None):
+        """The two-launch training step over a minibatch or a device-resident dataset
+        (see :class:`MiniStep`); None when the model or the shapes are outside it."""
+        ms = MiniStep(self, X, R, Y, dropmask, order, max_rows)
+        return ms if ms.supported else None
+
     # ------------------------------------------------------ tensor-core scoring
     def prepare_tc(self, precision="f16x2"):
         """Prepares the filter bank for the tcgen05 scan (redo after a weight change)."""
@@ -453,3 +461,91 @@ class DeepBindNet(object):
 
     def params_numpy(self, of="P"):
         return {k: self.view(k, of).detach().cpu().numpy().reshape(self.shapes[k]) for k in self.names}
+
+
+POOL_CODE = {"max": 0, "avg": 1, "sum": 2, "all": 3}
+
+
+class MiniStep(object):
+    """One Nesterov step of a small model as two launches (``db_ministep``): a CTA per
+    (sample or strand pair, model) runs the whole layer chain forward and backward for its
+    sample in shared memory, and an update kernel adds the samples' gradient shares, applies
+    L1 decay and the update of deepity_smat/gradstep.cu:41-72 and writes the next step's
+    look-ahead parameters -- against seven launches of the operator-fused path
+    (:meth:`DeepBindNet.train_step`), whose latencies are what a small step consists of.
+
+    ``X`` [npos] u8, ``R`` [B, 2], ``Y`` [B, I], ``dropmask`` [B, npool*I] bool: one
+    minibatch; or each with a leading axis [nbatch, ...]: a device-resident dataset that the
+    steps walk by themselves (``order``: optional int32 [nbatch] visiting order; a mask
+    without the leading axis is shared by all minibatches, e.g. redrawn per step by a kernel
+    in front).  The step counter lives on the device (``counters``).  Gradients land in
+    ``net.dP``, the loss [I] in ``loss``; ``net.P`` holds the parameters after every step
+    as the reference would (the look-ahead copy is ``PL``).  ``status`` is 2 after a step
+    that met an empty region or one longer than ``max_rows``."""
+
+    def __init__(self, net, X, R, Y, dropmask=None, order=None, max_rows=None):
+        self.net = net
+        dll = _lib.load()
+        stacked = X.dim() == 2
+        B = int(R.shape[-2])
+        if max_rows is None:
+            Rh = R.view(torch.int32).reshape(-1, 2).cpu().numpy().astype(np.int64)
+            max_rows = int((Rh[:, 1] - Rh[:, 0]).max()) if len(Rh) else 1
+        self.PL = torch.empty_like(net.P)
+        self.loss = torch.zeros(net.I, dtype=torch.float32, device=net.dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=net.dev)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=net.dev)
+        self._keep = (X, R, Y, dropmask, order)
+        a = _lib.c_ministep_args()
+        a.nmodel, a.nfilt, a.m, a.ptype = net.I, net.nf // net.I, net.m, POOL_CODE[net.pool]
+        a.hidden, a.loss_kind, a.strand_pairs, a.B = net.hidden, 1 if net.loss == "nll" else 0, int(net.strand_pairs), B
+        a.max_rows, a.npos = max(1, int(max_rows)), int(X.shape[-1])
+        a.X, a.X_stride = X.data_ptr(), X.stride(0) * X.element_size() if stacked else 0
+        a.R, a.R_stride = R.data_ptr(), R.stride(0) * R.element_size() if R.dim() == 3 else 0
+        a.Y, a.Y_stride = Y.data_ptr(), Y.stride(0) * Y.element_size() if Y.dim() == 3 else 0
+        if dropmask is not None:
+            a.dropmask, a.mask_stride = dropmask.data_ptr(), dropmask.stride(0) * dropmask.element_size() if dropmask.dim() == 3 else 0
+        if stacked:
+            a.counters, a.nbatch = self.counters.data_ptr(), int(X.shape[0])
+            a.order = order.data_ptr() if order is not None else None
+        a.P, a.PL, a.mP, a.dP = net.P.data_ptr(), self.PL.data_ptr(), net.mP.data_ptr(), net.dP.data_ptr()
+        a.drate, a.mrate = net.drate.data_ptr(), net.mrate.data_ptr()
+        off = {k: int(net.offsets[i]) for i, k in enumerate(net.names)}
+        a.off_Wscan, a.off_bscan, a.off_W1, a.off_b1 = off["Wscan"], off["bscan"], off["W1"], off["b1"]
+        a.off_W2, a.off_b2 = off.get("W2", 0), off.get("b2", 0)
+        a.loss, a.status = self.loss.data_ptr(), self.status.data_ptr()
+        self.args = a
+        ok = all(t.is_contiguous() for t in (X, R, Y)) and X.dtype == torch.uint8 and Y.dtype == torch.float32
+        self.supported = bool(ok and dll.db_ministep_supported(ctypes.byref(a)))
+        self.scratch_bytes = int(dll.db_ministep_scratch_bytes(ctypes.byref(a))) if self.supported else 0
+
+    def lookahead(self):
+        """PL = P + mrate * mP: before the first step and after any change of P or mP
+        made elsewhere (gradstep.cu:46-50)."""
+        bind_stream()
+        n = self.net
+        _lib.load().db_ministep_lookahead(self.PL.data_ptr(), n.P.data_ptr(), n.mP.data_ptr(), n.mrate.data_ptr(), n.P.numel())
+
+    def run(self):
+        """Enqueues one step on the current stream."""
+        bind_stream()
+        n = self.net
+        self.args.decay = n.decay.data_ptr() if (n.decay_on and n.decay is not None) else None
+        _lib.load().db_ministep(ctypes.byref(self.args))
+        return self.loss
+
+    def capture(self, steps=1, prologue=None):
+        """CUDA graph of the look-ahead refresh and ``steps`` consecutive steps
+        (``prologue``: a callable that launches further kernels in front of every step,
+        e.g. the draw of the dropout mask).  The scratch buffer is sized first: nothing may
+        be allocated while a stream is captured.  The step counter is not touched."""
+        _lib.load().db_reserve_scratch(self.scratch_bytes)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.lookahead()
+            for _ in range(steps):
+                if prologue is not None:
+                    prologue()
+                self.run()
+        return graph

@@ -36,7 +36,7 @@ def _per_model(value, rng, I):
 
 
 class Trainer(object):
-    def __init__(self, net, spec=None, seed=0, ninst=None, instances=None):
+    def __init__(self, net, spec=None, seed=0, ninst=None, instances=None, ministep=True):
         """``spec``: a :class:`deepbind_b200.cfg.sgd` (ranges are drawn once per model).
         ``ninst``/``instances``: the net holds the instances ``instances`` of a set of
         ``ninst`` (cfg.instantiate); rates are drawn for all and those kept, so that an
@@ -53,6 +53,9 @@ class Trainer(object):
         self.step = 0
         self.history = []                 # (step, mean training loss [I]) at every checkpoint
         self.reverse_complement = False   # set by fit()
+        # small models train by the two-launch step (model.MiniStep) where it applies and its
+        # per-sample gradient shares stay within a few megabytes; False forces the operator-fused step
+        self.ministep = ministep
 
     # ------------------------------------------------------------------ data
     def make_batches(self, seqs, Y):
@@ -103,7 +106,7 @@ class Trainer(object):
         while nfull < nb and batches[nfull][0].numel() == batches[0][0].numel() and batches[nfull][1].shape == batches[0][1].shape:
             nfull += 1
         graphs = {}
-        static = feed = None
+        static = feed = mstep = None
         if use_graph and nfull >= max(1, nb - 1) and uniform_draws is None:
             X0, R0, Y0 = batches[0]
             static = (X0.clone(), R0.clone(), Y0.clone(), self._mask(R0.shape[0], None))
@@ -121,7 +124,15 @@ class Trainer(object):
                     sm.bind_stream()
                     _lib.load().db_dropout_mask(sM0.data_ptr(), sM0.shape[0], sM0.shape[1], rate_dev.data_ptr(), net.I,
                                                 int(self.reverse_complement), mask_counters.data_ptr())
+            sMask = static[3]
+            if self.ministep:
+                Rst = feed.pairs[1][0]
+                max_rows = int((Rst[..., 1] - Rst[..., 0]).max())
+                cand = net.ministep(feed.pairs[0][0], feed.pairs[1][0], feed.pairs[2][0], sMask, max_rows=max_rows)
+                if cand is not None and cand.scratch_bytes <= (8 << 20):
+                    mstep = cand
         loss = None
+        ms_count = 0     # what the two-launch step's device-side counter holds
         K = 8            # steps per replay where a run of K steps allows it: a replay costs the host more than a small step
         cps = sorted(checkpoints)
         step = 0
@@ -137,6 +148,13 @@ class Trainer(object):
                 many = (step % nb) + K <= nfull and step + K <= min(max_steps, nextcp) and \
                     (step >= spec.weight_decay_start or step + K <= spec.weight_decay_start)
                 key = (bool(net.decay_on), K if many else 1)
+                if key not in graphs and mstep is not None:
+                    graphs[key] = (mstep.capture(steps=key[1], prologue=draw_mask if sM is not None else None), mstep.loss)
+                if mstep is not None:                   # the step counter of the resident dataset, as run so far
+                    want = (step // nb) * nfull + min(step % nb, nfull)
+                    if want != ms_count:
+                        mstep.counters[0] = want
+                    ms_count = want + key[1]
                 if key not in graphs:
                     # the capture's warm-up steps are real steps: put the state back afterwards
                     P0, mP0 = net.P.clone(), net.mP.clone()

@@ -202,6 +202,47 @@ void db_head_train(uint32_t nmodel, uint32_t npool, uint32_t hidden, int loss_ki
                    const float* W1, const float* b1, const float* W2, const float* b2,
                    float* loss, float* dpooled, float* dW1, float* db1, float* dW2, float* db2);
 
+/* A whole minibatch step of a small model in two launches (what deepity.sgd runs per step,
+ * sgd.py:121-147: look-ahead of gradstep.cu:46-50, forward and backward pass of the DeepBind
+ * layer chain -- corr1ord.cuh:47-166, elemwise.py:71-82,116-180, poolrgn.cuh:44-160,
+ * full.py:41-119, softmax.py:50-77, loss.py:40-155 and their gradients -- L1 decay, update of
+ * gradstep.cu:57-71).  One CTA per (sample or strand pair, model) takes its sample through
+ * the whole chain in shared memory and writes the sample's share of every gradient; a
+ * second kernel adds the shares (sample ascending), updates P, mP and the look-ahead copy PL
+ * = P + mrate*mP, and advances the step counter.  Gradients are taken at PL.
+ *
+ * The minibatch of a step is slot order[counters[0] % nbatch] (or the count itself without
+ * order) of a device-resident dataset: X, R, Y, dropmask point at slot 0 and the strides (in
+ * bytes) lead from slot to slot; counters = NULL: always slot 0.  All flat parameter vectors
+ * hold the blocks Wscan [4m, nfilt*nmodel] (columns model-major), bscan, W1, b1, W2, b2 at the
+ * given offsets (in elements); hidden = 0: a linear head, W1 [(npool*nmodel),1], b1 [nmodel],
+ * off_W2/off_b2 unused.  npool = nfilt (max, avg, sum pooling) or 2*nfilt (all).  dropmask
+ * (bool bytes [B, npool*nmodel], NULL: none), decay (NULL: none), dP (NULL: gradient not
+ * kept), loss [nmodel] (NULL: not kept).  max_rows: the longest region of any minibatch, in
+ * rows (L + m - 1); status (int32, may be NULL) is raised to 2 if a region is empty or longer.
+ * Scratch comes from the library's buffer (db_ministep_scratch_bytes; reserve it before a
+ * stream capture).  db_ministep_supported: nfilt 16 or 32, at most 128 pooled features and
+ * hidden units, B even with strand pairs, regions that fit shared memory.
+ * db_ministep_lookahead: PL = P + mrate*mP, to be called before the first step and whenever
+ * the host changed P or mP. */
+typedef struct db_ministep_args {
+	uint32_t nmodel, nfilt, m, ptype, hidden, loss_kind, strand_pairs, B, max_rows, npos;
+	const uint8_t* X; size_t X_stride;
+	const uint32_t* R; size_t R_stride;
+	const float* Y; size_t Y_stride;
+	const uint8_t* dropmask; size_t mask_stride;
+	uint32_t* counters; const uint32_t* order; uint32_t nbatch;
+	float* P; float* PL; float* mP; float* dP;
+	const float* drate; const float* mrate; const float* decay;
+	uint32_t off_Wscan, off_bscan, off_W1, off_b1, off_W2, off_b2;
+	float* loss;
+	int32_t* status;
+} db_ministep_args;
+int db_ministep_supported(const db_ministep_args* args);
+size_t db_ministep_scratch_bytes(const db_ministep_args* args);
+void db_ministep_lookahead(float* PL, const float* P, const float* mP, const float* mrate, size_t n);
+void db_ministep(const db_ministep_args* args);
+
 /* ---- minibatch assembly on the device (replaces the host-side string joins of
  * kangaroo/data.py:309-334 with util.py:43-74 acgt2ord / revcomp, and the strand
  * doubling of data.py:274-283) -----------------------------------------------

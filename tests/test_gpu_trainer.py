@@ -89,11 +89,15 @@ def test_graph_replay_equals_eager_steps(cuda, nseq):
     seqs, Y = make_data(rng, nseq, 40, False)
     spec = cfg.sgd(rate=0.02, momentum=0.9, batchsize=32, max_epochs=100, max_steps=12, checkpoints=1, weight_decay_start=5)
     out = []
-    for use_graph in (False, True):
+    for use_graph, ministep in ((False, False), (True, False), (True, True), (True, True)):
         net, _ = cfg.instantiate(cfg.loads(LINEAR), ninst=5, seed=2)
-        Trainer(net, spec, seed=1).fit(seqs, Y, use_graph=use_graph)
+        Trainer(net, spec, seed=1, ministep=ministep).fit(seqs, Y, use_graph=use_graph)
         out.append(net.P.cpu().numpy())
-    np.testing.assert_array_equal(out[0], out[1])
+    np.testing.assert_array_equal(out[0], out[1])         # the operator-fused step, call by call and replayed
+    # the two-launch step adds the samples' gradient shares in another order: same run up to rounding,
+    # and the same bits every time
+    assert np.max(np.abs(out[2] - out[0])) <= 2e-5 * np.abs(out[0]).max()
+    np.testing.assert_array_equal(out[2], out[3])
 
 
 def test_scoring_scales_by_one_minus_the_dropout_rate(cuda, orc):
@@ -141,13 +145,18 @@ def test_eight_step_replays_equal_eager_steps(cuda):
     seqs, Y = make_data(rng, 32 * 20 + 7, 40, False)               # 20 full minibatches and a short one
     spec = cfg.sgd(rate=0.02, momentum=0.9, batchsize=32, max_epochs=100, max_steps=75, checkpoints=3, weight_decay_start=11)
     out, hist = [], []
-    for use_graph in (False, True):
+    for use_graph, ministep in ((False, False), (True, False), (True, True)):
         net, _ = cfg.instantiate(cfg.loads(LINEAR), ninst=3, seed=2)
-        t = Trainer(net, spec, seed=1)
+        t = Trainer(net, spec, seed=1, ministep=ministep)
         t.fit(seqs, Y, use_graph=use_graph)
         out.append(net.P.cpu().numpy())
         hist.append([(s, np.asarray(l.cpu() if hasattr(l, "cpu") else l)) for s, l in t.history])
     np.testing.assert_array_equal(out[0], out[1])
-    assert [s for s, _ in hist[0]] == [s for s, _ in hist[1]] == [25, 50, 75]
-    for (_, a), (_, b) in zip(*hist):
+    assert [s for s, _ in hist[0]] == [s for s, _ in hist[1]] == [s for s, _ in hist[2]] == [25, 50, 75]
+    for (_, a), (_, b) in zip(hist[0], hist[1]):
         np.testing.assert_array_equal(a, b)
+    # the two-launch step (replays of eight and of one, the short minibatch call by call in between):
+    # the same run up to the order of the gradient sums
+    assert np.max(np.abs(out[2] - out[0])) <= 5e-5 * np.abs(out[0]).max()
+    for (_, a), (_, b) in zip(hist[0], hist[2]):
+        np.testing.assert_allclose(a, b, rtol=1e-4)
