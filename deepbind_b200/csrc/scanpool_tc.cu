@@ -48,12 +48,12 @@ static constexpr int TC_ECHUNKS = TC_STAGE_TILES * 256 + 128;   // 16-byte chunk
 static constexpr int TC_EPI_SETS = 4;      // epilogue warps per TMEM lane quarter; region g is reduced by set g % TC_EPI_SETS
 static constexpr int TC_BUILD_WARPS = 2;   // warps that encode the B operand (one stage ahead; a stage lasts 8 tiles)
 static constexpr int TC_EPI_WARP0 = 1 + TC_BUILD_WARPS;             // first epilogue warp
-static constexpr int TC_THREADS = 32 * (TC_EPI_WARP0 + 4 * TC_EPI_SETS);
+static constexpr int TC_SEND_WARP = TC_EPI_WARP0 + 4 * TC_EPI_SETS;  // forwards finished score rows to the peers of a multi-GPU scan
+static constexpr int TC_THREADS = 32 * (TC_SEND_WARP + 1);
 static_assert(TC_EPI_SETS == 4, "region-aligned tiles pair the four warps of a lane quarter with the two accumulator slots");
 static constexpr unsigned long long TC_TIMEOUT = 200000000ull;    // default deadline of a wait, clock cycles (about 0.1 s)
 
 static constexpr int DB_TC_MAX_PEERS = 8;
-static constexpr unsigned TC_RING_K = 8;         // regions per tile the score ring of a multi-GPU scan holds
 
 struct tc_args {
 	const uint8_t* X; const uint32_t* R; const __nv_bfloat16* Wt; const float* bias;
@@ -103,6 +103,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
 		if (*abort_flag) return false;
 		if (clock64() - t0 > timeout) { *abort_flag = 1; return false; }
 		__nanosleep(40);        // a spinning warp would take issue slots from the epilogue warp of its scheduler
+	}
+}
+// The same for a counter in shared memory that only grows.
+__device__ __forceinline__ bool count_wait(volatile unsigned* cnt, unsigned need, volatile int* abort_flag, unsigned long long timeout)
+{
+	if (*cnt >= need) return true;
+	const unsigned long long t0 = clock64();
+	while (true) {
+		if (*cnt >= need) return true;
+		if (*abort_flag) return false;
+		if (clock64() - t0 > timeout) { *abort_flag = 1; return false; }
+		__nanosleep(100);
 	}
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar)
@@ -305,12 +317,15 @@ __device__ __forceinline__ float pow2_above(float bound)
 // gathered matrix over NVLink (plain peer stores; posted writes, nothing is read back): the
 // all-gather of the score shards happens inside the scan, column by column, and costs no
 // pass of its own.  The ranks synchronise after their launches before anyone reads.
+template <bool PEERS>
 __device__ __forceinline__ void store_score(const tc_args& a, unsigned g, unsigned model, float v)
 {
 	const size_t o = (size_t)g * a.nmodel + model;
 	if (a.scores) a.scores[o] = v;
-	const size_t po = (size_t)a.row_off * a.nmodel + o;
-	for (unsigned p = 0; p < a.npeer; ++p) a.peers[p][po] = v;
+	if (PEERS) {
+		const size_t po = (size_t)a.row_off * a.nmodel + o;
+		for (unsigned p = 0; p < a.npeer; ++p) a.peers[p][po] = v;
+	}
 }
 
 struct pool_state {
@@ -446,7 +461,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 			part += __shfl_xor_sync(0xffffffffu, part, 4);
 			part += __shfl_xor_sync(0xffffffffu, part, 2);
 			part += __shfl_xor_sync(0xffffffffu, part, 1);
-			if ((lane & 15) == 0 && f < a.nf) store_score(a, g, model, part + hb);
+			if ((lane & 15) == 0 && f < a.nf) store_score<true>(a, g, model, part + hb);
 		}
 		ps.reset();
 		g += TC_EPI_SETS;
@@ -521,7 +536,7 @@ template <bool WANT_MAX, bool WANT_SUM, bool RELU>
 __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t tmem_base, uint64_t* t_full, uint64_t* t_empty,
                                                     volatile int* abort_flag, unsigned tile, unsigned g_first, unsigned nreg,
                                                     unsigned P, unsigned S, unsigned k, unsigned warp, unsigned lane,
-                                                    float* ring, unsigned* ring_cnt)
+                                                    unsigned* done_cnt)
 {
 	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
 	const unsigned set = (warp - TC_EPI_WARP0) >> 2;
@@ -594,40 +609,46 @@ __device__ __forceinline__ void tc_epilogue_uniform(const tc_args& a, uint32_t t
 				part += __shfl_xor_sync(0xffffffffu, part, 4);
 				part += __shfl_xor_sync(0xffffffffu, part, 2);
 				part += __shfl_xor_sync(0xffffffffu, part, 1);
-				if (a.npeer && k <= TC_RING_K) {
-					// Multi-GPU scan: the eight scores of this region and filter tile (two per lane
-					// quarter) meet in shared memory, and the warp that brings the last pair writes
-					// them as one 32-byte run to this rank's matrix and to every peer's: an NVLink
-					// write packet per (region, tile, peer) instead of four small ones.  The entry of
-					// tile t is free again by tile t+4: a warp reaches tile t+4 only after all eight
-					// warps of its slot have handed back tile t+2, which each does after its deposit
-					// (and, for the last arriver, its stores) of tile t.
-					float* e = ring + ((t & 3u) * TC_RING_K + j) * 8u;
-					if ((lane & 15) == 0) e[q4 * 2 + (lane >> 4)] = part + hb;
-					__syncwarp();
-					unsigned last = 0;
-					if (lane == 0) {
-						__threadfence_block();
-						last = atomicAdd(&ring_cnt[(t & 3u) * TC_RING_K + j], 1u) == 3u ? 1u : 0u;
-						if (last) { ring_cnt[(t & 3u) * TC_RING_K + j] = 0u; __threadfence_block(); }
-					}
-					if (__shfl_sync(0xffffffffu, last, 0)) {
-						const unsigned col = tile * 8u + (lane & 7u);
-						const float v = e[lane & 7u];
-						if (col < a.nmodel) {
-							const size_t o = (size_t)g * a.nmodel + col;
-							if (a.scores && lane < 8) a.scores[o] = v;
-							const size_t po = (size_t)a.row_off * a.nmodel + o;
-							for (unsigned p = lane >> 3; p < a.npeer; p += 4) a.peers[p][po] = v;
-						}
-					}
-				} else if ((lane & 15) == 0 && f < a.nf) store_score(a, g, model, part + hb);
+				// a multi-GPU scan writes its own matrix here; the sender warp forwards whole rows of
+				// the tile to the peers once all warps of the slot are through with it
+				if ((lane & 15) == 0 && f < a.nf) store_score<false>(a, g, model, part + hb);
 			}
 		}
 		if (sub >= kt) {                                // no region of this tile is ours: hand it back untouched
 			tc_fence_before();
 			__syncwarp();
 			if (lane == 0) mbar_arrive(&t_empty[slot]);
+		}
+		if (a.npeer) {                                  // this warp's scores of the tile are written: tell the sender
+			__syncwarp();
+			if (lane == 0) { __threadfence_block(); atomicAdd(&done_cnt[slot], 1u); }
+		}
+	}
+}
+
+// Multi-GPU scan, region-aligned tiles: the sender warp waits until the eight epilogue warps
+// of a tile's slot have written the tile's scores to this rank's matrix, reads the tile's
+// rows back (eight consecutive scores per region and filter tile: one 32-byte sector, still
+// in L2) and stores each as one 32-byte run into every peer's matrix: an NVLink write packet
+// per (region, tile, peer).  The epilogue warps, which bound the kernel, only bump a
+// counter.  The counters only grow, so a sender that falls behind is never overtaken.
+__device__ __forceinline__ void tc_send_rows(const tc_args& a, volatile int* abort_flag, unsigned tile, unsigned g_first,
+                                             unsigned nreg, unsigned k, unsigned lane, unsigned* done_cnt)
+{
+	const unsigned ntile = (nreg + k - 1) / k;
+	const unsigned col = tile * 8u + (lane & 7u);
+	for (unsigned t = 0; t < ntile; ++t) {
+		unsigned okv = 0;
+		if (lane == 0) okv = count_wait(&done_cnt[t & 1u], 2u * TC_EPI_SETS * (t / 2u + 1u), abort_flag, a.timeout) ? 1u : 0u;
+		if (__shfl_sync(0xffffffffu, okv, 0) == 0) return;
+		__threadfence_block();
+		const unsigned kt = min(k, nreg - t * k);
+		for (unsigned j = lane >> 3; j < kt; j += 4) {
+			if (col >= a.nmodel) continue;
+			const size_t o = (size_t)(g_first + t * k + j) * a.nmodel + col;
+			const float v = __ldcg(a.scores + o);
+			const size_t po = (size_t)a.row_off * a.nmodel + o;
+			for (unsigned p = 0; p < a.npeer; ++p) a.peers[p][po] = v;
 		}
 	}
 }
@@ -646,8 +667,7 @@ scanpool_tc_kernel(const tc_args a)
 	__shared__ uint32_t tmem_base_s;
 	__shared__ unsigned rows_s[2], blk_ok[2];
 	__shared__ int abort_s;
-	__shared__ __align__(16) float score_ring[4 * TC_RING_K * 8];
-	__shared__ unsigned score_ring_cnt[4 * TC_RING_K];
+	__shared__ unsigned done_cnt[2];
 	volatile int* abort_flag = &abort_s;
 
 	const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -657,7 +677,7 @@ scanpool_tc_kernel(const tc_args a)
 
 	// A CTA of a launch that has already failed returns at once.  One thread reads
 	// the status word so that the whole CTA takes the same decision.
-	if (threadIdx.x < 4 * TC_RING_K) score_ring_cnt[threadIdx.x] = 0u;
+	if (threadIdx.x < 2) done_cnt[threadIdx.x] = 0u;
 	if (threadIdx.x == 0) {
 		abort_s = *reinterpret_cast<volatile int*>(a.status);
 		rows_s[0] = a.R[2 * g_first];
@@ -800,10 +820,13 @@ scanpool_tc_kernel(const tc_args a)
 			__syncwarp();
 			if (lane == 0 && !a.hold_operands) mbar_arrive(&e_full[st]);
 		}
+	} else if (warp == TC_SEND_WARP) {
+		// ------------------------------------------------------------ rows to the peers (multi-GPU scan)
+		if (uni && a.npeer) tc_send_rows(a, abort_flag, tile, g_first, nreg, kreg, lane, done_cnt);
 	} else {
 		// ------------------------------------------------------------ epilogue
 		#define TC_EPI(MX, SM, RL) do { \
-			if (uni) tc_epilogue_uniform<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, nreg, P0, S0, kreg, warp, lane, score_ring, score_ring_cnt); \
+			if (uni) tc_epilogue_uniform<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, nreg, P0, S0, kreg, warp, lane, done_cnt); \
 			else tc_epilogue<MX, SM, RL>(a, tmem_base, t_full, t_empty, abort_flag, tile, g_first, g_last, row_lo, row_hi, warp, lane); } while (0)
 		const bool wm = a.ptype == DB_PT_MAX || a.ptype == DB_PT_ALL, ws = a.ptype != DB_PT_MAX;
 		if (a.relu) { if (wm && ws) TC_EPI(true, true, true); else if (wm) TC_EPI(true, false, true); else TC_EPI(false, true, true); }
