@@ -10,8 +10,9 @@ and runs
          [-> rectify -> full -> bias] [-> logistic] -> loss
 
 forward, backward and the Nesterov update entirely through libdeepbind_b200.so.
-It is the composite the benchmark and parity tests drive; the node/plug graph
-engine of the reference is not reproduced here.
+It is the composite the benchmark and parity tests drive, mapped as a whole onto
+the fused kernels; the reference's node/plug graph engine, which runs the same
+layers operator by operator, is ``deepbind_b200.graph``.
 """
 import ctypes
 
