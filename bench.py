@@ -61,6 +61,8 @@ def parse():
     ap.add_argument("--cpu-sample", type=int, default=8192, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the short runs of the other benchmark configurations")
+    ap.add_argument("--calibration-models", type=int, default=90,
+                    help="models of the calibration-sweep leg on one GPU (90 = the configuration; 12 = one rank's share on 8 GPUs)")
     ap.add_argument("--only-reference-kernels", action="store_true",
                     help="run only the comparison of the unfused operators with the reference's own kernels and print its JSON")
     return ap.parse_args()
@@ -203,7 +205,7 @@ def _read_peaks():
     return json.load(open(PEAKS_FILE)) if os.path.exists(PEAKS_FILE) else {}
 
 
-def side_workloads(dev, with_cpu):
+def side_workloads(dev, with_cpu, calibration_models=90):
     """Short device-timed runs of the other benchmark configurations (inputs resident
     in HBM, CUDA events, 3+ warm-up passes), each beside the CPU restatement timed on
     a bounded sample.  They ride along in the JSON line under `other_configs`."""
@@ -343,7 +345,7 @@ def side_workloads(dev, with_cpu):
     # config 2: ChIP-seq-style training, one model, minibatch 128, allpool -> 32 hidden (dropout 0.5) -> sigmoid
     train("chip_train", 1, 128, 101, "all", 32, "nll", 64, 2000, 5)
     # config 3: calibration sweep, 90 independent models trained at once on 40-nt probes, minibatch 64
-    train("calibration", 90, 64, 40, "max", 0, "mse", 64, 1000, 1)
+    train("calibration", calibration_models, 64, 40, "max", 0, "mse", 64, 1000, 1)
     return out
 
 
@@ -713,7 +715,7 @@ def main():
         if world == 1 and not args.no_side:
             del X, R, scores, X_host, R_host, out_host, scorer
             torch.cuda.empty_cache()
-            line["other_configs"] = side_workloads(dev, not args.no_cpu_baseline)
+            line["other_configs"] = side_workloads(dev, not args.no_cpu_baseline, args.calibration_models)
             rk = reference_kernels(dev)
             if rk is not None:
                 line["other_configs"]["reference_kernels"] = rk

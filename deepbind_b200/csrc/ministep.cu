@@ -46,6 +46,7 @@ static constexpr int US_S = 8;            // sample slices of the update kernel 
 
 struct ministep_dev {
 	db_ministep_args a;
+	unsigned spc;          // samples (minibatch rows) per CTA: 1, 2 or 4; even with strand pairs
 	float* partial;        // [I][B][(4m+1)*F]
 	float* rec;            // [I][B][RS]
 	unsigned np, HC, RS, n;
@@ -75,17 +76,16 @@ __host__ __device__ inline unsigned ms_common_bytes(unsigned m, unsigned F, unsi
 }
 
 template <int M>
-__global__ void __launch_bounds__(2 * MS_T)
+__global__ void __launch_bounds__(4 * MS_T)
 ministep_sample_kernel(const ministep_dev d)
 {
 	extern __shared__ __align__(16) unsigned char smem[];
 	const db_ministep_args& a = d.a;
 	const unsigned m = M > 0 ? (unsigned)M : a.m, F = a.nfilt, NQ = F / 4, AS = F + 4;
 	const unsigned nf = F * a.nmodel, np = d.np, H = a.hidden, HC = d.HC;
-	const unsigned S = a.strand_pairs ? 2u : 1u;
 	const unsigned b = blockIdx.y;
-	const unsigned strand = threadIdx.x / MS_T, tid = threadIdx.x % MS_T;
-	const unsigned row_id = blockIdx.x * S + strand;                    // row of the minibatch
+	const unsigned strand = threadIdx.x / MS_T, tid = threadIdx.x % MS_T;   // which of the CTA's samples; thread within it
+	const unsigned row_id = blockIdx.x * d.spc + strand;                // row of the minibatch
 
 	float* lut = reinterpret_cast<float*>(smem);
 	float* sb = lut + (size_t)m * NQ * 32;
@@ -103,7 +103,7 @@ ministep_sample_kernel(const ministep_dev d)
 	float* accs = reinterpret_cast<float*>(mine + L.accs);
 	uint8_t* xs = mine + L.xs;
 	__shared__ unsigned s_slot;
-	__shared__ float s_z[2];
+	__shared__ float s_z[4];
 
 	if (threadIdx.x == 0) {
 		const unsigned c = a.counters ? *reinterpret_cast<volatile const uint32_t*>(a.counters) % a.nbatch : 0u;
@@ -117,6 +117,8 @@ ministep_sample_kernel(const ministep_dev d)
 	for (unsigned t = threadIdx.x; t < np * HC; t += blockDim.x) w1s[t] = PL[a.off_W1 + (size_t)b * np * HC + t];
 	const float b1v = tid < HC ? PL[a.off_b1 + b * HC + tid] : 0.f;
 	const float b2v = H ? PL[a.off_b2 + b] : 0.f;
+	uint2 rg0 = make_uint2(0u, 0u);
+	if (a.R_stride == 0) rg0 = make_uint2(a.R[2 * row_id], a.R[2 * row_id + 1]);    // one region table for all minibatches
 	__syncthreads();
 	const size_t slot = s_slot;
 	const uint8_t* X = a.X + slot * a.X_stride;
@@ -128,7 +130,7 @@ ministep_sample_kernel(const ministep_dev d)
 	const float yv = Y[(size_t)row_id * a.nmodel + b];
 	const bool kept = !(mask && tid < np && !mask[mrow + tid]);
 
-	const unsigned r0 = R[2 * row_id], r1 = R[2 * row_id + 1];
+	const unsigned r0 = a.R_stride == 0 ? rg0.x : R[2 * row_id], r1 = a.R_stride == 0 ? rg0.y : R[2 * row_id + 1];
 	unsigned rows = r1 > r0 ? r1 - r0 : 0u;
 	if (rows == 0 || rows > a.max_rows) {                                // reported, and kept inside the staged window
 		if (tid == 0 && a.status) atomicMax(a.status, 2);
@@ -243,7 +245,7 @@ ministep_sample_kernel(const ministep_dev d)
 	{
 		const float z = s_z[strand];
 		bool keep = true;
-		if (a.strand_pairs) keep = strand ? !(s_z[0] >= z) : (z >= s_z[1]);
+		if (a.strand_pairs) keep = (strand & 1u) ? !(s_z[strand ^ 1u] >= z) : (z >= s_z[strand ^ 1u]);
 		float l;
 		if (a.loss_kind == 1) l = logf(fmaxf(1e-15f, z)) * yv + logf(fmaxf(1e-15f, 1.f - z)) * (1.f - yv);
 		else { const float e = z - yv; l = e * e; }
@@ -425,6 +427,12 @@ ministep_update_kernel(const ministep_dev d)
 			pi = (size_t)a.off_b2 + b; p0 = rec + np + H + HC;
 		}
 	} else if (e == NS + NH) p0 = rec + np + H + HC + 1;                     // the loss terms
+	// the parameter's state travels while the shares are added
+	float pl = 0.f, mr = 0.f, dr = 0.f, mp0 = 0.f, dc = 0.f;
+	if (w == 0 && p0 && e < NS + NH) {
+		pl = a.PL[pi]; mr = a.mrate[pi]; dr = a.drate[pi]; mp0 = a.mP[pi];
+		if (a.decay) dc = a.decay[pi];
+	}
 	if (p0) {
 		for (unsigned s = s0; s < s1; s += 16) {
 			float x0[16], x1[16];
@@ -448,16 +456,14 @@ ministep_update_kernel(const ministep_dev d)
 		if (a.loss) a.loss[b] = (a.loss_kind == 0 ? 0.5f : -1.f) * (g * (1.f / (float)B));
 		return;
 	}
-	const float pl = a.PL[pi];
 	if (a.decay) {
 		const float sg = pl > 0.f ? 1.f : (pl < 0.f ? -1.f : 0.f);
-		g = g + a.decay[pi] * sg;                                            // corr1ord.py:112-126, full.py:102-119
+		g = g + dc * sg;                                                     // corr1ord.py:112-126, full.py:102-119
 	}
 	if (a.dP) a.dP[pi] = g;
 	// gradstep.cu:57-71 (second half of the Nesterov step), then gradstep.cu:46-50 for the next one
-	const float mr = a.mrate[pi];
-	const float delta = g * a.drate[pi];
-	const float mp = a.mP[pi] * mr - delta;
+	const float delta = g * dr;
+	const float mp = mp0 * mr - delta;
 	const float p = pl - delta;
 	a.mP[pi] = mp;
 	a.P[pi] = p;
@@ -473,11 +479,16 @@ __global__ void ministep_lookahead_kernel(float* __restrict__ PL, const float* _
 
 static unsigned ms_npool(const db_ministep_args* a) { return a->ptype == DB_PT_ALL ? 2 * a->nfilt : a->nfilt; }
 
-static size_t ms_smem(const db_ministep_args* a)
+static size_t ms_smem(const db_ministep_args* a, unsigned spc)
 {
 	const unsigned HC = a->hidden ? a->hidden : 1u;
-	return ms_common_bytes(a->m, a->nfilt, ms_npool(a), HC) + (size_t)(a->strand_pairs ? 2 : 1) * ms_strand_layout(a->max_rows, a->m, a->nfilt, HC).total;
+	return ms_common_bytes(a->m, a->nfilt, ms_npool(a), HC) + (size_t)spc * ms_strand_layout(a->max_rows, a->m, a->nfilt, HC).total;
 }
+
+// Samples per CTA: one, or the two strands of a pair.  Four samples sharing the staged lookup
+// table and dense weights were measured slower where they could apply (12 models x 64 samples:
+// 26.3 against 23.0 us per step): the barriers of a 1024-thread CTA cost more than the staging.
+static unsigned ms_spc(const db_ministep_args* a) { return a->strand_pairs ? 2u : 1u; }
 
 }  // namespace db
 
@@ -491,7 +502,7 @@ DB_EXPORT int db_ministep_supported(const db_ministep_args* a)
 	if (a->ptype > (uint32_t)DB_PT_ALL) return 0;
 	if (a->strand_pairs && (a->B & 1u)) return 0;
 	if (!a->B || !a->nmodel || a->nmodel > 65535u || !a->max_rows) return 0;
-	return ms_smem(a) <= 200 * 1024 ? 1 : 0;
+	return ms_smem(a, a->strand_pairs ? 2u : 1u) <= 200 * 1024 ? 1 : 0;
 }
 
 DB_EXPORT size_t db_ministep_scratch_bytes(const db_ministep_args* a)
@@ -530,9 +541,9 @@ DB_EXPORT void db_ministep(const db_ministep_args* args)
 	const size_t npart = (size_t)a.nmodel * a.B * (size_t)(4 * a.m + 1) * a.nfilt;
 	float* sc = reinterpret_cast<float*>(scratch(db_ministep_scratch_bytes(args)));
 	d.partial = sc; d.rec = sc + ((npart + 63) & ~(size_t)63);
-	const size_t smem = ms_smem(args);
-	const unsigned S = a.strand_pairs ? 2u : 1u;
-	dim3 grid(a.B / S, a.nmodel), block(MS_T * S);
+	d.spc = ms_spc(args);
+	const size_t smem = ms_smem(args, d.spc);
+	dim3 grid(a.B / d.spc, a.nmodel), block(MS_T * d.spc);
 	auto launch = [&](auto kern) {
 		DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, (size_t)48 * 1024)));
 		kern<<<grid, block, smem, state().stream>>>(d);

@@ -43,6 +43,9 @@ CASES = [
     (3, "avg", 16, "mse", "ragged_rc", 64, 16, True, True),
     (2, "all", 0, "nll", "ragged", 50, 11, False, True),
     (4, "sum", 8, "mse", "ragged", 33, 24, True, False),
+    # enough (sample, model) pairs for four samples per CTA
+    (12, "max", 0, "mse", "uniform40", 64, 24, False, False),
+    (10, "all", 8, "nll", "ragged_rc", 64, 16, True, True),
 ]
 
 
