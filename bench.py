@@ -51,7 +51,8 @@ def parse():
     ap.add_argument("--variant", default="f16", choices=["f16x2", "bf16x3", "bf16x2", "f16", "bf16", "f32"],
                     help="arithmetic of the scan: one 16-bit piece per weight on tcgen05 (f16 = TF32-grade, bf16), several pieces "
                          "(f16x2, bf16x3 = fp32-grade), or the exact FP32 lookup-add kernel")
-    ap.add_argument("--gather-chunks", type=int, default=16, help="several GPUs: chunks of the shard whose all-gather overlaps the scan")
+    ap.add_argument("--gather-chunks", type=int, default=16, help="pieces of the shard: upload, scan and read-back of the host-to-host call overlap piece by piece; "
+                                                                       "with --gather nccl also the chunks whose all-gather overlaps the scan")
     ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
                     help="several GPUs: 'peer' = the scan kernel stores every score into all ranks' matrices over NVLink "
                          "(symmetric memory, no collective pass); 'nccl' = chunked all-gather overlapped with the scan")
@@ -531,7 +532,8 @@ def main():
     X = X_host.to(dev); R = R_host.to(dev)
     if nsplit:
         net.prepare_tc(args.variant)
-    scorer = ShardedScorer(net, nseq, group=None, nchunk=args.gather_chunks if world > 1 else 1, gather=args.gather)
+    # nchunk: pieces of the host-to-host pipeline (upload, scan, read-back overlapped) and of the NCCL gather
+    scorer = ShardedScorer(net, nseq, group=None, nchunk=args.gather_chunks, gather=args.gather)
     scores = scorer.scores
     status = scorer.status
     gathered = scorer.gathered
