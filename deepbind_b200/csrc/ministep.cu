@@ -39,14 +39,15 @@
 
 namespace db {
 
-static constexpr int MS_T = 256;          // threads per strand
+static constexpr int MS_T = 256;          // threads per sample, at most (128 for short regions)
 static constexpr int MS_PP = 8;           // row slices of the pooling pass
 static constexpr int US_E = 32;           // parameters per CTA of the update kernel
 static constexpr int US_S = 8;            // sample slices of the update kernel (one warp each)
 
 struct ministep_dev {
 	db_ministep_args a;
-	unsigned spc;          // samples (minibatch rows) per CTA: 1, 2 or 4; even with strand pairs
+	unsigned spc;          // samples (minibatch rows) per CTA: 1, or the 2 strands of a pair
+	unsigned T;            // threads per sample: 128 or 256
 	float* partial;        // [I][B][(4m+1)*F]
 	float* rec;            // [I][B][RS]
 	unsigned np, HC, RS, n;
@@ -55,8 +56,8 @@ struct ministep_dev {
 // Offsets (in bytes) of a strand's private shared-memory block.
 struct ms_layout { unsigned act, oh, small, amax, pp, accs, xs, total; };
 __host__ __device__ inline unsigned ms_units(unsigned m, unsigned F) { return ((m + 3) / 4) * F + F; }
-__host__ __device__ inline unsigned ms_rsplit(unsigned m, unsigned F) { const unsigned u = ms_units(m, F); return u >= (unsigned)MS_T ? 1u : (unsigned)MS_T / u; }
-__host__ __device__ inline ms_layout ms_strand_layout(unsigned max_rows, unsigned m, unsigned F, unsigned HC)
+__host__ __device__ inline unsigned ms_rsplit(unsigned m, unsigned F, unsigned T) { const unsigned u = ms_units(m, F); return u >= T ? 1u : T / u; }
+__host__ __device__ inline ms_layout ms_strand_layout(unsigned max_rows, unsigned m, unsigned F, unsigned HC, unsigned T)
 {
 	ms_layout l;
 	unsigned o = 0;
@@ -65,7 +66,7 @@ __host__ __device__ inline ms_layout ms_strand_layout(unsigned max_rows, unsigne
 	l.small = o; o += (6 * F + 3 * ((HC + 3) & ~3u) + 8) * 4;       // pooled[2F] pd[2F] dpd[2F] h1 a1 dh misc[8]
 	l.amax = o;  o += F * 4;
 	l.pp = o;    o += MS_PP * F * 3 * 4;                             // pooling slices: max, row, sum
-	l.accs = o;  o += (ms_rsplit(m, F) - 1) * ms_units(m, F) * 16 * 4; // gradient sums of the row splits after the first
+	l.accs = o;  o += (ms_rsplit(m, F, T) - 1) * ms_units(m, F) * 16 * 4; // gradient sums of the row splits after the first
 	l.xs = o;    o += (max_rows + m + 8 + 3) & ~3u;
 	l.total = (o + 15) & ~15u;
 	return l;
@@ -76,7 +77,7 @@ __host__ __device__ inline unsigned ms_common_bytes(unsigned m, unsigned F, unsi
 }
 
 template <int M>
-__global__ void __launch_bounds__(4 * MS_T)
+__global__ void __launch_bounds__(2 * MS_T)
 ministep_sample_kernel(const ministep_dev d)
 {
 	extern __shared__ __align__(16) unsigned char smem[];
@@ -84,14 +85,15 @@ ministep_sample_kernel(const ministep_dev d)
 	const unsigned m = M > 0 ? (unsigned)M : a.m, F = a.nfilt, NQ = F / 4, AS = F + 4;
 	const unsigned nf = F * a.nmodel, np = d.np, H = a.hidden, HC = d.HC;
 	const unsigned b = blockIdx.y;
-	const unsigned strand = threadIdx.x / MS_T, tid = threadIdx.x % MS_T;   // which of the CTA's samples; thread within it
+	const unsigned T = d.T;
+	const unsigned strand = threadIdx.x / T, tid = threadIdx.x % T;     // which of the CTA's samples; thread within it
 	const unsigned row_id = blockIdx.x * d.spc + strand;                // row of the minibatch
 
 	float* lut = reinterpret_cast<float*>(smem);
 	float* sb = lut + (size_t)m * NQ * 32;
 	float* w2s = sb + F;
 	float* w1s = w2s + ((HC + 3) & ~3u);
-	const ms_layout L = ms_strand_layout(a.max_rows, m, F, HC);
+	const ms_layout L = ms_strand_layout(a.max_rows, m, F, HC, T);
 	unsigned char* mine = smem + ms_common_bytes(m, F, np, HC) + (size_t)strand * L.total;
 	float* act = reinterpret_cast<float*>(mine + L.act);
 	float4* oh = reinterpret_cast<float4*>(mine + L.oh);
@@ -138,7 +140,7 @@ ministep_sample_kernel(const ministep_dev d)
 	}
 	// rows of the region that have a scan output (the last m-1 rows of the buffer have none)
 	const unsigned rows_w = d.n > r0 ? min(rows, d.n - r0) : 0u;
-	for (unsigned t = tid; t < ((rows + m + 8 + 3) & ~3u); t += MS_T) {
+	for (unsigned t = tid; t < ((rows + m + 8 + 3) & ~3u); t += T) {
 		const unsigned i = r0 + t;
 		xs[t] = (uint8_t)code16_of(i < a.npos ? X[i] : 254u);
 	}
@@ -147,7 +149,7 @@ ministep_sample_kernel(const ministep_dev d)
 	// ---- scan + bias + rectify: a thread owns one row x 16 filters per pass; and the channel
 	// weights of every input row for the backward pass (one-hot, 1/4 each for N, 0 for a dropped base)
 	{
-		const unsigned FG = F / 16, TRK = MS_T / FG;
+		const unsigned FG = F / 16, TRK = T / FG;
 		const unsigned rl = tid % TRK, fg = tid / TRK;
 		const unsigned char* lutp = reinterpret_cast<const unsigned char*>(lut) + fg * 512;
 		for (unsigned p0 = 0; p0 < rows; p0 += TRK) {
@@ -167,7 +169,7 @@ ministep_sample_kernel(const ministep_dev d)
 				*reinterpret_cast<float4*>(act + row * AS + fg * 16 + v) = x;
 			}
 		}
-		for (unsigned t = tid; t < rows + m + 4; t += MS_T) {
+		for (unsigned t = tid; t < rows + m + 4; t += T) {
 			const unsigned c = xs[t] >> 4;
 			const float q = c == 4u ? 0.25f : 0.f;
 			oh[t] = make_float4(c == 0u ? 1.f : q, c == 1u ? 1.f : q, c == 2u ? 1.f : q, c == 3u ? 1.f : q);
@@ -177,8 +179,9 @@ ministep_sample_kernel(const ministep_dev d)
 
 	// ---- pooling: MS_PP row slices per filter, rows ascending within a slice, slices ascending
 	// after that (strict '>' both times: the first maximum wins, as in poolrgn.cuh:60-78)
-	const unsigned slice = (rows + MS_PP - 1) / MS_PP;
-	if (tid < MS_PP * F) {
+	const unsigned PP = min((unsigned)MS_PP, T / F);                     // row slices of the pooling pass
+	const unsigned slice = (rows + PP - 1) / PP;
+	if (tid < PP * F) {
 		const unsigned f = tid % F, part = tid / F;
 		const unsigned ra = min(rows, part * slice), rb = min(rows, ra + slice);
 		float xmax = 0.f, xsum = 0.f; unsigned xi = 0xffffffffu;
@@ -197,8 +200,7 @@ ministep_sample_kernel(const ministep_dev d)
 	__syncthreads();
 	if (tid < F) {
 		float xmax = pp[tid * 3], xsum = pp[tid * 3 + 2]; unsigned xi = __float_as_uint(pp[tid * 3 + 1]);
-		#pragma unroll
-		for (unsigned part = 1; part < MS_PP; ++part) {
+		for (unsigned part = 1; part < PP; ++part) {
 			const float* e = pp + (part * F + tid) * 3;
 			const unsigned ri = __float_as_uint(e[1]);
 			if (ri != 0xffffffffu) {
@@ -262,7 +264,7 @@ ministep_sample_kernel(const ministep_dev d)
 	}
 	{   // the sample's record for the update kernel: pd | a1 | dh | dout | loss
 		float* rec = d.rec + ((size_t)b * a.B + row_id) * d.RS;
-		for (unsigned t = tid; t < d.RS; t += MS_T) {
+		for (unsigned t = tid; t < d.RS; t += T) {
 			float v;
 			if (t < np) v = pd[t];
 			else if (t < np + H) v = a1[t - np];
@@ -290,7 +292,7 @@ ministep_sample_kernel(const ministep_dev d)
 	__syncthreads();
 	const bool only_max = a.ptype == DB_PT_MAX;
 	if (!only_max) {
-		for (unsigned t = tid; t < rows * F; t += MS_T) {
+		for (unsigned t = tid; t < rows * F; t += T) {
 			const unsigned r = t / F, f = t % F;
 			float v = 0.f;
 			if (act[r * AS + f] > 0.f) {
@@ -305,9 +307,9 @@ ministep_sample_kernel(const ministep_dev d)
 	// ---- the sample's filter and bias gradient: a thread per (four taps, filter) and row split,
 	// rows ascending within a split, splits ascending after that
 	float* part = d.partial + ((size_t)b * a.B + row_id) * (size_t)(4 * m + 1) * F;
-	const unsigned nunit = ((m + 3) / 4) * F, U = nunit + F, RSP = ms_rsplit(m, F);
+	const unsigned nunit = ((m + 3) / 4) * F, U = nunit + F, RSP = ms_rsplit(m, F, T);
 	const unsigned rchunk = ((rows + RSP - 1) / RSP + 3u) & ~3u;
-	for (unsigned t0 = 0; t0 < U * RSP; t0 += MS_T) {
+	for (unsigned t0 = 0; t0 < U * RSP; t0 += T) {
 		const unsigned t = t0 + tid;
 		const unsigned split = t / U, unit = t % U;
 		const bool on = t < U * RSP;
@@ -479,10 +481,15 @@ __global__ void ministep_lookahead_kernel(float* __restrict__ PL, const float* _
 
 static unsigned ms_npool(const db_ministep_args* a) { return a->ptype == DB_PT_ALL ? 2 * a->nfilt : a->nfilt; }
 
+// Threads per sample: 256, or 128 where a region's rows fit one scan pass of 128 threads (the
+// fixed work of the kernel's phases is per warp).
+static unsigned ms_threads(const db_ministep_args* a) { return a->max_rows * (a->nfilt / 16u) <= 64u ? 128u : 256u; }
+
 static size_t ms_smem(const db_ministep_args* a, unsigned spc)
 {
 	const unsigned HC = a->hidden ? a->hidden : 1u;
-	return ms_common_bytes(a->m, a->nfilt, ms_npool(a), HC) + (size_t)spc * ms_strand_layout(a->max_rows, a->m, a->nfilt, HC).total;
+	return ms_common_bytes(a->m, a->nfilt, ms_npool(a), HC) +
+	       (size_t)spc * ms_strand_layout(a->max_rows, a->m, a->nfilt, HC, ms_threads(a)).total;
 }
 
 // Samples per CTA: one, or the two strands of a pair.  Four samples sharing the staged lookup
@@ -498,7 +505,7 @@ DB_EXPORT int db_ministep_supported(const db_ministep_args* a)
 {
 	if (!a) return 0;
 	if (a->nfilt != 16 && a->nfilt != 32) return 0;
-	if (a->m < 1 || a->m > 64 || a->hidden > MS_T || ms_npool(a) > MS_T) return 0;
+	if (a->m < 1 || a->m > 64 || a->hidden > 128u || ms_npool(a) > 128u) return 0;
 	if (a->ptype > (uint32_t)DB_PT_ALL) return 0;
 	if (a->strand_pairs && (a->B & 1u)) return 0;
 	if (!a->B || !a->nmodel || a->nmodel > 65535u || !a->max_rows) return 0;
@@ -528,7 +535,7 @@ DB_EXPORT void db_ministep(const db_ministep_args* args)
 	DB_API_TRY
 	DB_REQUIRE(args != nullptr, "ValueError: db_ministep got NULL");
 	DB_REQUIRE(db_ministep_supported(args), "ValueError: this model or minibatch shape is outside the two-launch step "
-	           "(16 or 32 filters per model, at most %d pooled features and hidden units, regions that fit shared memory)", MS_T);
+	           "(16 or 32 filters per model, at most %d pooled features and hidden units, regions that fit shared memory)", 128);
 	const db_ministep_args& a = *args;
 	DB_REQUIRE(a.X && a.R && a.Y && a.P && a.PL && a.mP && a.drate && a.mrate, "ValueError: db_ministep got a NULL pointer");
 	DB_REQUIRE(!a.counters || a.nbatch, "ValueError: a step counter needs the number of minibatches");
@@ -541,9 +548,9 @@ DB_EXPORT void db_ministep(const db_ministep_args* args)
 	const size_t npart = (size_t)a.nmodel * a.B * (size_t)(4 * a.m + 1) * a.nfilt;
 	float* sc = reinterpret_cast<float*>(scratch(db_ministep_scratch_bytes(args)));
 	d.partial = sc; d.rec = sc + ((npart + 63) & ~(size_t)63);
-	d.spc = ms_spc(args);
+	d.spc = ms_spc(args); d.T = ms_threads(args);
 	const size_t smem = ms_smem(args, d.spc);
-	dim3 grid(a.B / d.spc, a.nmodel), block(MS_T * d.spc);
+	dim3 grid(a.B / d.spc, a.nmodel), block(d.T * d.spc);
 	auto launch = [&](auto kern) {
 		DB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, (size_t)48 * 1024)));
 		kern<<<grid, block, smem, state().stream>>>(d);
