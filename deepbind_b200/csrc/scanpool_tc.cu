@@ -62,6 +62,7 @@ struct tc_args {
 	unsigned npos, n, nregion, nf, m, KC, nsplit, seqs_per_cta, nmodel;
 	int ptype, relu;
 	unsigned f16;                   // operand type of both MMA inputs: 0 = bf16, 1 = f16 (weights prescaled by a power of two)
+	unsigned rep;                   // at most 32 filters: the filter block is repeated in every lane quarter (see tc_replicated)
 	const uint32_t* maxabs;         // bit pattern of max |W|, kept behind the prepared tiles
 	float* peers[DB_TC_MAX_PEERS];  // score matrices of the ranks of a multi-GPU scan (peer-mapped), or none
 	unsigned npeer, row_off;        // this launch's region g is row row_off + g of each of them
@@ -394,6 +395,13 @@ struct pool_state {
 	}
 };
 
+// With at most 32 filters only one of the four TMEM lane quarters would hold results, and a
+// lane quarter can only be read by the warps of one SM sub-partition: one scheduler would do
+// the whole epilogue.  So the prepared operand repeats the filter block in all four quarters
+// (the tile has 128 rows either way), every quarter holds every filter, and the sixteen epilogue
+// warps share the regions instead of the filters: four schedulers work on the pooling.
+__host__ __device__ inline bool tc_replicated(unsigned nf) { return nf <= 32u; }
+
 template <bool WANT_MAX, bool WANT_SUM, bool RELU>
 __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base, uint64_t* t_full, uint64_t* t_empty,
                                             volatile int* abort_flag, unsigned tile, unsigned g_first, unsigned g_last,
@@ -401,7 +409,11 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 {
 	const unsigned q4 = warp & 3;                       // TMEM lane quarter of this warp
 	const unsigned set = (warp - TC_EPI_WARP0) >> 2;    // the warps of a quarter take the regions in turn
-	const unsigned f = tile * 128 + q4 * 32 + lane;     // this thread's filter = its TMEM lane
+	// this thread's filter = its TMEM lane; with a repeated filter block, its lane within the quarter
+	const unsigned f = a.rep ? lane : tile * 128 + q4 * 32 + lane;
+	// regions this warp reduces: every gstep-th from g_first + gidx on
+	const unsigned gstep = a.rep ? 4u * TC_EPI_SETS : (unsigned)TC_EPI_SETS;
+	const unsigned gidx = a.rep ? set * 4u + q4 : set;
 	const uint32_t maxabs_bits = *a.maxabs;
 	const float wscale = a.f16 ? tc_weight_scale(maxabs_bits) : 1.f, inv_wscale = 1.f / wscale;    // powers of two
 	const float b0 = (a.bias && f < a.nf) ? a.bias[f] : 0.f;
@@ -421,8 +433,8 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 	}
 	pool_state ps;
 	ps.reset();
-	// This warp reduces the regions g_first + set, + TC_EPI_SETS, ... and never looks at the others.
-	unsigned g = g_first + set;
+	// This warp reduces the regions g_first + gidx, + gstep, ... and never looks at the others.
+	unsigned g = g_first + gidx;
 	unsigned r0 = 0, r1 = 0;                            // bounds of the region being reduced
 	unsigned nr0 = 0, nr1 = 0, nprev = 0;               // bounds of this warp's next region and the end of the one before it, loaded ahead
 	bool ok = true;
@@ -434,7 +446,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 		}
 	}
 	auto fetch_next = [&]() {
-		const unsigned h = g + TC_EPI_SETS;
+		const unsigned h = g + gstep;
 		if (h < g_last) {
 			const uint2 r = reinterpret_cast<const uint2*>(a.R)[h];      // regions are (start, end) pairs: cudaMalloc alignment
 			nr0 = r.x; nr1 = r.y; nprev = a.R[2 * h - 1];
@@ -464,7 +476,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 			if ((lane & 15) == 0 && f < a.nf) store_score<true>(a, g, model, part + hb);
 		}
 		ps.reset();
-		g += TC_EPI_SETS;
+		g += gstep;
 		if (g >= g_last) return true;
 		r0 = nr0; r1 = max(nr1, nr0);
 		const bool bad = r0 < nprev;                   // regions must ascend without overlap
@@ -695,7 +707,7 @@ scanpool_tc_kernel(const tc_args a)
 	const unsigned nreg = g_last - g_first;
 	const unsigned P0 = a.R[2 * g_first + 1] - a.R[2 * g_first];
 	const unsigned S0 = nreg > 1 ? a.R[2 * g_first + 2] - a.R[2 * g_first] : P0;
-	bool same = P0 >= 1u && P0 <= 256u && S0 >= P0 && S0 <= 256u && row_hi <= a.n;
+	bool same = !a.rep && P0 >= 1u && P0 <= 256u && S0 >= P0 && S0 <= 256u && row_hi <= a.n;
 	for (unsigned i = threadIdx.x; same && i < nreg; i += TC_THREADS) {
 		const uint2 r = reinterpret_cast<const uint2*>(a.R)[g_first + i];
 		same = r.x == row_lo + i * S0 && r.y - r.x == P0;
@@ -862,7 +874,7 @@ __global__ void tc_prepare_kernel(const float* __restrict__ W, unsigned m, unsig
 	const float scale = f16 ? tc_weight_scale(*maxabs) : 1.f;
 	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
 		const unsigned e = i % 8, fl = (i / 8) % 128, kc = (i / 1024) % KC, tile = (unsigned)(i / ((size_t)1024 * KC));
-		const unsigned k = kc * 8 + e, f = tile * 128 + fl;
+		const unsigned k = kc * 8 + e, f = tc_replicated(nf) ? (fl & 31u) : tile * 128 + fl;
 		float w = ((k < 4 * m && f < nf) ? W[(size_t)k * nf + f] : 0.f) * scale;
 		for (unsigned s = 0; s < nsplit; ++s) {
 			uint16_t bits;
@@ -976,7 +988,7 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int preci
 	a.X = X; a.R = regions; a.Wt = (const __nv_bfloat16*)Wt; a.bias = bias; a.headW = headW; a.headB = headB;
 	a.pooled = pooled; a.scores = scores; a.status = status;
 	a.npos = npos; a.n = npos >= m ? npos - m + 1 : 0; a.nregion = nregion; a.nf = nf; a.m = m; a.KC = KC; a.nsplit = nsplit;
-	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu; a.f16 = f16;
+	a.nmodel = nmodel; a.ptype = ptype; a.relu = relu; a.f16 = f16; a.rep = tc_replicated(nf) ? 1u : 0u;
 	a.maxabs = reinterpret_cast<const uint32_t*>(static_cast<const unsigned char*>(Wt) + (size_t)ntile * nsplit * KC * 2048);
 	a.npeer = scores ? g_tc_npeer : 0u; a.row_off = g_tc_row_off;
 	for (unsigned p = 0; p < a.npeer; ++p) a.peers[p] = g_tc_peers[p];
