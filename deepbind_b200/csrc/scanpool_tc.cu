@@ -503,6 +503,7 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 		tc_fence_after();
 		const unsigned tile_lo = row_lo + t * 256u, tile_hi = min(tile_lo + 256u, row_hi);
 		const uint32_t taddr = tmem_base + ((q4 * 32u) << 16) + slot * 256u;
+		bool released = false;
 		while (ok && g < g_last && r0 < tile_hi) {
 			const unsigned pos = max(r0, tile_lo), end = min(r1, tile_hi);
 			if (end > pos) {
@@ -527,11 +528,21 @@ __device__ __forceinline__ void tc_epilogue(const tc_args& a, uint32_t tmem_base
 				if (live_end < end) ps.add_zero_rows<WANT_MAX, WANT_SUM, RELU>(end - live_end, cm, ca);
 			}
 			if (r1 > tile_hi) break;                       // the region continues in the next tile
+			// The warp's last columns of this tile are in registers once its next region starts
+			// beyond the tile: the tile goes back before the region's outputs are worked out.
+			if (!released && !(g + gstep < g_last && nr0 < tile_hi)) {
+				tc_fence_before();
+				__syncwarp();
+				if (lane == 0) mbar_arrive(&t_empty[slot]);
+				released = true;
+			}
 			ok = finish_region();
 		}
-		tc_fence_before();
-		__syncwarp();
-		if (lane == 0) mbar_arrive(&t_empty[slot]);
+		if (!released) {
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive(&t_empty[slot]);
+		}
 	}
 	// regions that end exactly where the data ends (and empty regions after it)
 	while (ok && g < g_last) ok = finish_region();
