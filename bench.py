@@ -291,7 +291,8 @@ def side_workloads(dev, with_cpu, calibration_models=90):
                                     "strand maximum by db_strand_max") if (ms == ms_tc and ms_tc < ms_exact) else
                                    "f32 lookup-add, bit-exact; strand maximum by db_strand_max",
                          "cpu": cpu_time(lambda: orc.score_net(p, Xh[:Rh[2 * ns - 1, 1] + 15], Rh[:2 * ns], "max", 1, strand_max=True), ns),
-                         "bound": "shared-memory operand return path", "hbm_gbs_algorithmic": (Xh.size + 4 * 200000) / (ms * 1e-3) / 1e9,
+                         "bound": "tensor pipe (8 MMAs of 128 x 256 x 16 per 256 rows; 16 of the tile's 128 filter rows are distinct)"
+                         if (ms == ms_tc and ms_tc < ms_exact) else "shared-memory operand return path", "hbm_gbs_algorithmic": (Xh.size + 4 * 200000) / (ms * 1e-3) / 1e9,
                          **rates(int((Rh[:, 1] - Rh[:, 0]).sum()), NMOTIF, 16, ms)}
     del X, R
 
