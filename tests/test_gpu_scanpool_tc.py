@@ -30,6 +30,8 @@ CASES = [
     (16, 8, 80, 20, 200, 0.05),      # ragged RNA with N: tiles of 36..215 positions
     (24, 9, 30, 200, 400, 0.0),      # regions spanning several 128-column tiles
     (10, 8, 40, 5, 60, 0.1),         # filter length not a multiple of 4 (zero-padded taps)
+    (16, 1, 300, 20, 200, 0.05),     # one model: the 16 filters repeated in every lane quarter, regions shared by all warps
+    (24, 2, 200, 101, 101, 0.0),     # two models (32 filters), equal lengths: still flat tiles
 ]
 
 
@@ -240,3 +242,21 @@ def test_full_size_genome_scan(cuda, orc):
     got = S[torch.from_numpy(pick).cuda()].cpu().numpy()
     assert np.max(np.abs(got - want)) <= 3e-6 * max(scale, np.abs(want).max())
     assert np.max(np.abs(S[torch.from_numpy(pick + half).cuda()].cpu().numpy() - want)) <= 3e-6 * max(scale, np.abs(want).max())
+
+
+def test_one_model_ragged_strand_max_against_the_exact_kernel(cuda):
+    """The ragged both-strand scoring of a single 16-filter model through the tensor-core scan
+    (fp32-grade pieces) against the bit-exact FP32 kernel: scores after the strand maximum."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    p = synth.model_params(1, 16, 51, "max")
+    Xh, Rh = synth.ragged_batch(6000, 20, 200, 16, seed=52, n_frac=0.05, both_strands=True)
+    net = DeepBindNet(p, 1, "max")
+    X, R = dev(Xh), dev(Rh)
+    exact = net.score(X, R, strand_max=True)
+    for prec, tol in (("f16x2", 3e-6), ("bf16x3", 1e-5)):
+        net.prepare_tc(prec)
+        got = net.score_tc(X, R, strand_max=True)
+        assert got.shape == exact.shape == (6000, 1)
+        assert float((got - exact).abs().max()) <= tol * float(exact.abs().max()), prec
