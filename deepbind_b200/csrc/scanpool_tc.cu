@@ -1015,6 +1015,8 @@ DB_EXPORT void db_scanpool_tc(const void* Wt, uint32_t m, uint32_t nf, int preci
 	unsigned want_chunks = max(1u, (8 * sms + ntile - 1) / ntile);
 	want_chunks = divup(want_chunks, step) * step;
 	unsigned spc = max(64u, divup(nregion, want_chunks));
+	// a small batch: fewer sequences per CTA rather than idle SMs (one wave, at least 8 sequences each)
+	if ((size_t)ntile * divup(nregion, spc) < sms) spc = max(8u, divup(nregion, max(1u, sms / ntile)));
 	a.seqs_per_cta = spc;
 	dim3 grid(ntile, divup(nregion, spc));
 	size_t smem = (size_t)nsplit * KC * 2048 + 2 * (size_t)TC_ECHUNKS * 16 + 128;
