@@ -52,6 +52,27 @@ def test_option_struct_layouts():
     assert _lib.c_corr1ord_options_t.nchannel.offset == 4
 
 
+def test_ministep_args_layout_matches_the_header(tmp_path):
+    """ctypes mirror of struct db_ministep_args against the C compiler's layout of the header's."""
+    import shutil
+    import subprocess
+    from deepbind_b200 import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    names = [n for n, _ in _lib.c_ministep_args._fields_]
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "deepbind_b200.h"\nint main(void) {\n'
+                   '  printf("%zu\\n", sizeof(db_ministep_args));\n' +
+                   "".join('  printf("%%zu\\n", offsetof(db_ministep_args, %s));\n' % n for n in names) + "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run([cc, "-I", inc, str(src), "-o", str(exe)], check=True)
+    out = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    assert out[0] == ctypes.sizeof(_lib.c_ministep_args)
+    assert out[1:] == [getattr(_lib.c_ministep_args, n).offset for n in names]
+
+
 def test_compute_without_a_device_fails_loudly():
     import torch
     if torch.cuda.is_available():
