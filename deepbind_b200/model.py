@@ -304,8 +304,9 @@ class DeepBindNet(object):
             else:
                 out = res
         if strand_max:
-            out = out.view(-1, 2, self.I)
-            out = torch.where(out[:, 0] >= out[:, 1], out[:, 0], out[:, 1])
+            both = out.contiguous()
+            out = torch.empty((both.shape[0] // 2, self.I), dtype=torch.float32, device=self.dev)
+            _lib.load().db_strand_max(out.data_ptr(), both.data_ptr(), out.shape[0], self.I)
         return out
 
     def score_chunked(self, X, R, out, chunk=16384):

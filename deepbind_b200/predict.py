@@ -17,11 +17,17 @@ from . import kangaroo_smat as ks
 from . import smat as sm
 
 
-def _score(net, X, R, reverse_complement):
-    return net.score(X, R, strand_max=bool(reverse_complement))
+def _score(net, X, R, reverse_complement, precision=None):
+    if precision is None:
+        return net.score(X, R, strand_max=bool(reverse_complement))
+    tcw = getattr(net, "_tcw", None)
+    if tcw is None or tcw.precision != fused.TC_PRECISION[precision]:
+        net.prepare_tc(precision)
+    return net.score_tc(X, R, strand_max=bool(reverse_complement))
 
 
-def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps=False, max_windows=1 << 21, group=None):
+def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps=False, max_windows=1 << 21, group=None,
+            precision=None):
     """Scores the sequence strings ``seqs`` with every model of ``net``.
 
     Returns a dict of CUDA tensors [nseq, I]: ``direct``; with ``scan`` = window
@@ -30,6 +36,13 @@ def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps
     ``reverse_complement`` both strands are scored and the larger score is kept,
     the forward strand on ties (predict.py:145-164).  Sequences are processed in
     groups of at most ``max_windows`` windows.
+
+    ``precision``: None scores with the exact FP32 kernels (pooled values bit-identical to the
+    operator-by-operator chain); "f16x2" or "bf16x3" with the tensor-core scan at fp32 grade
+    (exact products, another summation order: within 1e-5 of the exact scores, typically
+    below 1e-6), "f16" / "bf16" with one 16-bit piece per weight (5e-4 / 2e-3 of the largest
+    activation).  The weights are prepared once per ``net`` and precision; call
+    ``net.prepare_tc`` again after changing them.
 
     ``group`` (a torch.distributed process group, or "world" for the default one; one
     process per GPU, every rank holding the same ``net`` and ``seqs``): the sequences
@@ -43,7 +56,7 @@ def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps
         rank, world = shard.rank_world(grp)
         if world > 1:
             lo, hi = shard.shard_range(len(seqs), rank, world)
-            mine = predict(net, seqs[lo:hi], scan, stride, reverse_complement, want_pmaps, max_windows) if hi > lo else \
+            mine = predict(net, seqs[lo:hi], scan, stride, reverse_complement, want_pmaps, max_windows, precision=precision) if hi > lo else \
                 {k: torch.empty((0, net.I), dtype=torch.float32, device=net.dev) for k in (("direct", "max", "avg", "sum") if scan else ("direct",))}
             out = {k: shard.gather_scores(v.contiguous(), grp) for k, v in mine.items() if k != "pmaps"}
             if want_pmaps and scan:
@@ -52,7 +65,7 @@ def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps
     pad = net.m - 1
     dev = net.dev
     X, R = fused.build_batch(seqs, pad, reverse_complement, device=dev)
-    out = {"direct": _score(net, X, R, reverse_complement)}
+    out = {"direct": _score(net, X, R, reverse_complement, precision)}
     if not scan:
         return out
     lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=len(seqs))
@@ -67,7 +80,7 @@ def predict(net, seqs, scan=None, stride=1, reverse_complement=False, want_pmaps
         while hi < len(seqs) and total + int(nwin[hi]) <= max_windows:
             total += int(nwin[hi]); hi += 1
         Xw, Rw, woff = fused.build_windows(seqs[lo:hi], scan, stride, pad, reverse_complement, device=dev)
-        Z = _score(net, Xw, Rw, reverse_complement).contiguous()            # [windows, I]: the prediction maps, stacked
+        Z = _score(net, Xw, Rw, reverse_complement, precision).contiguous() # [windows, I]: the prediction maps, stacked
         # per-sequence reductions = region pooling over the rows of Z
         regions = sm.asarray(np.stack([woff[:-1], woff[1:]], axis=1).astype(np.uint32))
         Zs = sm.sarray(Z, np.float32)

@@ -49,6 +49,25 @@ def test_scan_mode(cuda, orc, I, W, stride, rc):
     np.testing.assert_allclose(got["avg"].cpu().numpy(), want["avg"], rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("precision,tol", [("f16x2", 3e-6), ("bf16x3", 1e-5), ("f16", 5e-4)])
+@pytest.mark.parametrize("I,pool,hidden,rc", [(1, "max", 0, True), (3, "all", 0, False), (2, "all", 32, True)])
+def test_tensor_core_precisions_of_the_driver(cuda, orc, precision, tol, I, pool, hidden, rc):
+    """predict(precision=...) scores through the tensor-core scan: direct and scan mode against
+    the oracle, tolerance relative to the largest score of the call."""
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    from deepbind_b200.predict import predict
+    rng = np.random.default_rng(17 + I)
+    m = 24
+    seqs = seqs_of(rng, 120, 20, 130)
+    p = synth.model_params(I, m, 9, pool, hidden=hidden)
+    want = orc.predict(p, seqs, m, pool, I, scan=40, stride=7, reverse_complement=rc)
+    got = predict(DeepBindNet(p, I, pool), seqs, scan=40, stride=7, reverse_complement=rc, precision=precision)
+    for k in ("direct", "max", "avg"):
+        w = np.asarray(want[k])
+        assert np.abs(got[k].cpu().numpy() - w).max() <= 4 * tol * np.abs(w).max() + 1e-6, k
+
+
 @pytest.mark.parametrize("nseq", [500, 40000])
 def test_predict_host_equals_device_scoring(cuda, nseq):
     """Host buffers in, host scores out: the small single-launch path and the
