@@ -353,9 +353,15 @@ def score_net(params, X, R, pool="max", nmodel=1, strand_max=False):
         h = np.maximum(h, 0)
         h = blockwise_dot(h, params["W2"], I) + params["b2"].reshape(1, -1)
     if strand_max:
-        h = h.reshape(-1, 2, I)
-        h = np.where(h[:, 0] >= h[:, 1], h[:, 0], h[:, 1])
+        h = strand_max_rows(h, I)
     return h
+
+
+def strand_max_rows(Z, I=1):
+    """kangaroo/predict.py:144-164: rows are forward / reverse-complement pairs; the forward
+    row is kept if it is >= the other, else the reverse-complement row."""
+    Z = np.asarray(Z).reshape(-1, 2, I)
+    return np.where(Z[:, 0] >= Z[:, 1], Z[:, 0], Z[:, 1])
 
 
 def input_gradients(params, X, R, pool="max", nmodel=1, loss="mse", strand_max=False, dropout_rate=None):
