@@ -330,9 +330,47 @@ def predict(params, seqs, m, pool="max", nmodel=1, scan=None, stride=1, reverse_
     return out
 
 
-# -------------------------------------------------------- composite networks
+# ------------------------------------------------------------- layer math
 def logistic(x):
+    """deepity/std/softmax.py:50-61 with one column per model; elemwise.py:112."""
     return 1.0 / (1.0 + np.exp(-x))
+
+
+def bias_add(X, b):
+    """deepity/std/elemwise.py:171: Z = X + b, b a row vector."""
+    return (X + np.asarray(b, X.dtype).reshape(1, -1)).astype(X.dtype)
+
+
+def relu(X):
+    """deepity/std/elemwise.py:77: Z = maximum(0, X)."""
+    return np.maximum(X, 0).astype(X.dtype)
+
+
+def relu_bprop(dZ, Z):
+    """deepity/std/elemwise.py:78: dX = dZ * sign(Z) with Z the rectified value."""
+    return (dZ * np.sign(Z)).astype(dZ.dtype)
+
+
+def loss(kind, Z, Y, Ymask=None, Zmask=None):
+    """deepity/std/loss.py:52-65,98-112,125-147: (loss [ncol], dZ).  Elementwise term (Z-Y)^2
+    (mse, scaled 1/2) or log(max(1e-15,Z))*Y + log(max(1e-15,1-Z))*(1-Y) (nll, negated), masked,
+    mean over rows; dZ = (Z - Y), masked, times 1/nrow for both."""
+    dt = Z.dtype
+    if kind == "nll":
+        L = np.log(np.maximum(1e-15, Z)) * Y + np.log(np.maximum(1e-15, 1 - Z)) * (1 - Y)
+        scale = -1.0
+    else:
+        L = (Z - Y) ** 2
+        scale = 0.5
+    dZ = (Z - Y).astype(dt)
+    for M in (Ymask, Zmask):
+        if M is not None:
+            L = np.where(M, L, 0)
+            dZ = np.where(M, dZ, 0).astype(dt)
+    return (scale * L.mean(axis=0)).astype(dt), (dZ * dt.type(1.0 / Z.shape[0])).astype(dt)
+
+
+# -------------------------------------------------------- composite networks
 
 
 def score_net(params, X, R, pool="max", nmodel=1, strand_max=False):
@@ -420,46 +458,30 @@ def train_grads(params, X, R, Y, pool="all", nmodel=1, loss="nll", dropmask=None
     nf = params["Wscan"].shape[1]
     X = _c(X, np.uint8).ravel()
     Z0 = corr1ord(params["Wscan"], X)
-    A0 = np.maximum(Z0 + params["bscan"].reshape(1, -1).astype(dt), 0).astype(dt)
+    A0 = relu(bias_add(Z0, params["bscan"]))
     pooled, amax = poolrgn(A0, R, pool, want_argmax=True)
     pd = pooled if dropmask is None else (pooled * dropmask).astype(dt)
-    h1 = (blockwise_dot(pd, params["W1"], I) + params["b1"].reshape(1, -1)).astype(dt)
+    h1 = bias_add(blockwise_dot(pd, params["W1"], I).astype(dt), params["b1"])
     if "W2" in params:
-        a1 = np.maximum(h1, 0).astype(dt)
-        out = (blockwise_dot(a1, params["W2"], I) + params["b2"].reshape(1, -1)).astype(dt)
+        a1 = relu(h1)
+        out = bias_add(blockwise_dot(a1, params["W2"], I).astype(dt), params["b2"])
     else:
         out = h1
     Yb = np.tile(_c(Y, dt).reshape(len(Y), -1), (1, I)) if Y.shape[-1] != I or Y.ndim == 1 else _c(Y, dt)
     nrow = out.shape[0]
-    if loss == "nll":
-        Zo = logistic(out).astype(dt)
-        L = np.log(np.maximum(1e-15, Zo)) * Yb + np.log(np.maximum(1e-15, 1 - Zo)) * (1 - Yb)
-        scale = -1.0
-    else:
-        Zo = out
-        L = (Zo - Yb) ** 2
-        scale = 0.5
-    if Ymask is not None:
-        L = np.where(Ymask, L, 0)
+    Zo = logistic(out).astype(dt) if loss == "nll" else out
     Zmask = None
     if strand_pairs:
         Zmask = np.zeros(Zo.shape, np.uint8)
         calc_zmask(Zo, Zmask)
         Zmask = Zmask.astype(bool)
-        L = np.where(Zmask, L, 0)
-    lossval = scale * L.mean(axis=0)
-    dout = (Zo - Yb).astype(dt)
-    if Ymask is not None:
-        dout = np.where(Ymask, dout, 0).astype(dt)
-    if Zmask is not None:
-        dout = np.where(Zmask, dout, 0).astype(dt)
-    dout = (dout * dt.type(1.0 / nrow)).astype(dt)
+    lossval, dout = globals()["loss"](loss, Zo, Yb, Ymask, Zmask)
     g = {}
     if "W2" in params:
         g["b2"] = dout.sum(axis=0).astype(dt)
         g["W2"] = blockwise_dot_tn(a1, dout, I, params["W2"])
         da1 = blockwise_dot_nt(dout, params["W2"], I)
-        dh1 = (da1 * np.sign(a1)).astype(dt)
+        dh1 = relu_bprop(da1.astype(dt), a1)
     else:
         dh1 = dout
     g["b1"] = dh1.sum(axis=0).astype(dt)
@@ -468,7 +490,7 @@ def train_grads(params, X, R, Y, pool="all", nmodel=1, loss="nll", dropmask=None
     dpooled = dpd if dropmask is None else (dpd * dropmask).astype(dt)
     dA0 = np.zeros_like(A0)
     poolrgn_bprop(dA0, R, dpooled, amax, pool)
-    dZ0 = (dA0 * np.sign(A0)).astype(dt)
+    dZ0 = relu_bprop(dA0, A0)
     g["bscan"] = dZ0.sum(axis=0).astype(dt)
     g["Wscan"] = corr1ord_bprop_W(np.zeros_like(params["Wscan"]), X, dZ0)
     if decay:

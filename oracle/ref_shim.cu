@@ -12,7 +12,10 @@
 #include <smat_cuda/cuda_context.h>
 #include <smat_cuda/cuda_errors.h>
 #include <base/assert.h>
+#include <smat/vm/argument.h>
+#include <smat/vm/instruction_db.h>
 #include "kangaroo_smat.h"
+#include <cstring>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -157,6 +160,11 @@ void assert_failed(const char* fmt, ...)
 	char buf[512]; va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof buf, fmt, ap); va_end(ap);
 	throw std::runtime_error(buf);
 }
+const char* dtype2str(dtype_t dt)
+{
+	static const char* names[] = {"b8", "i8", "u8", "i16", "u16", "i32", "u32", "i64", "u64", "f32", "f64"};
+	return (unsigned)dt < 11u ? names[dt] : "?";
+}
 unsigned lcm(unsigned a, unsigned b)
 {
 	unsigned x = a, y = b;
@@ -249,3 +257,43 @@ REF_API int ref_blockwise_dot_nt_combined(int dtype, int nblock, int Xoffset, in
 REF_API int ref_blockwise_dot_tn_combined(int dtype, int nblock, int Xoffset, int bcast, int n, int m, int k, int p,
                                           const void* X, void* dW, const void* dZ)
 { REF_TRY launch_blockwise_dot_tn_combined(0, (dtype_t)dtype, nblock, Xoffset, bcast != 0, n, m, k, p, X, dW, dZ); REF_CATCH }
+
+// ---- smat's element-wise kernels: what the reference's bias, rectify, logistic and loss nodes
+// run on (deepity/std/elemwise.py:71-82,162-180, softmax.py:50-61, loss.py:125-155).
+SM_NAMESPACE_BEGIN
+void execute_elemwise2(opcode_t opcode, const argument& a, const argument& b);
+void execute_elemwise3(opcode_t opcode, const argument& a, const argument& b, const argument& c);
+SM_NAMESPACE_END
+
+// Opcode of a built-in element-wise instruction by name (smat/vm/instruction_db.h:56-125), -1 if unknown.
+REF_API int ref_opcode(const char* name)
+{
+	static const struct { const char* n; int oc; } tab[] = {
+		{"add", oc_add}, {"sub", oc_sub}, {"mul", oc_mul}, {"div", oc_div}, {"maxe", oc_maxe}, {"mine", oc_mine},
+		{"exp", oc_exp}, {"log", oc_log}, {"sigm", oc_sigm}, {"sign", oc_sign}, {"sqr", oc_sqr}, {"neg", oc_neg}, {"abs", oc_abs},
+	};
+	for (const auto& t : tab) if (!strcmp(t.n, name)) return t.oc;
+	return -1;
+}
+
+// b = f(a), arrays [nrow, ncol]
+REF_API int ref_elemwise2(int opcode, int dtype, const void* a, void* b, unsigned nrow, unsigned ncol)
+{
+	REF_TRY
+	execute_elemwise2((opcode_t)opcode, darray((size_t)a, (dtype_t)dtype, shape_t(ncol, nrow)), darray((size_t)b, (dtype_t)dtype, shape_t(ncol, nrow)));
+	REF_CATCH
+}
+
+// c = f(a, b) with smat's broadcasting: a and b are arrays [arow, acol], [brow, bcol] (a row
+// vector, a column vector or a 1 x 1 array broadcast against the other), or, with a NULL
+// pointer, the f32 constant given beside it; c has the broadcast shape.
+REF_API int ref_elemwise3(int opcode, int dtype, const void* a, float aconst, unsigned arow, unsigned acol,
+                          const void* b, float bconst, unsigned brow, unsigned bcol, void* c)
+{
+	REF_TRY
+	const unsigned crow = arow > brow ? arow : brow, ccol = acol > bcol ? acol : bcol;
+	argument A = a ? darray((size_t)a, (dtype_t)dtype, shape_t(acol, arow)) : carray(aconst);
+	argument B = b ? darray((size_t)b, (dtype_t)dtype, shape_t(bcol, brow)) : carray(bconst);
+	execute_elemwise3((opcode_t)opcode, A, B, darray((size_t)c, (dtype_t)dtype, shape_t(ccol, crow)));
+	REF_CATCH
+}
