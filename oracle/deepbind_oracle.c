@@ -9,8 +9,9 @@
  *
  * Parity status: the reference ships no golden vectors for this path, so the
  * oracle is pinned by (a) hand-derived known-answer cases in the tests and
- * (b) the reference's own CUDA kernels compiled for the test GPU and run on the
- * same inputs (see ref_shim.cu).  Each function cites the reference source it
+ * (b) the reference's own CUDA kernels and launchers -- every kernel restated in
+ * this file -- compiled for the test GPU and run on the same inputs (see
+ * build_ref.sh, ref_shim.cu).  Each function cites the reference source it
  * follows (paths relative to the reference tree).
  *
  * Build: gcc -O3 -march=native -fopenmp -ffp-contract=off -fno-fast-math

@@ -6,9 +6,16 @@ losses and the composite networks.  Nothing in the product package imports this
 module; the tests, the smoke check and the benchmark's CPU-baseline legs do.
 
 Parity status: the reference holds no golden vectors for this path.  The oracle
-is pinned by hand-derived known-answer cases (tests/test_oracle_kat.py) and, on
-a GPU, by the reference's own CUDA kernels compiled from its sources
-(oracle/ref_shim.cu, tests/test_gpu_ref_kernels.py).
+is pinned by the reference's own code run beside it: its CUDA kernels and launchers
+(scan, pooling, update, masks, dropout, block-diagonal products, smat's element-wise
+kernels under the layer math) compiled from its sources for the test GPU
+(oracle/build_ref.sh, oracle/ref_shim.cu; tests/test_gpu_ref_kernels.py,
+tests/test_gpu_ref_deepity.py, tests/test_gpu_ref_layers.py), and the Python it uses
+for ordinal encoding, reverse complement, batch assembly and strand selection, executed
+where it lies into a committed fixture (tests/golden/make_ref_util.py,
+tests/test_ref_util_tables.py); plus hand-derived known-answer cases
+(tests/test_oracle_kat.py).  Not pinned by reference code: column sums of the bias
+gradient (the reference's reduction order is its own) and random initialisation.
 
 All arrays are C-contiguous NumPy arrays; layouts follow the reference:
 W [4m, nf] (tap-major, channel, filter fastest), X uint8 [npos], regions
