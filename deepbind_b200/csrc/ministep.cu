@@ -111,6 +111,9 @@ ministep_sample_kernel(const ministep_dev d)
 		const unsigned c = a.counters ? *reinterpret_cast<volatile const uint32_t*>(a.counters) % a.nbatch : 0u;
 		s_slot = a.order ? a.order[c] : c;
 	}
+	// The update kernel may be scheduled now (programmatic dependent launch): it fetches the
+	// parameters' state and then waits for this whole grid before it touches anything we read or write.
+	asm volatile("griddepcontrol.launch_dependents;");
 	// everything that does not depend on the minibatch is fetched while the slot is looked up
 	const float* PL = a.PL;
 	build_lut(lut, PL + a.off_Wscan, m, nf, b * F, F);
@@ -404,7 +407,6 @@ ministep_update_kernel(const ministep_dev d)
 	const unsigned e = blockIdx.x * US_E + lane;
 	const unsigned NS = (4 * m + 1) * F, NH = np * HC + HC + (H ? H + 1 : 0);
 	__shared__ float sums[US_S][US_E];
-	if (b == 0 && blockIdx.x == 0 && threadIdx.x == 0 && a.counters) *a.counters = *a.counters + 1;
 	const float* rec = d.rec + (size_t)b * B * RS;
 	const unsigned per = (B + US_S - 1) / US_S, s0 = min(B, w * per), s1 = min(B, s0 + per);
 	float g = 0.f;
@@ -435,6 +437,11 @@ ministep_update_kernel(const ministep_dev d)
 		pl = a.PL[pi]; mr = a.mrate[pi]; dr = a.drate[pi]; mp0 = a.mP[pi];
 		if (a.decay) dc = a.decay[pi];
 	}
+	// Launched as a programmatic dependent of the sample kernel, this grid may have started while
+	// that one was still running: from here on everything depends on its results (and nothing
+	// above was written by it or is still read by it).
+	asm volatile("griddepcontrol.wait;" ::: "memory");
+	if (b == 0 && blockIdx.x == 0 && threadIdx.x == 0 && a.counters) *a.counters = *a.counters + 1;
 	if (p0) {
 		for (unsigned s = s0; s < s1; s += 16) {
 			float x0[16], x1[16];
@@ -560,7 +567,16 @@ DB_EXPORT void db_ministep(const db_ministep_args* args)
 	else launch(ministep_sample_kernel<0>);
 	DB_LAUNCH_CHECK();
 	const unsigned nelem = (4 * a.m + 1) * a.nfilt + d.np * d.HC + d.HC + (a.hidden ? a.hidden + 1 : 0) + 1;
-	ministep_update_kernel<<<dim3(divup(nelem, (unsigned)US_E), a.nmodel), US_E * US_S, 0, state().stream>>>(d);
+	{
+		cudaLaunchConfig_t cfg = {};
+		cfg.gridDim = dim3(divup(nelem, (unsigned)US_E), a.nmodel); cfg.blockDim = dim3(US_E * US_S);
+		cfg.dynamicSmemBytes = 0; cfg.stream = state().stream;
+		cudaLaunchAttribute attr[1];
+		attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attr[0].val.programmaticStreamSerializationAllowed = 1;
+		cfg.attrs = attr; cfg.numAttrs = 1;
+		DB_CUDA(cudaLaunchKernelEx(&cfg, ministep_update_kernel, d));
+	}
 	DB_LAUNCH_CHECK();
 	DB_API_CATCH
 }
