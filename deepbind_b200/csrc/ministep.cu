@@ -73,11 +73,12 @@ __host__ __device__ inline ms_layout ms_strand_layout(unsigned max_rows, unsigne
 }
 __host__ __device__ inline unsigned ms_common_bytes(unsigned m, unsigned F, unsigned np, unsigned HC)
 {
-	return (m * (F / 4) * 32 + F + ((HC + 3) & ~3u) + np * HC) * 4;      // lut, bias, w2, W1
+	return (m * (F / 4) * 32 + F + ((HC + 3) & ~3u) + np * (HC + 1)) * 4;      // lut, bias, w2, W1 (rows padded by one)
 }
 
+// 80 registers: six CTAs of 128 threads per SM, so that 12 models x 64 samples are one wave.
 template <int M>
-__global__ void __launch_bounds__(2 * MS_T)
+__global__ void __maxnreg__(80)
 ministep_sample_kernel(const ministep_dev d)
 {
 	extern __shared__ __align__(16) unsigned char smem[];
@@ -115,15 +116,53 @@ ministep_sample_kernel(const ministep_dev d)
 	// parameters' state and then waits for this whole grid before it touches anything we read or write.
 	asm volatile("griddepcontrol.launch_dependents;");
 	// everything that does not depend on the minibatch is fetched while the slot is looked up
+	// All of it is requested before any of it is used: one trip to L2 instead of one per array.
 	const float* PL = a.PL;
-	build_lut(lut, PL + a.off_Wscan, m, nf, b * F, F);
-	for (unsigned t = threadIdx.x; t < F; t += blockDim.x) sb[t] = PL[a.off_bscan + b * F + t];
-	if (H) for (unsigned t = threadIdx.x; t < H; t += blockDim.x) w2s[t] = PL[a.off_W2 + b * H + t];
-	for (unsigned t = threadIdx.x; t < np * HC; t += blockDim.x) w1s[t] = PL[a.off_W1 + (size_t)b * np * HC + t];
 	const float b1v = tid < HC ? PL[a.off_b1 + b * HC + tid] : 0.f;
 	const float b2v = H ? PL[a.off_b2 + b] : 0.f;
 	uint2 rg0 = make_uint2(0u, 0u);
 	if (a.R_stride == 0) rg0 = make_uint2(a.R[2 * row_id], a.R[2 * row_id + 1]);    // one region table for all minibatches
+	const unsigned lf = F == 16 ? 4u : 5u;                               // F is 16 or 32
+	const unsigned WS = HC + 1;                                          // row stride of W1 in shared memory: no bank conflicts either way
+	{
+		const float* W = PL + a.off_Wscan + b * F;
+		const float* W1g = PL + a.off_W1 + (size_t)b * np * HC;
+		const unsigned nlut = m * F, nw1 = np * HC, nt = blockDim.x;
+		for (unsigned base = 0; base < max(nlut, nw1); base += 4 * nt) {
+			float4 w[4]; float v1[4];
+			#pragma unroll
+			for (int i = 0; i < 4; ++i) {
+				const unsigned t = base + i * nt + threadIdx.x;
+				w[i] = make_float4(0.f, 0.f, 0.f, 0.f); v1[i] = 0.f;
+				if (t < nlut) {
+					const unsigned j = t >> lf, f = t & (F - 1);
+					w[i] = make_float4(W[(size_t)(4 * j + 0) * nf + f], W[(size_t)(4 * j + 1) * nf + f],
+					                   W[(size_t)(4 * j + 2) * nf + f], W[(size_t)(4 * j + 3) * nf + f]);
+				}
+				if (t < nw1) v1[i] = W1g[t];
+			}
+			float bs = 0.f, w2v = 0.f;
+			if (base == 0) {
+				if (threadIdx.x < F) bs = PL[a.off_bscan + b * F + threadIdx.x];
+				if (threadIdx.x < H) w2v = PL[a.off_W2 + b * H + threadIdx.x];
+			}
+			#pragma unroll
+			for (int i = 0; i < 4; ++i) {
+				const unsigned t = base + i * nt + threadIdx.x;
+				if (t < nlut) {                                              // the table entry of build_lut: four channels, their mean for N, zeros
+					const unsigned j = t >> lf, f = t & (F - 1);
+					float z = w[i].x; z += w[i].y; z += w[i].z; z += w[i].w;
+					float* e = lut + ((size_t)(j * NQ + f / 4) * 8) * 4 + (f & 3);
+					e[0] = w[i].x; e[4] = w[i].y; e[8] = w[i].z; e[12] = w[i].w; e[16] = z * 0.25f; e[20] = 0.f; e[24] = 0.f; e[28] = 0.f;
+				}
+				if (t < nw1) w1s[(t / HC) * WS + t % HC] = v1[i];
+			}
+			if (base == 0) {
+				if (threadIdx.x < F) sb[threadIdx.x] = bs;
+				if (threadIdx.x < H) w2s[threadIdx.x] = w2v;
+			}
+		}
+	}
 	__syncthreads();
 	const size_t slot = s_slot;
 	const uint8_t* X = a.X + slot * a.X_stride;
@@ -185,7 +224,7 @@ ministep_sample_kernel(const ministep_dev d)
 	const unsigned PP = min((unsigned)MS_PP, T / F);                     // row slices of the pooling pass
 	const unsigned slice = (rows + PP - 1) / PP;
 	if (tid < PP * F) {
-		const unsigned f = tid % F, part = tid / F;
+		const unsigned f = tid & (F - 1), part = tid >> lf;
 		const unsigned ra = min(rows, part * slice), rb = min(rows, ra + slice);
 		float xmax = 0.f, xsum = 0.f; unsigned xi = 0xffffffffu;
 		if (ra < rb) {
@@ -227,7 +266,7 @@ ministep_sample_kernel(const ministep_dev d)
 	// ---- dense head, forward
 	if (tid < HC) {
 		float s = 0.f;
-		for (unsigned u = 0; u < np; ++u) s = fmaf(pd[u], w1s[u * HC + tid], s);
+		for (unsigned u = 0; u < np; ++u) s = fmaf(pd[u], w1s[u * WS + tid], s);
 		s = s + b1v;
 		h1[tid] = s;
 		a1[tid] = s > 0.f ? s : 0.f;
@@ -262,7 +301,7 @@ ministep_sample_kernel(const ministep_dev d)
 	__syncthreads();
 	if (tid < np) {
 		float s = 0.f;
-		for (unsigned c = 0; c < HC; ++c) s = fmaf(dh[c], w1s[tid * HC + c], s);
+		for (unsigned c = 0; c < HC; ++c) s = fmaf(dh[c], w1s[tid * WS + c], s);
 		dpd[tid] = kept ? s : 0.f;
 	}
 	{   // the sample's record for the update kernel: pd | a1 | dh | dout | loss
@@ -296,7 +335,7 @@ ministep_sample_kernel(const ministep_dev d)
 	const bool only_max = a.ptype == DB_PT_MAX;
 	if (!only_max) {
 		for (unsigned t = tid; t < rows * F; t += T) {
-			const unsigned r = t / F, f = t % F;
+			const unsigned r = t >> lf, f = t & (F - 1);
 			float v = 0.f;
 			if (act[r * AS + f] > 0.f) {
 				v = davg[f];
@@ -323,7 +362,7 @@ ministep_sample_kernel(const ministep_dev d)
 			#pragma unroll
 			for (int k = 0; k < 4; ++k) c[q][k] = 0.f;
 		if (on && unit < nunit) {
-			const unsigned j0 = 4 * (unit / F), fl = unit % F;
+			const unsigned j0 = 4 * (unit >> lf), fl = unit & (F - 1);
 			const float4* ohj = oh + j0;
 			if (only_max) {
 				const unsigned r = amax[fl];
@@ -381,7 +420,7 @@ ministep_sample_kernel(const ministep_dev d)
 		}
 		if (on && split == 0) {
 			if (unit < nunit) {
-				const unsigned j0 = 4 * (unit / F), fl = unit % F;
+				const unsigned j0 = 4 * (unit >> lf), fl = unit & (F - 1);
 				#pragma unroll
 				for (int q = 0; q < 4; ++q)
 					if (j0 + q < m) {
