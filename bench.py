@@ -273,8 +273,7 @@ def side_workloads(dev, with_cpu, calibration_models=90):
     for _ in range(3):
         tc_graph.replay()
     ms_tc = _events_ms(tc_graph.replay, 50)
-    assert int(tc_status.item()) == 0
-    use_tc = tc_err <= 1e-5 and ms_tc < ms_exact
+    use_tc = tc_err <= 1e-5 and ms_tc < ms_exact and int(tc_status.item()) == 0
     ms = ms_tc if use_tc else ms_exact
     out["pbm_forward"] = {"unit": "sequences/s", "value": 4096 / ms * 1e3, "ms": ms, "ms_separate_launches": ms_eager,
                           "ms_exact_f32_kernel_graph": ms_exact, "ms_tensor_core_f16x2_graph": ms_tc,
@@ -359,7 +358,8 @@ def side_workloads(dev, with_cpu, calibration_models=90):
                 graph2.replay()
             ms2 = _events_ms(graph2.replay, reps // K) / K
             torch.cuda.synchronize()
-            assert int(mstep.status.item()) == 0 and bool(torch.isfinite(net2.P).all())
+            if int(mstep.status.item()) != 0 or not bool(torch.isfinite(net2.P).all()):
+                ms2 = None                            # a failed or diverged run is not a timing
         ms = ms7 if ms2 is None else min(ms7, ms2)
         cpu = None
         if with_cpu:
