@@ -319,7 +319,8 @@ class DeepBindNet(object):
             out[s:e].copy_(self.score(X, R[s:e]))
         return out
 
-    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False, npiece=16, on_piece=None, before_piece=None):
+    def predict_host(self, X_host, R_host, out_host, chunk=16384, dev_bufs=None, tc=False, npiece=16, on_piece=None, before_piece=None,
+                     wait=True):
         """The call a user makes for scoring: ordinal batch in (pinned) host
         memory -> scores in (pinned) host memory.  Mirrors what
         kangaroo.predict does per batch (code/libs/kangaroo/kangaroo/predict.py:168-176):
@@ -328,7 +329,15 @@ class DeepBindNet(object):
         (``shard.shard_range(nseq, c, npiece)``) and ``on_piece(lo, hi)``, if given, is
         called right after piece [lo, hi) was enqueued on the current stream (a caller
         with several GPUs starts that piece's all-gather there); ``before_piece(lo, hi)``
-        is called just before the piece's scan is enqueued."""
+        is called just before the piece's scan is enqueued.
+
+        ``wait=False`` (pipelined path only) returns as soon as everything is enqueued:
+        a caller streaming batch after batch through the same device buffers calls
+        again at once, and the next batch's uploads and scans run while this batch's
+        last scores are still on their way to the host (piece c of the next call waits
+        only for piece c of this one: its scan for the upload, its read-back for the
+        scan); :meth:`predict_host_wait` synchronises and raises if any scan since the
+        last wait failed (a failed scan makes the later ones return at once)."""
         if dev_bufs is None:
             dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.dev),
                         torch.empty(R_host.shape, dtype=torch.int32, device=self.dev),
@@ -338,7 +347,8 @@ class DeepBindNet(object):
         if tc:
             if not hasattr(self, "_status"):
                 self._status = torch.zeros(1, dtype=torch.int32, device=self.dev)
-            self._status.zero_()                # a failure of an earlier call must not outlive it
+            if getattr(self, "_pipe", None) is None:
+                self._status.zero_()            # a failure of an earlier, finished call must not outlive it
         if tc and self.hidden == 0 and self.nf == 16 * self.I and self.dropout_rate is None and R.shape[0] >= 8 * 4096:
             # Both transfers are pipelined with the scan, piece by piece: the bases of the next
             # piece go up on one side stream and the scores of the last piece come back on another
@@ -353,16 +363,27 @@ class DeepBindNet(object):
             npiece = max(1, min(int(npiece), nseq))
             cuts = [shard_range(nseq, c, npiece)[0] for c in range(npiece)] + [nseq]
             first = [int(R_host[lo, 0]) for lo in cuts[:-1]] + [npos]          # regions ascend (the batch layout)
-            self._up_stream.wait_stream(cur)
-            ups = []
+            # a call still in flight on the same buffers and cuts: piece by piece dependencies; anything else: all of it first
+            key = (X.data_ptr(), out.data_ptr(), tuple(cuts))
+            prev = getattr(self, "_pipe", None)
+            if prev is not None and prev["key"] != key:
+                self.predict_host_wait()
+                prev = None
+            if prev is None:
+                self._up_stream.wait_stream(cur)
+            ups, dones, reads = [], [], []
             with torch.cuda.stream(self._up_stream):
                 for c in range(npiece):
+                    if prev is not None:            # the rows this upload overwrites were read by scans c and c+1 of the call before
+                        self._up_stream.wait_event(prev["done"][min(c + 1, npiece - 1)])
                     a0, a1 = first[c], min(npos, first[c + 1] + self.m - 1)    # the piece's rows and the taps' reach past them
                     X[a0:a1].copy_(X_host[a0:a1], non_blocking=True)
                     ev = torch.cuda.Event(); ev.record(self._up_stream); ups.append(ev)
             for c in range(npiece):
                 lo, hi = cuts[c], cuts[c + 1]
                 cur.wait_event(ups[c])
+                if prev is not None:
+                    cur.wait_event(prev["read"][c])  # the scores this scan overwrites have reached the host
                 if before_piece is not None:
                     before_piece(lo, hi)
                 self.score_tc(X, R[lo:hi], check=False, out=out[lo:hi], status=self._status)
@@ -370,12 +391,14 @@ class DeepBindNet(object):
                     on_piece(lo, hi)
                 done = torch.cuda.Event()
                 done.record(cur)
+                dones.append(done)
                 self._copy_stream.wait_event(done)
                 with torch.cuda.stream(self._copy_stream):
                     out_host[lo:hi].copy_(out[lo:hi], non_blocking=True)
-            self._copy_stream.synchronize()
-            cur.synchronize()
-            self._check_tc_status()
+                    rd = torch.cuda.Event(); rd.record(self._copy_stream); reads.append(rd)
+            self._pipe = {"key": key, "done": dones, "read": reads}
+            if wait:
+                self.predict_host_wait()
             return out_host
         X.copy_(X_host, non_blocking=True)
         R.copy_(R_host, non_blocking=True)
@@ -390,6 +413,16 @@ class DeepBindNet(object):
         if tc:
             self._check_tc_status()
         return out_host
+
+    def predict_host_wait(self):
+        """Waits for every :meth:`predict_host` call enqueued with ``wait=False`` and raises if
+        a scan among them failed."""
+        if getattr(self, "_pipe", None) is None:
+            return
+        self._copy_stream.synchronize()
+        torch.cuda.current_stream().synchronize()
+        self._pipe = None
+        self._check_tc_status()
 
     def _check_tc_status(self):
         """Raises if a tensor-core scan of the call just synchronised gave up (1 = a

@@ -262,11 +262,14 @@ class ShardedScorer(object):
         after every rank's scan, enqueued before it, has finished."""
         self._dist.all_reduce(self._flag, group=self.group)
 
-    def run_host(self, X_host, R_host, out_host, dev_bufs=None):
+    def run_host(self, X_host, R_host, out_host, dev_bufs=None, wait=True):
         """The same from (pinned) host buffers to (pinned) host scores of this rank's
         shard: upload, scan and read-back are pipelined piece by piece
         (``DeepBindNet.predict_host``) and, with several ranks, every piece's all-gather
-        starts as soon as the piece is enqueued.  Synchronises before it returns."""
+        starts as soon as the piece is enqueued.  Synchronises before it returns, unless
+        ``wait=False`` (one rank, or the peer gather): then the call returns once everything
+        is enqueued, the next call's uploads and scans overlap this call's last read-backs
+        piece by piece, and :meth:`wait_host` synchronises and reports a failed scan."""
         if dev_bufs is None:
             dev_bufs = (torch.empty(X_host.shape, dtype=torch.uint8, device=self.net.dev),
                         torch.empty(R_host.shape, dtype=torch.int32, device=self.net.dev), self.scores)
@@ -280,18 +283,20 @@ class ShardedScorer(object):
                 dll().db_scanpool_tc_peers(tab, len(others), self.rank * self.nseq + lo)
             try:
                 self.net.predict_host(X_host, R_host, out_host, dev_bufs=(dev_bufs[0], dev_bufs[1], self.scores), tc=True,
-                                      npiece=self.nchunk, before_piece=piece_rows)
+                                      npiece=self.nchunk, before_piece=piece_rows, wait=wait)
             finally:
                 dll().db_scanpool_tc_peers(None, 0, 0)
             self._peer_barrier()
-            torch.cuda.current_stream().synchronize()
+            if wait:
+                torch.cuda.current_stream().synchronize()
             return out_host
 
         def gather_piece(lo, hi):
             c = len(works)
             works.append(self._dist.all_gather_into_tensor(self.chunks[c], self.scores[lo:hi], group=self.group, async_op=True))
         self.net.predict_host(X_host, R_host, out_host, dev_bufs=(dev_bufs[0], dev_bufs[1], self.scores), tc=True,
-                              npiece=self.nchunk, on_piece=gather_piece if self.world > 1 else None)
+                              npiece=self.nchunk, on_piece=gather_piece if self.world > 1 else None,
+                              wait=wait or self.world > 1)
         if self.world > 1 and not works:         # a batch too small for the pipelined path: gather it now
             shard.chunked_gather(lambda lo, hi: None, self.scores, self.chunks, self.group)
         for w in works:
@@ -299,6 +304,11 @@ class ShardedScorer(object):
         if self.world > 1:
             torch.cuda.current_stream().synchronize()
         return out_host
+
+    def wait_host(self):
+        """Completes the :meth:`run_host` calls made with ``wait=False``."""
+        self.net.predict_host_wait()
+        torch.cuda.current_stream().synchronize()
 
     def check(self):
         st = int(self.status.item())

@@ -94,6 +94,38 @@ def test_predict_host_equals_device_scoring(cuda, nseq):
     assert torch.equal(out2, exact)
 
 
+def test_predict_host_streamed_batches(cuda):
+    """Three different batches streamed through the same device buffers with wait=False: each
+    batch's host scores equal one device launch on that batch (the pieces of a call wait only for
+    the same pieces of the call before), and a later call with other cuts first drains the pipe."""
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    m, I, nseq = 24, 16, 40000
+    net = DeepBindNet(synth.model_params(I, m, 7, "all"), I, "all")
+    net.prepare_tc("f16x2")
+    dev_bufs = None
+    hosts = []
+    for seed in (1, 2, 3):
+        Xh, Rh = synth.uniform_batch(nseq, 60, m, seed=seed)
+        hosts.append((torch.from_numpy(Xh).pin_memory(), torch.from_numpy(Rh.view(np.int32)).pin_memory(),
+                      torch.empty((nseq, I), dtype=torch.float32).pin_memory()))
+    X = torch.empty(hosts[0][0].shape, dtype=torch.uint8, device=cuda)
+    R = torch.empty(hosts[0][1].shape, dtype=torch.int32, device=cuda)
+    out = torch.empty((nseq, I), dtype=torch.float32, device=cuda)
+    for Xh, Rh, oh in hosts:
+        net.predict_host(Xh, Rh, oh, dev_bufs=(X, R, out), tc=True, npiece=8, wait=False)
+    net.predict_host_wait()
+    for Xh, Rh, oh in hosts:
+        want = net.score_tc(Xh.cuda(), Rh.cuda())
+        assert torch.equal(oh, want.cpu())
+    # other cuts on the same buffers: the pending calls are completed first
+    net.predict_host(hosts[0][0], hosts[0][1], hosts[0][2], dev_bufs=(X, R, out), tc=True, npiece=8, wait=False)
+    net.predict_host(hosts[1][0], hosts[1][1], hosts[1][2], dev_bufs=(X, R, out), tc=True, npiece=5)
+    assert torch.equal(hosts[1][2], net.score_tc(hosts[1][0].cuda(), hosts[1][1].cuda()).cpu())
+    assert torch.equal(hosts[0][2], net.score_tc(hosts[0][0].cuda(), hosts[0][1].cuda()).cpu())
+
+
 @pytest.mark.parametrize("hidden,rate,I", [(32, 0.5, 3), (32, None, 2), (0, 0.25, 2)])
 def test_predict_host_tensor_core_with_a_dense_head(cuda, hidden, rate, I):
     """Nets whose head is not the in-kernel linear one (hidden layer, test-mode dropout)
