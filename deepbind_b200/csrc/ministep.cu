@@ -40,7 +40,7 @@
 namespace db {
 
 static constexpr int MS_T = 256;          // threads per sample, at most (128 for short regions)
-static constexpr int MS_PP = 8;           // row slices of the pooling pass
+static constexpr int MS_PP = 16;          // row slices of the pooling pass, at most
 static constexpr int US_E = 32;           // parameters per CTA of the update kernel
 static constexpr int US_S = 8;            // sample slices of the update kernel (one warp each)
 
@@ -334,14 +334,16 @@ ministep_sample_kernel(const ministep_dev d)
 	__syncthreads();
 	const bool only_max = a.ptype == DB_PT_MAX;
 	if (!only_max) {
-		for (unsigned t = tid; t < rows * F; t += T) {
-			const unsigned r = t >> lf, f = t & (F - 1);
+		// a thread keeps its filter: its mean share, maximum delta and argmax row stay in registers
+		const unsigned f = tid & (F - 1), rstep = T >> lf;
+		const float va = davg[f], vm = a.ptype == DB_PT_ALL ? dmax[f] : 0.f;
+		const unsigned am = a.ptype == DB_PT_ALL ? amax[f] : 0xffffffffu;
+		float* col = act + f;
+		#pragma unroll 4
+		for (unsigned r = tid >> lf; r < rows; r += rstep) {
 			float v = 0.f;
-			if (act[r * AS + f] > 0.f) {
-				v = davg[f];
-				if (a.ptype == DB_PT_ALL && amax[f] == r) v = v + dmax[f];
-			}
-			act[r * AS + f] = v;
+			if (col[r * AS] > 0.f) v = r == am ? va + vm : va;
+			col[r * AS] = v;
 		}
 		__syncthreads();
 	}
