@@ -188,27 +188,27 @@ ministep_sample_kernel(const ministep_dev d)
 	}
 	__syncthreads();
 
-	// ---- scan + bias + rectify: a thread owns one row x 16 filters per pass; and the channel
+	// ---- scan + bias + rectify: a thread owns one row x 8 filters per pass; and the channel
 	// weights of every input row for the backward pass (one-hot, 1/4 each for N, 0 for a dropped base)
 	{
-		const unsigned FG = F / 16, TRK = T / FG;
-		const unsigned rl = tid % TRK, fg = tid / TRK;
-		const unsigned char* lutp = reinterpret_cast<const unsigned char*>(lut) + fg * 512;
+		const unsigned FH = F / 8, TRK = T / FH;                        // half groups of 8 filters; rows per pass
+		const unsigned rl = tid % TRK, fh = tid / TRK;
+		const unsigned char* lutp = reinterpret_cast<const unsigned char*>(lut) + fh * 256;
 		for (unsigned p0 = 0; p0 < rows; p0 += TRK) {
 			const unsigned row = p0 + rl;
 			if (row >= rows) continue;
-			float z[16];
-			if (row < rows_w) scan_row<M>(lutp, NQ * 128, xs, row, m, z);
+			float z[8];
+			if (row < rows_w) scan_row_half<M>(lutp, NQ * 128, xs, row, m, z);
 			else {
 				#pragma unroll
-				for (int v = 0; v < 16; ++v) z[v] = 0.f;
+				for (int v = 0; v < 8; ++v) z[v] = 0.f;
 			}
 			#pragma unroll
-			for (int v = 0; v < 16; v += 4) {
-				const float4 q = *reinterpret_cast<const float4*>(sb + fg * 16 + v);
+			for (int v = 0; v < 8; v += 4) {
+				const float4 q = *reinterpret_cast<const float4*>(sb + fh * 8 + v);
 				float4 x = make_float4(z[v] + q.x, z[v + 1] + q.y, z[v + 2] + q.z, z[v + 3] + q.w);
 				x.x = x.x > 0.f ? x.x : 0.f; x.y = x.y > 0.f ? x.y : 0.f; x.z = x.z > 0.f ? x.z : 0.f; x.w = x.w > 0.f ? x.w : 0.f;
-				*reinterpret_cast<float4*>(act + row * AS + fg * 16 + v) = x;
+				*reinterpret_cast<float4*>(act + row * AS + fh * 8 + v) = x;
 			}
 		}
 		for (unsigned t = tid; t < rows + m + 4; t += T) {

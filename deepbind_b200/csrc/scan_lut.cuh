@@ -69,6 +69,41 @@ __device__ __forceinline__ void scan_row(const unsigned char* lutp, unsigned str
 	}
 }
 
+// The same for eight filters (two of the four quads of a 16-filter group; `lutp` points at the
+// first of them): two threads share a row where a lone warp per scheduler would otherwise
+// wait out its shared-memory loads.
+template <int M>
+__device__ __forceinline__ void scan_row_half(const unsigned char* lutp, unsigned stride, const uint8_t* xs,
+                                              unsigned rl, unsigned m, float (&z)[8])
+{
+	#pragma unroll
+	for (int v = 0; v < 8; ++v) z[v] = 0.f;
+	if constexpr (M > 0) {
+		constexpr int NW = (M + 3) / 4;
+		const uint32_t* xw = reinterpret_cast<const uint32_t*>(xs) + (rl >> 2);
+		const unsigned sh = (rl & 3u) * 8u;
+		uint32_t win[NW];
+		#pragma unroll
+		for (int i = 0; i < NW; ++i) win[i] = __funnelshift_r(xw[i], xw[i + 1], sh);
+		#pragma unroll
+		for (int j = 0; j < M; ++j) {
+			unsigned c16 = (win[j >> 2] >> (8 * (j & 3))) & 0xffu;
+			const float4* e = reinterpret_cast<const float4*>(lutp + (size_t)j * stride + c16);
+			float4 a = e[0], b = e[8];
+			z[0] += a.x; z[1] += a.y; z[2] += a.z; z[3] += a.w;
+			z[4] += b.x; z[5] += b.y; z[6] += b.z; z[7] += b.w;
+		}
+	} else {
+		for (unsigned j = 0; j < m; ++j) {
+			unsigned c16 = xs[rl + j];
+			const float4* e = reinterpret_cast<const float4*>(lutp + (size_t)j * stride + c16);
+			float4 a = e[0], b = e[8];
+			z[0] += a.x; z[1] += a.y; z[2] += a.z; z[3] += a.w;
+			z[4] += b.x; z[5] += b.y; z[6] += b.z; z[7] += b.w;
+		}
+	}
+}
+
 __device__ __forceinline__ void bwd_fma4(float (&c)[4], float v, const float4& w)
 {
 	c[0] = fmaf(v, w.x, c[0]); c[1] = fmaf(v, w.y, c[1]); c[2] = fmaf(v, w.z, c[2]); c[3] = fmaf(v, w.w, c[3]);
