@@ -338,7 +338,7 @@ def side_workloads(dev, with_cpu, calibration_models=90):
         Xs, Ys = Xall[0].clone(), Yall[0].clone()
         Ms = Mall[0].clone() if Mall is not None else None
         feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)] + ([(Mall, Ms)] if Ms is not None else []))
-        K = 8                                         # steps per replay: the host's cost of a replay is above a small step's GPU time
+        K = 32                                        # steps per replay: a replay costs the host about as much as two small steps take on the GPU
         graph, _ = net.capture_train_step(Xs, R1, Ys, Ms, feed=feed, steps=K)
 
         def step():
@@ -413,7 +413,7 @@ def calibration_sharded(dev, rank, world):
     net.set_rates(lr_all[ids], 0.9)
     Xs, Ys = Xall[0].clone(), Yall[0].clone()
     feed = fused.MinibatchFeed([(Xall, Xs), (Yall, Ys)])
-    K = 8                                             # steps per replay
+    K = 32                                            # steps per replay
     # few models per GPU: the two-launch step (a CTA per sample and model) where its gradient shares stay small
     mstep = net.ministep(Xall, R1, Yall, None, max_rows=Lc + M - 1)
     if mstep is not None and mstep.scratch_bytes <= (8 << 20):
