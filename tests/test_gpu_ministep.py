@@ -89,6 +89,38 @@ def test_one_step_equals_the_operator_fused_step(cuda, I, pool, hidden, loss, ki
     assert float((ms.PL - want).abs().max()) <= 1e-7 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("I,nmotif,pool,hidden,B,L,m", [
+    (2, 32, "all", 16, 6, 30, 24),      # 32 filters per model: two groups of 16 in the scan, 64 pooled features
+    (1, 16, "max", 128, 2, 1, 8),       # one-base sequences (rows = filter length), the widest hidden layer
+    (3, 16, "avg", 0, 1, 200, 16),      # a single sample of 215 rows
+])
+def test_edge_shapes(cuda, I, nmotif, pool, hidden, B, L, m):
+    import torch
+    from deepbind_b200 import synth
+    from deepbind_b200.model import DeepBindNet
+    p = synth.model_params(I, m, 13, pool, hidden=hidden, nmotif=nmotif)
+    Xh, Rh = synth.uniform_batch(B, L, m, seed=14)
+    X = torch.from_numpy(Xh).cuda(); R = torch.from_numpy(Rh.view(np.int32)).cuda()
+    Y = torch.from_numpy(synth.rng(15).standard_normal((B, I)).astype(np.float32)).cuda()
+
+    def make():
+        net = DeepBindNet(p, I, pool, loss="mse")
+        net.set_rates(0.01, 0.9)
+        return net
+    old, new = make(), make()
+    loss_old = old.train_step(X, R, Y)
+    ms = new.ministep(X, R, Y)
+    assert ms is not None
+    ms.lookahead()
+    loss_new = ms.run()
+    torch.cuda.synchronize()
+    assert int(ms.status.item()) == 0
+    assert _rel(loss_new, loss_old) <= 2e-6
+    for k, g_old in _blocks(old, "dP").items():
+        assert _rel(_blocks(new, "dP")[k], g_old) <= 2e-5, k
+    assert _rel(new.P, old.P) <= 2e-6
+
+
 def test_steps_over_a_resident_dataset_eager_and_replayed(cuda):
     """Twelve steps over five stacked minibatches in a given order: graph replay equals
     eager launches bit for bit, both follow the operator-fused trainer step for step, and
