@@ -210,6 +210,10 @@ class ShardedScorer(object):
         self.gather = gather if self.world > 1 else "nccl"
         if self.gather == "peer":
             import ctypes
+            import os
+            # the kernel uses plain peer stores; without an NVSwitch multicast binding a rank
+            # that leaves early cannot disturb the others' buffers
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
             if self.world > 8:
                 raise ValueError("the peer gather serves at most 8 ranks (one box)")
