@@ -703,6 +703,10 @@ scanpool_tc_kernel(const tc_args a)
 	if (threadIdx.x < 2) done_cnt[threadIdx.x] = 0u;
 	if (threadIdx.x == 0) {
 		abort_s = *reinterpret_cast<volatile int*>(a.status);
+		if (a.maxabs[1] != 0u) {                                    // a weight was Inf or NaN when the bank was prepared
+			atomicCAS(a.status, 0, 4);
+			abort_s = 4;
+		}
 		rows_s[0] = a.R[2 * g_first];
 		rows_s[1] = max(a.R[2 * (g_last - 1) + 1], rows_s[0]);
 	}
@@ -873,6 +877,7 @@ __global__ void tc_maxabs_kernel(const float* __restrict__ W, size_t count, uint
 	for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
 		const float w = fabsf(W[i]);
 		if (w <= 3.4e38f) mx = max(mx, __float_as_uint(w));        // non-negative floats order like their bit patterns
+		else out[1] = 1u;                                           // Inf or NaN: the scan refuses the bank (status 4)
 	}
 	mx = __reduce_max_sync(0xffffffffu, mx);
 	if ((threadIdx.x & 31) == 0 && mx) atomicMax(out, mx);

@@ -216,5 +216,6 @@ def scanpool_tc(tcw, X, R, ptype="all", relu=True, headW=None, headB=None, want_
         code = int(status.item())
         if code:
             raise _lib.SmatException("scanpool_tc(...) raised an exception\nRuntimeError: tensor-core scan failed: %s" %
-                                     {1: "a device-side wait timed out", 3: "regions must ascend without overlap"}.get(code, code))
+                                     {1: "a device-side wait timed out", 3: "regions must ascend without overlap",
+                                      4: "the filter bank holds an Inf or NaN weight"}.get(code, code))
     return pooled, scores

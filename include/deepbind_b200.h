@@ -307,7 +307,7 @@ void db_scanpool_bwd(uint32_t m, uint32_t nf, const uint8_t* X, uint32_t npos,
  * Regions (8-byte aligned table) must ascend without overlap (the batch layout of
  * data.py:329-334); rows between regions are scanned and discarded.  status: device
  * int the caller zeroes; 0 = ok, 1 = a device-side wait timed out, 3 = regions out
- * of order. */
+ * of order, 4 = the prepared filter bank held an Inf or NaN weight (nothing is written). */
 enum db_tc_precision { DB_TC_BF16 = 1, DB_TC_BF16X2 = 2, DB_TC_BF16X3 = 3, DB_TC_F16X2 = 4, DB_TC_F16 = 5 };
 size_t db_tc_weights_bytes(uint32_t m, uint32_t nf, int precision);
 void db_tc_prepare(const float* W, uint32_t m, uint32_t nf, int precision, void* prepared);

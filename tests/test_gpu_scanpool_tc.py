@@ -175,6 +175,26 @@ def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable(cuda):
     assert bool(torch.isfinite(ok).all())
 
 
+@pytest.mark.parametrize("bad", [np.inf, -np.inf, np.nan])
+def test_a_filter_bank_with_a_non_finite_weight_is_refused(cuda, bad):
+    """max |W| sets the f16 prescale and the bound of the saturating rectifier, so an Inf or
+    NaN weight cannot be scanned: preparing the bank records it, the scan writes nothing and
+    reports status 4."""
+    import torch
+    from deepbind_b200 import fused, synth, SmatException
+    m, I = 24, 8
+    X, R = synth.uniform_batch(64, 101, m, seed=2)
+    p = synth.model_params(I, m, 3, "all")
+    W = p["Wscan"].copy()
+    W[17, 5] = bad
+    tcw = fused.TCWeights(dev(W), dev(p["bscan"]), "f16x2")
+    with pytest.raises(SmatException, match="Inf or NaN"):
+        fused.scanpool_tc(tcw, dev(X), dev(R), "all")
+    good = fused.TCWeights(dev(p["Wscan"]), dev(p["bscan"]), "f16x2")
+    out, _ = fused.scanpool_tc(good, dev(X), dev(R), "all")
+    assert bool(torch.isfinite(out).all())
+
+
 def test_gaps_between_regions_and_tail_rows(cuda, orc):
     from deepbind_b200 import fused
     rng = np.random.default_rng(8)
